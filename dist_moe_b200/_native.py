@@ -1,0 +1,115 @@
+"""ctypes binding of the C-ABI library (``include/dist_moe_b200.h``).
+
+The CUDA library is the only compute path.  If it cannot be loaded the import
+of this module raises: there is no CPU or eager fallback behind it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_float, c_int, c_int32, c_int64, c_uint64, c_void_p
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libdist_moe_b200.so"
+
+RC_NAMES = {0: "ok", -1: "bad argument", -2: "unsupported shape", -3: "too large", -4: "CUDA driver entry point unavailable"}
+STATUS_NAMES = {
+    0: "ok",
+    1: "expert-parallel ranks published different token counts",
+    2: "DistMoE scratch capacity exceeded",
+    3: "expert id outside [-1, num_experts)",
+    4: "barrier timed out waiting for a peer",
+    5: "GEMM pipeline wait timed out",
+    6: "activation arena overflow",
+}
+
+
+class Operand(ctypes.Structure):
+    """``dm_operand``: (allocation base, allocation bytes, device offset pointer)."""
+
+    _fields_ = [("base", c_void_p), ("bytes", c_int64), ("offset", c_void_p)]
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _load() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        from .build import build
+
+        build()
+    if not _LIB_PATH.exists():
+        raise ImportError(f"dist_moe_b200: CUDA library missing at {_LIB_PATH}; run python -m dist_moe_b200.build")
+    return ctypes.CDLL(str(_LIB_PATH))
+
+
+lib = _load()
+
+_P = c_void_p
+_SIGNATURES = {
+    "dm_version": (c_int, []),
+    "dm_publish": (c_int, [_P, _P, c_int, _P, _P, c_int64, c_int64, c_int, c_int, c_int, _P, _P]),
+    "dm_barrier": (c_int, [_P, c_int, c_int, c_int, _P, c_uint64, _P, _P]),
+    "dm_route_workspace_words": (c_int64, [c_int64, c_int, c_int]),
+    "dm_route": (
+        c_int,
+        [_P, _P, _P, c_int, c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int64, c_int64]
+        + [_P] * 7
+        + [c_int64, _P, _P],
+    ),
+    "dm_plan_fwd_bf16": (
+        c_int,
+        [_P] * 10 + [c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, _P, _P],
+    ),
+    "dm_plan_bwd_bf16": (c_int, [_P] * 9 + [c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "dm_gather_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int64, _P, _P]),
+    "dm_cond_copy": (c_int, [_P, _P, _P, _P, c_int64, _P, c_int, _P]),
+    "dm_swiglu_fwd": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_float, c_float, _P, c_float, _P, _P]),
+    "dm_swiglu_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_float, c_float, _P]),
+    "dm_scale_and_sum": (c_int, [_P, _P, c_int, _P, c_int, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int, _P]),
+    "dm_broadcast_and_scale": (c_int, [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_int64, c_int, c_int64, _P]),
+    "dm_gemm_fprop": (
+        c_int,
+        [Operand, _P, Operand, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
+    ),
+    "dm_gemm_dgrad": (c_int, [Operand, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P]),
+    "dm_gemm_wgrad": (c_int, [Operand, Operand, _P, c_int, c_int, _P, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
+}
+
+EXPORTS = tuple(_SIGNATURES)
+
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(rc: int, what: str) -> None:
+    """Raise on a non-zero return code of an entry point."""
+    if rc == 0:
+        return
+    if rc < 0:
+        raise NativeError(f"{what}: {RC_NAMES.get(rc, rc)}")
+    if rc >= 1000:
+        raise NativeError(f"{what}: cuTensorMapEncodeTiled failed with CUresult {rc - 1000}")
+    raise NativeError(f"{what}: CUDA error {rc}")
+
+
+def ptr(t) -> int | None:
+    """Device (or pinned host) address of a tensor, ``None`` for ``None``."""
+    return None if t is None else t.data_ptr()
+
+
+def operand(t, offset=None, nbytes: int | None = None) -> Operand:
+    """Build a ``dm_operand`` from an allocation tensor and an optional device int64 offset tensor."""
+    if t is None:
+        return Operand(None, 0, None)
+    size = t.numel() * t.element_size() if nbytes is None else nbytes
+    return Operand(t.data_ptr(), size, None if offset is None else offset.data_ptr())
+
+
+def stream_ptr() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,606 @@
+// Persistent grouped BF16 GEMMs on tcgen05 tensor cores (sm_100a).
+//
+// One CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: fills a 4-stage shared-memory ring (A 128x64, B 256x64 bf16,
+//               128-byte swizzle) with cp.async.bulk.tensor loads, no multicast.
+//   warp 1      MMA issuer: owns the TMEM allocation (512 columns = two 128x256 fp32
+//               accumulators), issues tcgen05.mma (M128 N256 K16) from one lane and
+//               releases stages / publishes accumulators with tcgen05.commit.
+//   warps 2..5  epilogue: tcgen05.ld their 32 TMEM lanes, convert and store (plain rows,
+//               fused SwiGLU, per-row scatter to peer memory, or weight-gradient
+//               read-modify-write) while the next tile's main loop already runs.
+//
+// Groups are the local experts; their row ranges come from device memory
+// (expert_offsets), so the tile list is built by every CTA at kernel start and no
+// host read is needed.  Activation operands are addressed as (arena base, device
+// byte offset): the tensor map views the whole arena as [row][128-byte line][64 bf16]
+// with overlapping strides, so a planner-chosen offset only changes a coordinate.
+//
+// Three operand arrangements share the kernel:
+//   fprop  C[r,n]  = sum_k A[r,k] W[e][n][k]     A, W K-major
+//   dgrad  C[r,n]  = sum_k A[r,k] W[e][k][n]     A K-major, W N-major
+//   wgrad  dW[e][n][k] (+)= sum_r dY[r,n] X[r,k] both operands MN-major; the ragged last
+//          64-row chunk of an expert is zeroed in shared memory before the MMA reads it.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "../../include/dist_moe_b200.h"
+
+namespace dm {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kMaxGroups = 256;
+constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
+constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 1024;  // + slack for 1024-byte alignment
+
+enum GemmMode : int { kFprop = 0, kDgrad = 1, kWgrad = 2 };
+
+struct GemmParams {
+  CUtensorMap tm_a;
+  CUtensorMap tm_b;
+  const int64_t* a_off;  // device byte offsets (may be null = 0)
+  const int64_t* b_off;
+  const int64_t* c_off;
+  const int64_t* h2_off;
+  uint8_t* c_base;
+  uint8_t* h2_base;
+  const int64_t* scatter_ptrs;
+  const int32_t* expert_offsets;
+  const int* cond;
+  int* status;
+  int e_local;
+  int max_rows;
+  int N;        // output columns (fprop/dgrad), dW rows (wgrad)
+  int Kd;       // contraction (fprop/dgrad), dW columns (wgrad)
+  int fused;    // fprop: W13 gate/up pairing + SwiGLU epilogue (N = 2F)
+  int out_fp32; // wgrad
+  int accumulate;
+  ActParams act;
+};
+
+struct Tile {
+  int e, m_blk, n_blk, row0, row_end, k_iters;
+};
+
+template <int kMode>
+__device__ __forceinline__ Tile decode_tile(int tile, int& e, const int* tile_start, const int* off, int n_tiles,
+                                            int Kd) {
+  while (tile >= tile_start[e + 1]) ++e;
+  const int local = tile - tile_start[e];
+  Tile t;
+  t.e = e;
+  const int rows = off[e + 1] - off[e];
+  if (kMode == kWgrad) {
+    t.n_blk = local % n_tiles;
+    t.m_blk = local / n_tiles;
+    t.row0 = off[e];
+    t.row_end = off[e + 1];
+    t.k_iters = (rows + kBK - 1) / kBK;
+  } else {
+    const int m_tiles = (rows + kBM - 1) / kBM;
+    t.m_blk = local % m_tiles;
+    t.n_blk = local / m_tiles;
+    t.row0 = off[e] + t.m_blk * kBM;
+    t.row_end = off[e + 1];
+    t.k_iters = (Kd + kBK - 1) / kBK;
+  }
+  return t;
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+  if (p.cond != nullptr && *p.cond == 0) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  __shared__ uint64_t full_bar[kStages];
+  __shared__ uint64_t empty_bar[kStages];
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int s_off[kMaxGroups + 1];
+  __shared__ int s_tile_start[kMaxGroups + 1];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- tile table -----------------------------------------------------------
+  const int n_tiles = (kMode == kWgrad) ? (p.Kd + kBN - 1) / kBN
+                                        : (p.fused ? (p.N / 2) / (kBN / 2) : (p.N + kBN - 1) / kBN);
+  const int wgrad_m_tiles = (p.N + kBM - 1) / kBM;
+  for (int i = threadIdx.x; i <= p.e_local; i += blockDim.x) {
+    int v = p.expert_offsets[i];
+    s_off[i] = v < p.max_rows ? v : p.max_rows;
+  }
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 4);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.e_local; ++e) {
+      s_tile_start[e] = acc;
+      const int rows = s_off[e + 1] - s_off[e];
+      acc += (kMode == kWgrad) ? wgrad_m_tiles * n_tiles : ((rows + kBM - 1) / kBM) * n_tiles;
+    }
+    s_tile_start[p.e_local] = acc;
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&p.tm_a);
+    tma_prefetch_desc(&p.tm_b);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const int total_tiles = s_tile_start[p.e_local];
+
+  const int64_t a_off = p.a_off ? *p.a_off : 0;
+  const int64_t b_off = p.b_off ? *p.b_off : 0;
+
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    int stage = 0;
+    uint32_t phase = 0;
+    int e = 0;
+    const int a_line0 = static_cast<int>(a_off >> 7);
+    const int b_line0 = static_cast<int>(b_off >> 7);
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
+      for (int kb = 0; kb < t.k_iters; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
+          if (ok) {
+            uint8_t* sa = smem + stage * kStageBytes;
+            uint8_t* sb = sa + kABytes;
+            mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+            if (kMode == kWgrad) {
+              const int row = t.row0 + kb * kBK;
+#pragma unroll
+              for (int b = 0; b < kBM / 64; ++b)
+                tma_load_3d(sa + b * 8192, &p.tm_a, 0, a_line0 + t.m_blk * (kBM / 64) + b, row, &full_bar[stage]);
+#pragma unroll
+              for (int b = 0; b < kBN / 64; ++b)
+                tma_load_3d(sb + b * 8192, &p.tm_b, 0, b_line0 + t.n_blk * (kBN / 64) + b, row, &full_bar[stage]);
+            } else {
+              tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
+              if (kMode == kFprop) {
+                int r0, r1;
+                if (p.fused) {
+                  const int F = p.N / 2;
+                  r0 = t.e * p.N + t.n_blk * (kBN / 2);
+                  r1 = r0 + F;
+                } else {
+                  r0 = t.e * p.N + t.n_blk * kBN;
+                  r1 = r0 + kBN / 2;
+                }
+                tma_load_2d(sb, &p.tm_b, kb * kBK, r0, &full_bar[stage]);
+                tma_load_2d(sb + kBBytes / 2, &p.tm_b, kb * kBK, r1, &full_bar[stage]);
+              } else {
+#pragma unroll
+                for (int b = 0; b < kBN / 64; ++b)
+                  tma_load_2d(sb + b * 8192, &p.tm_b, t.n_blk * kBN + b * 64, t.e * p.Kd + kb * kBK,
+                              &full_bar[stage]);
+              }
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, kMode == kWgrad ? 1 : 0, kMode == kFprop ? 0 : 1);
+    int stage = 0;
+    uint32_t phase = 0;
+    int e = 0;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (lane == 0) ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * kBN;
+      for (int kb = 0; kb < t.k_iters; ++kb) {
+        if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        tcgen05_fence_after();
+        uint8_t* sa = smem + stage * kStageBytes;
+        uint8_t* sb = sa + kABytes;
+        if (kMode == kWgrad) {
+          const int valid = (t.row_end - t.row0) - kb * kBK;  // rows of this chunk that belong to the expert
+          if (valid < kBK) {
+            // Rows [valid, 64) of every 64x64 box are one contiguous byte range.
+            const int vec_per_box = (kBK - valid) * 8;
+            const int boxes = (kBM + kBN) / 64;
+            for (int i = lane; i < boxes * vec_per_box; i += 32) {
+              const int box = i / vec_per_box, v = i - box * vec_per_box;
+              reinterpret_cast<uint4*>(sa + box * 8192 + valid * 128)[v] = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sa), b_addr = smem_u32(sb);
+#pragma unroll
+          for (int j = 0; j < kBK / 16; ++j) {
+            uint64_t da, db;
+            if (kMode == kWgrad) {
+              da = umma_smem_desc(a_addr + j * 2048, 8192, 1024);
+            } else {
+              da = umma_smem_desc(a_addr + j * 32, 16, 1024);
+            }
+            if (kMode == kFprop) {
+              db = umma_smem_desc(b_addr + j * 32, 16, 1024);
+            } else {
+              db = umma_smem_desc(b_addr + j * 2048, 8192, 1024);
+            }
+            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok) break;
+      if (lane == 0) {
+        if (t.k_iters > 0)
+          tcgen05_commit(&tmem_full_bar[buf]);
+        else
+          mbar_arrive(&tmem_full_bar[buf]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ======================= epilogue =======================
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32)
+    const int row_in_tile = quad * 32 + lane;
+    int e = 0;
+    int it = 0;
+    bool ok = true;
+    const int64_t c_off = p.c_off ? *p.c_off : 0;
+    const int64_t h2_off = p.h2_off ? *p.h2_off : 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;
+
+      if (kMode == kWgrad) {
+        const int out_row = t.m_blk * kBM + row_in_tile;       // row of dW[e]
+        const bool row_ok = out_row < p.N;
+        const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kd;
+        for (int c0 = 0; c0 < kBN; c0 += 32) {
+          uint32_t r[32];
+          if (t.k_iters > 0) {
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          const int col = t.n_blk * kBN + c0;
+          if (row_ok && col < p.Kd) {
+            if (p.out_fp32) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c_base) + row_elems + col);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (col + 4 * j + 4 <= p.Kd) {
+                  float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                  if (p.accumulate) {
+                    const float4 o = dst[j];
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                  }
+                  dst[j] = v;
+                }
+              }
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c_base) + row_elems + col);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col + 8 * j + 8 <= p.Kd) {
+                  float f[8];
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[8 * j + q]);
+                  if (p.accumulate) {
+                    const uint4 o = dst[j];
+                    const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                      f[2 * q] += __uint_as_float(w[q] << 16);
+                      f[2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u);
+                    }
+                  }
+                  dst[j] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                                      pack_bf16x2(f[6], f[7]));
+                }
+              }
+            }
+          }
+        }
+      } else {
+        const int row = t.row0 + row_in_tile;
+        const bool row_ok = row < t.row_end;
+        uint8_t* out_row = nullptr;
+        if (row_ok) {
+          if (p.scatter_ptrs != nullptr)
+            out_row = reinterpret_cast<uint8_t*>(p.scatter_ptrs[row]);
+          else
+            out_row = p.c_base + c_off + static_cast<int64_t>(row) * p.N * 2;
+        }
+        if (kMode == kFprop && p.fused) {
+          const int F = p.N / 2;
+          uint8_t* h2_row = row_ok ? p.h2_base + h2_off + static_cast<int64_t>(row) * F * 2 : nullptr;
+          for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(taddr + c0, g);
+            tmem_ld_32x32(taddr + kBN / 2 + c0, u);
+            tmem_ld_wait();
+            const int col = t.n_blk * (kBN / 2) + c0;  // column inside the gate (and up) half
+            if (out_row != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t gp[4], up[4], zp[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  gp[q] = pack_bf16x2(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(g[8 * j + 2 * q + 1]));
+                  up[q] = pack_bf16x2(__uint_as_float(u[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q + 1]));
+                  const float z0 = swiglu_f32(__uint_as_float(gp[q] << 16), __uint_as_float(up[q] << 16), p.act);
+                  const float z1 =
+                      swiglu_f32(__uint_as_float(gp[q] & 0xffff0000u), __uint_as_float(up[q] & 0xffff0000u), p.act);
+                  zp[q] = pack_bf16x2(z0, z1);
+                }
+                if (col + 8 * j + 8 <= F) {
+                  *reinterpret_cast<uint4*>(out_row + (col + 8 * j) * 2) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
+                  *reinterpret_cast<uint4*>(out_row + (F + col + 8 * j) * 2) = make_uint4(up[0], up[1], up[2], up[3]);
+                  *reinterpret_cast<uint4*>(h2_row + (col + 8 * j) * 2) = make_uint4(zp[0], zp[1], zp[2], zp[3]);
+                }
+              }
+            }
+          }
+        } else {
+          for (int c0 = 0; c0 < kBN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+            const int col = t.n_blk * kBN + c0;
+            if (out_row != nullptr && col < p.N) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col + 8 * j + 8 <= p.N) {
+                  uint4 v;
+                  v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+                  v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                  v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                  v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                  *reinterpret_cast<uint4*>(out_row + (col + 8 * j) * 2) = v;
+                }
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) set_status(p.status, kPipelineTimeout, kMode, blockIdx.x);
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor-map encoding through the driver entry point (no link-time
+// dependency on libcuda) and launch.
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 matrix [rows][cols], cols contiguous; box = box_rows x 64 columns.
+static int encode_2d(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return kRcNoDriver;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
+}
+
+// Arena view: element (c0, line, row) lives at base + 2*c0 + 128*line + pitch*row.
+// `line` spans the whole allocation, so an operand at byte offset o is reached
+// with line = o/128 + column/64; rows may run `guard` rows past the operand.
+static int encode_arena(CUtensorMap* tm, const dm_operand& op, int64_t pitch_bytes, int64_t rows, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return kRcNoDriver;
+  const int64_t lines = op.bytes / 128;
+  if (lines <= 0 || (pitch_bytes % 128) != 0 || (reinterpret_cast<uintptr_t>(op.base) % 128) != 0) return kRcBadArg;
+  cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(lines), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(pitch_bytes)};
+  cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, op.base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int kMode>
+static int launch(const GemmParams& p, int num_sms, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kGemmSmemBytes));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const int grid = num_sms > 0 ? num_sms : sm_count();
+  grouped_gemm_kernel<kMode><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace dm
+
+using namespace dm;
+
+extern "C" int dm_gemm_fprop(dm_operand a, const void* w, dm_operand c, dm_operand h2, const int64_t* scatter_ptrs,
+                             const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
+                             int fuse_swiglu, int clamped, float alpha, float limit, const int* cond, int num_sms,
+                             int* status, void* stream) {
+  if (!a.base || !w || !expert_offsets || e_local <= 0 || max_rows < 0 || N <= 0 || Kd <= 0) return kRcBadArg;
+  if (!c.base && !scatter_ptrs) return kRcBadArg;
+  if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
+  if ((Kd % 64) != 0 || (N % 8) != 0) return kRcUnsupportedShape;
+  if (fuse_swiglu && (((N / 2) % (kBN / 2)) != 0 || !h2.base || !c.base || scatter_ptrs)) return kRcUnsupportedShape;
+  if (max_rows == 0) return kRcOk;
+  GemmParams p{};
+  int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
+  if (rc != kRcOk) return rc;
+  rc = encode_2d(&p.tm_b, w, static_cast<int64_t>(e_local) * N, Kd, kBN / 2);
+  if (rc != kRcOk) return rc;
+  p.a_off = a.offset;
+  p.c_off = c.offset;
+  p.h2_off = h2.offset;
+  p.c_base = static_cast<uint8_t*>(c.base);
+  p.h2_base = static_cast<uint8_t*>(h2.base);
+  p.scatter_ptrs = scatter_ptrs;
+  p.expert_offsets = expert_offsets;
+  p.cond = cond;
+  p.status = status;
+  p.e_local = e_local;
+  p.max_rows = static_cast<int>(max_rows);
+  p.N = static_cast<int>(N);
+  p.Kd = static_cast<int>(Kd);
+  p.fused = fuse_swiglu ? 1 : 0;
+  p.act = ActParams{clamped, alpha, limit};
+  return launch<kFprop>(p, num_sms, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dm_gemm_dgrad(dm_operand a, const void* w, dm_operand c, const int64_t* scatter_ptrs,
+                             const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
+                             const int* cond, int num_sms, int* status, void* stream) {
+  if (!a.base || !w || !expert_offsets || e_local <= 0 || max_rows < 0 || N <= 0 || Kd <= 0) return kRcBadArg;
+  if (!c.base && !scatter_ptrs) return kRcBadArg;
+  if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
+  if ((Kd % 64) != 0 || (N % 8) != 0) return kRcUnsupportedShape;
+  if (max_rows == 0) return kRcOk;
+  GemmParams p{};
+  int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
+  if (rc != kRcOk) return rc;
+  // W = [e_local * Kd][N], N contiguous; box = 64 k-rows x 64 columns.
+  rc = encode_2d(&p.tm_b, w, static_cast<int64_t>(e_local) * Kd, N, 64);
+  if (rc != kRcOk) return rc;
+  p.a_off = a.offset;
+  p.c_off = c.offset;
+  p.c_base = static_cast<uint8_t*>(c.base);
+  p.scatter_ptrs = scatter_ptrs;
+  p.expert_offsets = expert_offsets;
+  p.cond = cond;
+  p.status = status;
+  p.e_local = e_local;
+  p.max_rows = static_cast<int>(max_rows);
+  p.N = static_cast<int>(N);
+  p.Kd = static_cast<int>(Kd);
+  return launch<kDgrad>(p, num_sms, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int accumulate,
+                             const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
+                             int num_sms, int* status, void* stream) {
+  if (!dy.base || !x.base || !dw || !expert_offsets || e_local <= 0 || max_rows < 0 || N <= 0 || Kd <= 0)
+    return kRcBadArg;
+  if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
+  if ((N % 64) != 0 || (Kd % 64) != 0) return kRcUnsupportedShape;
+  GemmParams p{};
+  int rc = encode_arena(&p.tm_a, dy, N * 2, max_rows + 256, kBK);
+  if (rc != kRcOk) return rc;
+  rc = encode_arena(&p.tm_b, x, Kd * 2, max_rows + 256, kBK);
+  if (rc != kRcOk) return rc;
+  p.a_off = dy.offset;
+  p.b_off = x.offset;
+  p.c_base = static_cast<uint8_t*>(dw);
+  p.expert_offsets = expert_offsets;
+  p.status = status;
+  p.e_local = e_local;
+  p.max_rows = static_cast<int>(max_rows);
+  p.N = static_cast<int>(N);
+  p.Kd = static_cast<int>(Kd);
+  p.out_fp32 = out_is_fp32 ? 1 : 0;
+  p.accumulate = accumulate ? 1 : 0;
+  return launch<kWgrad>(p, num_sms, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,205 @@
+/*
+ * dist_moe_b200 -- C ABI of the routed-expert hot path (sm_100a).
+ *
+ * Every entry point is `extern "C"`, takes raw device pointers, sizes and a
+ * CUDA stream (passed as void*; it is a cudaStream_t), launches asynchronously
+ * on that stream, never synchronises, never allocates device memory, and
+ * returns 0 on success, a negative DM_RC_* for an argument error, or a positive
+ * cudaError_t.  Contract violations that only the device can see (unequal token
+ * counts between ranks, receive capacity exceeded, invalid expert id, a peer
+ * that never arrived) are reported through `status` (int32[8], word 0 = first
+ * DM_STATUS_* code) instead of trapping, and make the dependent kernels no-ops.
+ *
+ * Each declaration names the reference interface it stands in for
+ * (paths relative to the dist_moe repository).
+ */
+#ifndef DIST_MOE_B200_H_
+#define DIST_MOE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DM_RC_OK 0
+#define DM_RC_BAD_ARG (-1)
+#define DM_RC_UNSUPPORTED_SHAPE (-2)
+#define DM_RC_TOO_LARGE (-3)
+#define DM_RC_NO_DRIVER (-4)
+
+#define DM_STATUS_OK 0
+#define DM_STATUS_TOKEN_COUNT_MISMATCH 1
+#define DM_STATUS_CAPACITY_EXCEEDED 2
+#define DM_STATUS_INVALID_EXPERT_ID 3
+#define DM_STATUS_BARRIER_TIMEOUT 4
+#define DM_STATUS_PIPELINE_TIMEOUT 5
+#define DM_STATUS_ARENA_OVERFLOW 6
+
+/* Bytes of the routing-buffer header that precedes the int16 expert ids
+ * (dist_moe/_buffers.py:33-35). Word 0 of the header is the int32 token count. */
+#define DM_ROUTING_HEADER_BYTES 128
+
+/* Library version / build probe; returns the compiled SM architecture (1000). */
+int dm_version(void);
+
+/* ---------------------------------------------------------------------------
+ * Publication  (dist_moe/kernels/triton/conditional_copy.py:158-212, 302-361
+ * `copy_routing_and_dispatch`; 133-155 `copy_routing`)
+ *   dispatch_local[0 : T*D]   = x            (bf16, skipped when x == NULL)
+ *   routing_local header      = int32 T
+ *   routing_local ids         = int16(ids)   (ids are int32 or int64)
+ * validate != 0 checks ids in [-1, E) and reports DM_STATUS_INVALID_EXPERT_ID.
+ * ------------------------------------------------------------------------- */
+int dm_publish(const void* x_bf16, const void* ids, int ids_are_int64, void* dispatch_local,
+               void* routing_local, int64_t T, int64_t D, int K, int E, int validate, int* status,
+               void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Expert-parallel device barrier (dist_moe/_triton_ops.py:61-102
+ * `symmetric_memory_barrier`; kernel dist_moe/kernels/triton/barrier.py:31-61).
+ * signal_pads: device array of `ep` addresses, one uint32 pad per rank, pad
+ * layout [channel][ep].  `cond` (int32*, may be NULL) predicates the barrier on
+ * the device.  The wait is bounded by timeout_ns; on expiry the kernel records
+ * DM_STATUS_BARRIER_TIMEOUT and returns.
+ * ------------------------------------------------------------------------- */
+int dm_barrier(const uint64_t* signal_pads, int rank, int ep, int channel, const int* cond,
+               uint64_t timeout_ns, int* status, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Routing metadata (dist_moe/_routing_metadata.py:718-1102
+ * `dist_dispatch_routing`; kernels
+ * dist_moe/kernels/triton/dist_dispatch_routing_kernel.py:298-956).
+ *
+ * Inputs: the peers' published routing buffers (device array of `ep`
+ * addresses), the peers' dispatch/combine buffer addresses, strides in bytes.
+ * Outputs (all device):
+ *   counts[e_local]         rows per local expert (rounded up to m_multiple_of when > 0)
+ *   per_rank[ep]            rows every rank receives (same rounding)
+ *   expert_offsets[e_local+1] exclusive prefix of counts; last entry = rows received
+ *   fwd/bwd/sct pointer tables int64[ptrs_size]; rows ordered by (local expert,
+ *   source rank, token); padding rows hold 0.  bwd may be NULL.
+ * Workspace: int32 words, at least dm_route_workspace_words(...).
+ * A capacity violation sets DM_STATUS_CAPACITY_EXCEEDED and zeroes the counts.
+ * ------------------------------------------------------------------------- */
+int64_t dm_route_workspace_words(int64_t T, int ep, int E);
+int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
+             int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
+             int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,
+             int64_t capacity_rows, int64_t ptrs_size, int32_t* counts, int32_t* per_rank,
+             int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
+             int64_t* scatter_ptrs, int32_t* workspace, int64_t workspace_words, int* status,
+             void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Activation-arena planner, BF16
+ * (dist_moe/_activation_buffer.py:2318-2591 `get_forward_plan`/`get_backward_plan`;
+ * kernels dist_moe/_activation_buffer_planner_kernel.py:1068-1477).
+ * All state tensors are device int64 and updated in place exactly as the
+ * reference does.  fwd_state = [x, x_gathered, h1, h2, h3, slot id],
+ * bwd_offsets = [x_gathered, h1, h2, grad_h2, grad_h3_gathered, grad_h1].
+ * need_recompute is one byte (bool).  Overflow sets DM_STATUS_ARENA_OVERFLOW.
+ * ------------------------------------------------------------------------- */
+int dm_plan_fwd_bf16(const int32_t* recv_rows, const int32_t* per_rank, int64_t* saved_bytes_per_rank,
+                     int64_t* buffer_offsets, int64_t* peak_min_free, uint8_t* need_recompute,
+                     int32_t* recompute_cond, int64_t* fwd_state, const int64_t* slot_selector,
+                     int64_t* moe_layer_id, int ep, int64_t num_tokens, int K, int64_t D, int64_t F,
+                     int64_t slot_bytes, int num_slots, int num_moe_layers, int scratch_only,
+                     int* status, void* stream);
+int dm_plan_bwd_bf16(const int32_t* recv_rows, const int32_t* per_rank, int64_t* saved_bytes_per_rank,
+                     int64_t* buffer_offsets, int64_t* peak_min_free, const uint8_t* need_recompute,
+                     const int64_t* fwd_state, int64_t* bwd_offsets, int64_t* moe_layer_id, int ep,
+                     int64_t num_tokens, int K, int64_t D, int64_t F, int64_t slot_bytes, int num_slots,
+                     int* status, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Row gather (the gather half of dist_moe/kernels/dist_grouped_gemm.py:1148-1237
+ * `dist_grouped_gemm_fprop_dispatch` and 1441-1489 `..._dgrad_dispatch`):
+ *   dst[r, :] = *(ptrs[r])   for r < *num_rows, a zero row where ptrs[r] == 0.
+ * dst = dst_base + (dst_offset ? *dst_offset : 0).  Sources may be peer memory.
+ * ------------------------------------------------------------------------- */
+int dm_gather_rows(const int64_t* ptrs, const int32_t* num_rows, void* dst_base, const int64_t* dst_offset,
+                   int64_t row_bytes, int64_t max_rows, const int* cond, void* stream);
+
+/* Device-predicated copy (dist_moe/kernels/triton/conditional_copy.py:482-630).
+ * Copies `bytes` from src(+*src_offset) to dst(+*dst_offset) when cond is NULL
+ * or (*cond != 0) == (expect != 0). */
+int dm_cond_copy(const void* src_base, const int64_t* src_offset, void* dst_base, const int64_t* dst_offset,
+                 int64_t bytes, const int* cond, int expect, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * SwiGLU (dist_moe/kernels/triton/swiglu.py:272-504 `swiglu_fwd`, 671-925 `swiglu_bwd`)
+ *   h1 = [gate | up] rows of 2F bf16, h2 rows of F bf16, fp32 math.
+ *   clamped: g = min(gate, limit), u = clamp(up, +-limit), h2 = g*sigmoid(alpha*g)*(u+1).
+ *   clip_stats (fp32[3], may be NULL) += [#gate > clip_limit, #|up| > clip_limit, #valid].
+ * Row count is read from *num_rows.
+ * ------------------------------------------------------------------------- */
+int dm_swiglu_fwd(const void* h1_base, const int64_t* h1_offset, void* h2_base, const int64_t* h2_offset,
+                  const int32_t* num_rows, int64_t max_rows, int64_t F, int clamped, float alpha, float limit,
+                  float* clip_stats, float clip_limit, const int* cond, void* stream);
+int dm_swiglu_bwd(const void* h1_base, const int64_t* h1_offset, const void* grad_h2_base,
+                  const int64_t* grad_h2_offset, void* grad_h1_base, const int64_t* grad_h1_offset,
+                  const int32_t* num_rows, int64_t max_rows, int64_t F, int clamped, float alpha, float limit,
+                  void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Top-k reduction and its backward
+ * (dist_moe/kernels/triton/broadcast_n_reduction.py:70-183 `scale_and_sum`,
+ *  723-805 `reduce_from_topk`, 386-511 `broadcast_and_scale`).
+ *   scale_and_sum:       out[t,:] = bf16( sum_k scores[t,k] * h3[t,k,:] ), routes with id < 0 skipped;
+ *                        scores == NULL means weight 1 (reduce_from_topk).
+ *                        save_base(+*save_offset) (may be NULL) receives a copy of h3 when save_cond is
+ *                        NULL or (*save_cond != 0) == (save_expect != 0).
+ *   broadcast_and_scale: grad_h3[t,k,:] = bf16(scores[t,k] * grad_out[t,:]);
+ *                        grad_scores[t,k] = sum_d h3[t,k,d] * grad_out[t,d]  (0 for id < 0).
+ * scores are fp32 or bf16 (scores_are_bf16); ids int32 or int64.
+ * ------------------------------------------------------------------------- */
+int dm_scale_and_sum(const void* h3, const void* scores, int scores_are_bf16, const void* ids, int ids_are_int64,
+                     void* out, int64_t T, int K, int64_t D, void* save_base, const int64_t* save_offset,
+                     const int* save_cond, int save_expect, void* stream);
+int dm_broadcast_and_scale(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
+                           int ids_are_int64, const void* h3_base, const int64_t* h3_offset, void* grad_h3,
+                           float* grad_scores, int64_t T, int K, int64_t D, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * BF16 grouped GEMMs on tcgen05/TMEM fed by TMA
+ * (dist_moe/kernels/dist_grouped_gemm.py:1148-1237 fprop dispatch, 1498-1556
+ *  fprop combine, 1441-1489 dgrad dispatch, 1559-1608 dgrad combine;
+ *  dist_moe/kernels/grouped_gemm.py:640- `grouped_gemm_wgrad`).
+ *
+ * Activations live in the arena: an operand is (arena_base, arena_bytes,
+ * device int64 byte offset).  Rows of local expert e are
+ * [expert_offsets[e], expert_offsets[e+1]); padding rows are zero rows whose
+ * scatter pointer is 0.  The allocation behind an operand must extend at least
+ * 256 rows past the operand's last row (guard tail): edge tiles read, but never
+ * use, what lies there.
+ *
+ *  dm_gemm_fprop:   C[r, :] = A[r, :] * W[e]^T           W = [e_local, N, Kd] (Kd contiguous)
+ *     fuse_swiglu != 0: W = [e_local, 2, F, Kd]; writes h1 = C (2F wide) and h2 = SwiGLU(h1).
+ *     scatter_ptrs != NULL: row r of C goes to scatter_ptrs[r] (peer memory) instead of C.
+ *  dm_gemm_dgrad:   C[r, :] = A[r, :] * W[e]             W = [e_local, Kd, N] (N contiguous), A = [rows, Kd]
+ *     scatter_ptrs as above.
+ *  dm_gemm_wgrad:   dW[e] (+)= dY[e]^T * X[e]            dY = [rows, N], X = [rows, Kd], dW = [e_local, N, Kd]
+ *     out_is_fp32 selects fp32 or bf16 dW; accumulate != 0 adds into dW.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  void* base;             /* arena (or any 256-byte aligned allocation) */
+  int64_t bytes;          /* extent of that allocation, including the guard tail */
+  const int64_t* offset;  /* device byte offset of the operand, NULL = 0 */
+} dm_operand;
+
+int dm_gemm_fprop(dm_operand a, const void* w, dm_operand c, dm_operand h2, const int64_t* scatter_ptrs,
+                  const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
+                  int64_t Kd, int fuse_swiglu, int clamped, float alpha, float limit, const int* cond, int num_sms,
+                  int* status, void* stream);
+int dm_gemm_dgrad(dm_operand a, const void* w, dm_operand c, const int64_t* scatter_ptrs,
+                  const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
+                  int64_t Kd, const int* cond, int num_sms, int* status, void* stream);
+int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int accumulate,
+                  const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
+                  int64_t Kd, int num_sms, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIST_MOE_B200_H_ */

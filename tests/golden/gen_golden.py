@@ -1,0 +1,243 @@
+"""Generate golden vectors by executing the reference's own code on the CPU.
+
+Run in a container that has the reference checkout (default ``/root/reference``):
+
+    python tests/golden/gen_golden.py [--reference /root/reference]
+
+What runs, unmodified, from the reference:
+* ``dist_moe.plan_memory`` (pure Python) -> ``plan_memory.json``;
+* the Triton routing kernels (gather / split / prefix / combine,
+  ``dist_moe/kernels/triton/dist_dispatch_routing_kernel.py``) and the BF16 planner
+  kernels (``dist_moe/_activation_buffer_planner_kernel.py``) under Triton's CPU
+  interpreter (``TRITON_INTERPRET=1``) -> ``routing_*.npz``, ``planner_bf16.json``.
+
+Three shims make the interpreter accept those kernels; none changes arithmetic:
+``range`` inside the kernel module yields interpreter scalars (the kernels call
+``.to(...)`` on loop indices), ``device_trap_if`` (inline PTX ``trap``) becomes a
+Python assertion, and ``get_flat_tid`` (inline PTX read of %tid) returns 0.  Peer buffers are ordinary host arrays whose addresses are
+passed where the kernels expect peer pointers.
+"""
+
+from __future__ import annotations
+
+import argparse
+import builtins
+import json
+import os
+import sys
+from pathlib import Path
+
+os.environ["TRITON_INTERPRET"] = "1"
+HERE = Path(__file__).resolve().parent
+
+
+def _shim(module, np, tl, TensorHandle):
+    def _range(*args):
+        vals = [int(a.handle.data.item()) if hasattr(a, "handle") else int(a) for a in args]
+        for i in builtins.range(*vals):
+            yield tl.core.tensor(TensorHandle(np.array([i], dtype=np.int32), tl.int32), tl.int32)
+
+    def _trap(cond):
+        data = cond.handle.data if hasattr(cond, "handle") else np.asarray(cond)
+        assert not bool(np.any(data)), "reference kernel would trap"
+
+    def _flat_tid():
+        return tl.core.tensor(TensorHandle(np.array([0], dtype=np.int32), tl.int32), tl.int32)
+
+    module.range = _range
+    if hasattr(module, "device_trap_if"):
+        module.device_trap_if = _trap
+    if hasattr(module, "get_flat_tid"):
+        module.get_flat_tid = _flat_tid  # the reference reads %tid with inline PTX; one program = thread 0
+
+
+def gen_plan_memory(ref):
+    import dist_moe
+    import torch
+
+    F = dist_moe.BlockScaledFormat
+    cases = {
+        "tiny_bf16": (dict(max_num_local_input_tokens=16, hidden_dim=256, intermediate_dim=256, top_k=2, num_experts=8,
+                           max_moe_layers_per_activation_slot=1), 2),
+        "c2_bf16_ep8": (dict(max_num_local_input_tokens=4096, hidden_dim=2048, intermediate_dim=1408, top_k=6,
+                             num_experts=64, max_moe_layers_per_activation_slot=1,
+                             activation_slot_capacity_factor=1.0), 8),
+        "c2_bf16_ep1": (dict(max_num_local_input_tokens=4096, hidden_dim=2048, intermediate_dim=1408, top_k=6,
+                             num_experts=64, max_moe_layers_per_activation_slot=1,
+                             activation_slot_capacity_factor=1.0), 1),
+        "bf16_two_slots": (dict(max_num_local_input_tokens=512, hidden_dim=1024, intermediate_dim=2048, top_k=4,
+                                num_experts=32, max_moe_layers_per_activation_slot=3, num_activation_slots=2,
+                                device_scratch_capacity_factor=1.5, activation_slot_capacity_factor=0.5), 4),
+        "bf16_exact_bytes": (dict(max_num_local_input_tokens=128, hidden_dim=512, intermediate_dim=384, top_k=2,
+                                  num_experts=8, max_moe_layers_per_activation_slot=2,
+                                  activation_slot_bytes=3_000_000), 2),
+        "bf16_inference": (dict(max_num_local_input_tokens=1024, hidden_dim=2880, intermediate_dim=2880, top_k=4,
+                                num_experts=128, max_moe_layers_per_activation_slot=1, inference=True,
+                                num_activation_slots=0), 8),
+        "c3_mxfp8_ep8": (dict(max_num_local_input_tokens=8192, hidden_dim=4096, intermediate_dim=1536, top_k=8,
+                              num_experts=128, max_moe_layers_per_activation_slot=1,
+                              device_scratch_capacity_factor=1.25,
+                              block_scaled=("MXFP8_E4M3", "staged")), 8),
+        "mxfp8_mega": (dict(max_num_local_input_tokens=256, hidden_dim=512, intermediate_dim=256, top_k=2,
+                            num_experts=16, max_moe_layers_per_activation_slot=2,
+                            activation_slot_capacity_factor=1.0, block_scaled=("MXFP8_E4M3", "mega")), 4),
+        "c4_nvfp4_decode": (dict(max_num_local_input_tokens=128, hidden_dim=7168, intermediate_dim=2048, top_k=8,
+                                 num_experts=256, max_moe_layers_per_activation_slot=1, inference=True,
+                                 num_activation_slots=0, block_scaled=("NVFP4", "staged")), 8),
+        "c4_nvfp4_prefill": (dict(max_num_local_input_tokens=8192, hidden_dim=7168, intermediate_dim=2048, top_k=8,
+                                  num_experts=256, max_moe_layers_per_activation_slot=1, inference=True,
+                                  num_activation_slots=0, block_scaled=("NVFP4", "staged")), 8),
+        "mxfp8_inference": (dict(max_num_local_input_tokens=1024, hidden_dim=3072, intermediate_dim=3072, top_k=8,
+                                 num_experts=128, max_moe_layers_per_activation_slot=1, inference=True,
+                                 num_activation_slots=0, block_scaled=("MXFP8_E4M3", "staged")), 8),
+    }
+    out = {}
+    for name, (kw, ep) in cases.items():
+        kw = dict(kw)
+        spec = dict(kw)
+        bs = kw.pop("block_scaled", None)
+        if bs is not None:
+            kw["block_scaled"] = dist_moe.BlockScaledConfig(format=getattr(F, bs[0]), pipeline=bs[1])
+        plan = dist_moe.plan_memory(dist_moe.Config(**kw), ep)
+        fields = {k: v for k, v in plan.__dict__.items()}
+        out[name] = {"config": spec, "ep_size": ep, "plan": fields, "explain": plan.explain()}
+    (HERE / "plan_memory.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+    print("plan_memory.json:", len(out), "cases")
+
+
+def _ref_route(np, torch, triton, tl, K, ids_all, rank, E, m_mult, bwd, gather_stride, bwd_stride, scatter_stride):
+    """Run the reference's four routing kernels for one rank; mirrors the launcher
+    dist_moe/_routing_metadata.py:886-1102 (grid and buffer shapes only)."""
+    EP, T, topk = ids_all.shape
+    EL = E // EP
+    header = 128
+    bufs = []
+    for s in range(EP):
+        b = np.zeros(header + T * topk * 2, dtype=np.uint8)
+        b[:4] = np.frombuffer(np.int32(T).tobytes(), dtype=np.uint8)
+        b[header:] = np.frombuffer(ids_all[s].astype(np.int16).tobytes(), dtype=np.uint8)
+        bufs.append(torch.from_numpy(b))
+    routing_ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64)
+    disp_base = torch.tensor([(s + 1) << 40 for s in range(EP)], dtype=torch.int64)
+    comb_base = torch.tensor([((s + 1) << 40) | (1 << 39) for s in range(EP)], dtype=torch.int64)
+
+    block_size_k = triton.next_power_of_2(topk)
+    block_size_t = max(1, 256 // block_size_k)
+    max_workers = (512 if bwd else 256) // EP
+    num_workers = max(1, min(max_workers, (T + block_size_t - 1) // block_size_t))
+    num_workers = min(max_workers, triton.next_power_of_2(num_workers))
+    tpw = (T + num_workers - 1) // num_workers
+    cnts = torch.full((EP, EL, num_workers), 12345, dtype=torch.int32)
+    per_rank = torch.full((E,), 777, dtype=torch.int32)
+    gathered = torch.full((EP, T, topk), -7, dtype=torch.int16)
+    gw = max(1, (T + 1023) // 1024)
+    K._triton_dist_gather_metadata[(EP, gw, 1)](
+        routing_buffer_ptrs=routing_ptrs, gathered_expert_ids_ptr=gathered, per_rank_token_cnts_ptr=cnts,
+        num_tokens_per_rank_ptr=per_rank, world_size=EP, num_tokens=T, num_experts=E, topk=topk, block_size_t=1024,
+        num_gather_workers=gw, split_num_workers=num_workers, index_ty=tl.int16, routing_header_size_bytes=header,
+        BLOCK_K=block_size_k, BLOCK_WORLD_SIZE=triton.next_power_of_2(EP))
+    shape = (EP, EL, num_workers, tpw)
+    pr_bwd = torch.zeros(shape, dtype=torch.int64) if bwd else None
+    pr_fwd = torch.zeros(shape, dtype=torch.int64)
+    pr_sct = torch.zeros(shape, dtype=torch.int64)
+    K._triton_dispatch_routing_split[(EP, num_workers, 1)](
+        gathered_expert_ids_ptr=gathered, gather_buffer_ptrs=disp_base, scatter_buffer_ptrs=comb_base,
+        per_rank_token_cnts_ptr=cnts, per_rank_bwd_gather_ptrs_ptr=pr_bwd, gather_stride_bytes=gather_stride,
+        bwd_gather_stride_bytes=bwd_stride, per_rank_fwd_gather_ptrs_ptr=pr_fwd, per_rank_scatter_ptrs_ptr=pr_sct,
+        scatter_stride_bytes=scatter_stride, num_tokens_per_rank_ptr=per_rank, expert_id_offset=rank * EL,
+        dest_rank_base=0, world_size=EP, num_tokens=T, num_experts=E, topk=topk, block_size_t=block_size_t,
+        BLOCK_EL=triton.next_power_of_2(EL), BLOCK_K=block_size_k)
+    from dist_moe._routing_metadata import _routing_ptrs_capacity
+
+    ptrs_size = _routing_ptrs_capacity(world_size=EP, num_tokens=T, topk=topk, num_local_experts=EL,
+                                       m_multiple_of=m_mult, max_num_recv_tokens=None,
+                                       pointer_capacity_multiple_of=1)
+    sentinel = -(1 << 62)
+    out_bwd = torch.full((ptrs_size,), sentinel, dtype=torch.int64) if bwd else None
+    out_fwd = torch.full((ptrs_size,), sentinel, dtype=torch.int64)
+    out_sct = torch.full((ptrs_size,), sentinel, dtype=torch.int64)
+    counts = torch.zeros((EL,), dtype=torch.int32)
+    max_compact = 16 * 148
+    limit = max(1, max_compact // E)
+    cpp = min(num_workers, 1 << (limit.bit_length() - 1))
+    wpc = num_workers // cpp
+    offs = torch.zeros((EP, EL, cpp), dtype=torch.int64)
+    K._triton_dispatch_routing_prefix[(1, 1, 1)](
+        per_rank_token_cnts_ptr=cnts, token_cnts_ptr=counts, num_tokens_per_rank_ptr=per_rank,
+        compact_offsets_ptr=offs, world_size=EP, num_experts=E, num_workers=num_workers, compact_ctas_per_pair=cpp,
+        workers_per_compact_cta=wpc, BLOCK_EL=triton.next_power_of_2(EL), m_multiple_of=m_mult,
+        max_num_recv_tokens=0, has_max_num_recv_tokens=False)
+    K._triton_dispatch_routing_combine[(EP * EL * cpp, 1, 1)](
+        per_rank_token_cnts_ptr=cnts, per_rank_bwd_gather_ptrs_ptr=pr_bwd, per_rank_fwd_gather_ptrs_ptr=pr_fwd,
+        per_rank_scatter_ptrs_ptr=pr_sct, token_cnts_ptr=counts, compact_offsets_ptr=offs,
+        bwd_gather_ptrs_ptr=out_bwd, fwd_gather_ptrs_ptr=out_fwd, scatter_ptrs_ptr=out_sct, world_size=EP,
+        num_experts=E, block_size_t=block_size_t, num_workers=num_workers, num_tokens_per_worker=tpw,
+        compact_ctas_per_pair=cpp, workers_per_compact_cta=wpc, m_multiple_of=m_mult)
+    res = dict(counts=counts.numpy(), per_rank=per_rank[:EP].numpy().copy(), fwd=out_fwd.numpy(),
+               sct=out_sct.numpy(), disp_base=disp_base.numpy(), comb_base=comb_base.numpy(),
+               sentinel=np.int64(sentinel))
+    if bwd:
+        res["bwd"] = out_bwd.numpy()
+    return res
+
+
+def gen_routing(ref):
+    import numpy as np
+    import torch
+    import triton
+    import triton.language as tl
+    from triton.runtime.interpreter import TensorHandle
+
+    from dist_moe.kernels.triton import dist_dispatch_routing_kernel as K
+
+    _shim(K, np, tl, TensorHandle)
+    rng = np.random.default_rng(2027)
+
+    def random_ids(EP, T, topk, E, drop=0.0, skew=None):
+        ids = np.empty((EP, T, topk), dtype=np.int64)
+        p = None
+        if skew is not None:
+            p = 1.0 / np.arange(1, E + 1) ** skew
+            p /= p.sum()
+        for s in range(EP):
+            for t in range(T):
+                ids[s, t] = rng.choice(E, size=topk, replace=False, p=p)
+        if drop:
+            ids[rng.random(ids.shape) < drop] = -1
+        return ids
+
+    cases = {}
+    EP, T, topk, E = 2, 16, 2, 8  # quickstart ids: (global_token*K + k) % E
+    ids = np.stack([(((r * T + np.arange(T))[:, None] * topk + np.arange(topk)[None, :]) % E) for r in range(EP)])
+    cases["quickstart"] = (ids, E, 0, True, 512, 512, 512)
+    cases["random_ep4"] = (random_ids(4, 300, 3, 16, drop=0.1), 16, 0, True, 2048, 2048, 2048)
+    cases["skew_pad128"] = (random_ids(2, 200, 4, 8, skew=1.1), 8, 128, True, 1024, 1024, 1024)
+    cases["packed_stride_pad128_nobwd"] = (random_ids(4, 64, 2, 8, drop=0.05), 8, 128, False, 4048, 0, 14336)
+    cases["single_rank"] = (random_ids(1, 130, 2, 4), 4, 0, True, 256, 256, 256)
+    cases["multi_chunk"] = (random_ids(2, 600, 2, 4), 4, 0, True, 128, 128, 128)
+    for name, (ids, E, m_mult, bwd, gs, bs, ss) in cases.items():
+        EP = ids.shape[0]
+        blob = {"ids": ids.astype(np.int16), "num_experts": np.int64(E), "m_multiple_of": np.int64(m_mult),
+                "gather_stride": np.int64(gs), "bwd_stride": np.int64(bs), "scatter_stride": np.int64(ss)}
+        for rank in range(EP):
+            res = _ref_route(np, torch, triton, tl, K, ids, rank, E, m_mult, bwd, gs, bs if bwd else gs, ss)
+            for k, v in res.items():
+                blob[f"r{rank}_{k}"] = v
+        np.savez_compressed(HERE / f"routing_{name}.npz", **blob)
+        print("routing", name, "ok")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    steps = {"plan": gen_plan_memory, "routing": gen_routing}
+    for name, fn in steps.items():
+        if not args.only or name in args.only.split(","):
+            fn(args.reference)
+
+
+if __name__ == "__main__":
+    main()

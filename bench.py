@@ -1,0 +1,333 @@
+"""Benchmark of the routed-expert layer (BF16 training layer, forward + backward).
+
+Workload (``BASELINE.json`` configs[1]): T=4096 tokens per rank, D=2048, F=1408, E=64 experts
+sharded over the ranks (E_local = 64 / N), top-6 softmax routing renormalised to 1, plain
+SwiGLU, weight gradients accumulated in place into ``parameter.grad``.  Inputs are seeded
+synthetic data: x ~ N(0,1), weights ~ N(0,0.02), router logits ~ N(0,1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+For N > 1 launch one process per GPU with ``python -m torch.distributed.run``.  Rank 0 prints
+one JSON line.  ``--impl reference`` times the CPU restatement of the reference's math
+(``oracle/moe.py``; the reference itself has no CPU path and its GPU kernels need a newer
+software stack than this image) on the host cores, on a bounded token sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+T, D, F, E, K = 4096, 2048, 1408, 64, 6
+CPU_SAMPLE_TOKENS = 256
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return FALLBACK_PEAKS, "fallback"
+
+
+def make_inputs(rank: int, world: int, device, tokens: int = T):
+    """Seeded synthetic inputs: seed 1000+rank for tokens/router, 2027 for the weights."""
+    g = torch.Generator().manual_seed(1000 + rank)
+    x = torch.randn(tokens, D, generator=g).bfloat16()
+    logits = torch.randn(tokens, E, generator=g)
+    top = torch.topk(torch.softmax(logits, -1), K)
+    scores = (top.values / top.values.sum(-1, keepdim=True)).float()
+    ids = top.indices.to(torch.int64)
+    e_local = E // world
+    gw = torch.Generator().manual_seed(2027)
+    w13_all = (torch.randn(E, 2, F, D, generator=gw) * 0.02).bfloat16()
+    w2_all = (torch.randn(E, D, F, generator=gw) * 0.02).bfloat16()
+    sl = slice(rank * e_local, (rank + 1) * e_local)
+    return x, ids, scores, w13_all[sl].contiguous(), w2_all[sl].contiguous()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(steps: int, warmup: int, threads: int | None = None):
+    """Forward + backward of a token sample through the eager CPU restatement (all 64 experts)."""
+    from oracle import moe as oracle_moe
+
+    cores = threads or os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, ids, scores, w13, w2 = make_inputs(0, 1, "cpu", tokens=CPU_SAMPLE_TOKENS)
+    w13 = w13.requires_grad_(True)
+    w2 = w2.requires_grad_(True)
+    times = []
+    for i in range(warmup + steps):
+        xs = x.clone().requires_grad_(True)
+        ss = scores.clone().requires_grad_(True)
+        t0 = time.perf_counter()
+        out = oracle_moe.moe_forward(xs, ids, ss, w13, w2)
+        out.float().sum().backward()
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    per_step = sum(times) / len(times)
+    return {"value": CPU_SAMPLE_TOKENS / per_step, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{CPU_SAMPLE_TOKENS} of {T} tokens, all {E} experts, fwd+bwd, eager torch bf16 on CPU",
+            "ms_per_step": per_step * 1e3}
+
+
+def base_line(args, world):
+    return {
+        "metric": "MoE layer tokens/s (BF16 training layer, fwd+bwd), whole job",
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (seeded N(0,1) tokens, N(0,0.02) weights, softmax top-6 routing)",
+        "config": {
+            "workload": f"BF16 training layer EP={world}: T={T} tokens/rank, D={D}, F={F}, E={E} (E_local={E // world}), "
+                        f"K={K}, plain SwiGLU, fwd+bwd, in-place wgrad accumulation",
+            "l2": "no flush: per-step working set (expert weights + routed activations, > 1 GB at N=1) exceeds the 126 MB L2",
+        },
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 5))
+    cb = cpu_baseline(steps, max(1, min(args.warmup, 2)))
+    line = base_line(args, world)
+    line.update({
+        "impl": "reference",
+        "value": cb["value"],
+        "ms_per_step": cb["ms_per_step"],
+        "dtype": "bf16",
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "CPU restatement of the reference's math on the host cores; the reference has no CPU path and its "
+                "CuTe-DSL/Triton kernels need torch>=2.14, triton>=3.8, cutlass-dsl>=4.6 (this image: 2.11/3.6/4.5)",
+    })
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import dist_moe_b200 as dm
+    from dist_moe_b200 import _bf16, _native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+
+    x_h, ids_h, scores_h, w13_h, w2_h = make_inputs(rank, world, dev)
+    x_pin, ids_pin, scores_pin = x_h.pin_memory(), ids_h.pin_memory(), scores_h.pin_memory()
+    w13 = w13_h.to(dev).requires_grad_(True)
+    w2 = w2_h.to(dev).requires_grad_(True)
+    w13.grad = torch.zeros_like(w13)
+    w2.grad = torch.zeros_like(w2)
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, activation_slot_capacity_factor=1.0,
+                    device_scratch_capacity_factor=min(1.25, float(world)))
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    opts = dm.ExecutionOptions(inplace_wgrad_accum=True)
+    x = x_h.to(dev)
+    ids = ids_h.to(dev)
+    scores = scores_h.to(dev)
+    out_host = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
+
+    def step(xd, idd, sd):
+        xs = xd.requires_grad_(True)
+        ss = sd.requires_grad_(True)
+        out = dm.routed_experts(xs, idd, ss, w13, w2, ctx, options=opts)
+        out.float().sum().backward()
+        return out
+
+    def step_e2e():
+        xd = x_pin.to(dev, non_blocking=True)
+        idd = ids_pin.to(dev, non_blocking=True)
+        sd = scores_pin.to(dev, non_blocking=True)
+        out = step(xd, idd, sd)
+        out_host.copy_(out.detach(), non_blocking=True)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        sync_all()
+        ms = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(3, args.warmup)):
+        step(x.detach().clone(), ids, scores.detach().clone())
+    ctx.check_status()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    _bf16.PROFILE = []
+    launches0 = _native.LAUNCHES[0]
+    total_ms = timed(lambda: step(x.detach(), ids, scores.detach()), args.steps)
+    launches = _native.LAUNCHES[0] - launches0
+    events, _bf16.PROFILE = _bf16.PROFILE, None
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.check_status()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    ctx.check_status()
+
+    # ---- roofline of the dominant kernel (the grouped tcgen05 GEMM, all launches of the timed region)
+    torch.cuda.synchronize()
+    gemm_ms = sum(s.elapsed_time(e) for name, s, e in events if name.startswith("gemm"))
+    n_gemm = sum(1 for name, _, _ in events if name.startswith("gemm"))
+    rows = int(ctx._state.last_recv_rows()) if hasattr(ctx._state, "last_recv_rows") else T * K
+    flops_step = 18.0 * rows * D * F
+    pk, pk_kind = peaks()
+    peak_tf = pk.get("bf16_tflops_sustained") or pk["bf16_tflops"]
+    achieved = flops_step * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    roofline = {
+        "kernel": "grouped_gemm_kernel<fprop|dgrad|wgrad> (tcgen05, 7 launches per step)",
+        "bound": "tensor",
+        "achieved": achieved,
+        "peak": peak_tf,
+        "peak_source": f"{pk_kind} bf16_tflops_sustained",
+        "unit": "TFLOP/s",
+        "frac": achieved / peak_tf if achieved else None,
+        "flops_per_launch": flops_step / 7.0,
+        "avg_launch_ms": gemm_ms / n_gemm if n_gemm else None,
+        "launches": n_gemm,
+        "traffic": None,
+    }
+
+    if rank == 0:
+        line = base_line(args, world)
+        ms_step = total_ms / args.steps
+        line.update({
+            "value": world * T / (ms_step * 1e-3),
+            "ms_per_step": ms_step,
+            "e2e": {"value": world * T / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": x_pin.numel() * 2 + ids_pin.numel() * 8 + scores_pin.numel() * 4,
+                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": roofline,
+            "routed_rows_rank0": rows,
+        })
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_baseline(2, 1)
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

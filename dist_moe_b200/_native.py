@@ -85,9 +85,15 @@ for _name, (_res, _args) in _SIGNATURES.items():
     _fn.argtypes = _args
 
 
+# Kernel launches issued through this binding (benchmarks report the count).
+LAUNCHES = [0]
+_LAUNCHES_PER_CALL = {"dm_route": 3}
+
+
 def check(rc: int, what: str) -> None:
     """Raise on a non-zero return code of an entry point."""
     if rc == 0:
+        LAUNCHES[0] += _LAUNCHES_PER_CALL.get(what, 1)
         return
     if rc < 0:
         raise NativeError(f"{what}: {RC_NAMES.get(rc, rc)}")

@@ -1,0 +1,154 @@
+"""Device-resident state of a context: symmetric buffers, arena, planner state.
+
+Layout in HBM (per rank):
+* routing buffer   int16[64 + Tmax*K]   128-byte header (int32 T) + published expert ids
+* dispatch buffer  bf16[Tmax, K, D]     forward: first T*D elements hold x; backward: per-route input grads
+* combine buffer   bf16[Tmax, K, D]     forward: per-route expert outputs; backward: per-route output grads
+  (dist_moe/_buffers.py:574-629 allocates the same three symmetric buffers)
+* arena            uint8[total_device_buffer_bytes + guard]  activation slots then shared scratch
+* planner state    int64 vectors updated in place by the planner kernels
+  (dist_moe/_activation_buffer.py:242-307)
+Peers are reached through raw addresses obtained from torch's symmetric-memory
+rendezvous; all traffic is issued by this library's own kernels.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any
+
+import torch
+
+from . import _native as nat
+from .formats import BlockScaledFormat, format_constants
+
+ROUTING_HEADER_BYTES = 128
+GUARD_ROWS = 256
+BARRIER_TIMEOUT_NS = 5_000_000_000
+
+
+class SymmetricBuffer:
+    """One buffer that every rank of the group can address."""
+
+    def __init__(self, nbytes: int, device: torch.device, group: Any, ep_size: int, rank: int):
+        self.nbytes = nbytes
+        self.ep_size = ep_size
+        self.rank = rank
+        n = (nbytes + 15) // 16 * 16
+        if ep_size == 1:
+            self.tensor = torch.zeros(n, dtype=torch.uint8, device=device)
+            self.pad = torch.zeros(512, dtype=torch.uint8, device=device)
+            ptrs, pads = [self.tensor.data_ptr()], [self.pad.data_ptr()]
+            self._handle = None
+        else:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.tensor = symm_mem.empty(n, dtype=torch.uint8, device=device)
+            self.tensor.zero_()
+            self._handle = symm_mem.rendezvous(self.tensor, group)
+            ptrs, pads = list(self._handle.buffer_ptrs), list(self._handle.signal_pad_ptrs)
+            if self._handle.signal_pad_size < 4 * ep_size:
+                raise RuntimeError("symmetric-memory signal pad is too small for the expert-parallel barrier")
+        self.peer_ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.peer_pads = torch.tensor(pads, dtype=torch.int64, device=device)
+        self.peer_ptrs_host = ptrs
+
+    def local(self) -> torch.Tensor:
+        return self.tensor
+
+
+class ContextState:
+    def __init__(self, *, group: Any, ep_size: int, config, plan, device: torch.device):
+        import torch.distributed as dist
+
+        self.group = group
+        self.ep = ep_size
+        self.rank = dist.get_rank(group) if (group is not None and ep_size > 1) else 0
+        self.config = config
+        self.plan = plan
+        self.device = device
+        self.e_local = config.num_experts // ep_size
+        T, K, D, F = config.max_num_local_input_tokens, config.top_k, config.hidden_dim, config.intermediate_dim
+        self.block_scaled = config.block_scaled is not None
+        self.m_multiple = 128 if self.block_scaled else 0
+        self.capacity_rows = plan.total_scratch_capacity_rows
+        with torch.cuda.device(device):
+            self.routing = SymmetricBuffer(ROUTING_HEADER_BYTES + T * K * 2, device, group, ep_size, self.rank)
+            self.dispatch = SymmetricBuffer(T * K * D * 2, device, group, ep_size, self.rank)
+            self.combine = SymmetricBuffer(T * K * D * 2, device, group, ep_size, self.rank)
+            guard = GUARD_ROWS * max(D, 2 * F) * 2
+            self.arena_bytes = plan.total_device_buffer_bytes
+            self.arena = torch.zeros(self.arena_bytes + guard, dtype=torch.uint8, device=device)
+            n = plan.num_activation_slots
+            self.num_slots = n
+            self.slot_bytes = plan.activation_slot_bytes
+            self.buffer_offsets = torch.zeros(n + 1, dtype=torch.int64, device=device)
+            self.saved_bytes = torch.zeros(max(1, n * ep_size), dtype=torch.int64, device=device)
+            self.peak_min_free = torch.zeros(n + 1, dtype=torch.int64, device=device)
+            self.moe_layer_id = torch.zeros(max(1, n), dtype=torch.int64, device=device)
+            self.slot_selector = torch.zeros(1, dtype=torch.int64, device=device)
+            self.status = torch.zeros(8, dtype=torch.int32, device=device)
+            self.num_layers_in_slot = config.max_moe_layers_per_activation_slot
+            words = nat.lib.dm_route_workspace_words(T, ep_size, config.num_experts)
+            self.route_workspace = torch.zeros(max(1, words), dtype=torch.int32, device=device)
+            self.route_workspace_words = words
+            self.reset()
+        if config.block_scaled is not None:
+            ob, vpe, sb, vec, gs = format_constants(config.block_scaled.format)
+            self.format = config.block_scaled.format
+        else:
+            self.format = None
+        self.num_sms = config.num_sms or 0
+
+    # ---- planner state -------------------------------------------------------
+    def reset(self) -> None:
+        n = self.num_slots
+        offs = [i * self.slot_bytes for i in range(n)] + [self.arena_bytes]
+        self.buffer_offsets.copy_(torch.tensor(offs, dtype=torch.int64))
+        self.saved_bytes.zero_()
+        peak = [self.slot_bytes] * n + [self.arena_bytes - n * self.slot_bytes]
+        self.peak_min_free.copy_(torch.tensor(peak, dtype=torch.int64))
+        self.moe_layer_id.zero_()
+
+    def select_slot(self, slot: int, num_layers: int) -> None:
+        if self.num_slots == 0:
+            return
+        if not 0 <= slot < self.num_slots:
+            raise ValueError(f"activation_slot must be in [0, {self.num_slots})")
+        if not 1 <= num_layers <= self.config.max_moe_layers_per_activation_slot:
+            raise ValueError(
+                "num_moe_layers_in_slot must be in [1, max_moe_layers_per_activation_slot="
+                f"{self.config.max_moe_layers_per_activation_slot}]")
+        self.slot_selector.fill_(slot)
+        self.num_layers_in_slot = num_layers
+
+    def last_recv_rows(self) -> int:
+        """Rows this rank received in the most recent call (reads the device; not for hot paths)."""
+        call = getattr(self, "last_call", None)
+        return int(call.recv_rows.item()) if call is not None else 0
+
+    # ---- status --------------------------------------------------------------
+    def check_status(self) -> None:
+        torch.cuda.synchronize(self.device)
+        words = self.status.tolist()
+        if words[0] != 0:
+            self.status.zero_()
+            raise RuntimeError(
+                f"dist_moe_b200 device contract violation: {nat.STATUS_NAMES.get(words[0], words[0])} "
+                f"(details {words[1:4]})")
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self.arena = torch.empty(0, dtype=torch.uint8, device=self.device)
+
+    # ---- barrier -------------------------------------------------------------
+    def barrier(self, buf: SymmetricBuffer, cond: torch.Tensor | None = None) -> None:
+        if self.ep == 1:
+            return
+        nat.check(nat.lib.dm_barrier(buf.peer_pads.data_ptr(), self.rank, self.ep, 0, nat.ptr(cond),
+                                     BARRIER_TIMEOUT_NS, self.status.data_ptr(), nat.stream_ptr()), "dm_barrier")
+
+    def arena_operand(self, offset_tensor: torch.Tensor | None) -> nat.Operand:
+        return nat.Operand(self.arena.data_ptr(), self.arena.numel(),
+                           None if offset_tensor is None else offset_tensor.data_ptr())

@@ -1,0 +1,84 @@
+"""``plan_memory`` and ``Config`` validation against the reference (CPU).
+
+``tests/golden/plan_memory.json`` holds the reference's own ``plan_memory`` outputs for
+BF16, MXFP8 and NVFP4 configurations (written by ``tests/golden/gen_golden.py``); the
+literal numbers below are the ones the reference's tests and README pin
+(tests/test_dist_moe_vmm.py:146-167, README.md:435-446)."""
+
+import dataclasses
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+import dist_moe_b200 as dm
+
+GOLDEN = json.loads((Path(__file__).resolve().parent / "golden" / "plan_memory.json").read_text())
+
+
+def _config(spec):
+    kw = dict(spec)
+    bs = kw.pop("block_scaled", None)
+    if bs is not None:
+        kw["block_scaled"] = dm.BlockScaledConfig(format=getattr(dm.BlockScaledFormat, bs[0]), pipeline=bs[1])
+    return dm.Config(**kw)
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN))
+def test_plan_memory_matches_reference_byte_for_byte(name):
+    case = GOLDEN[name]
+    plan = dm.plan_memory(_config(case["config"]), case["ep_size"])
+    got = dataclasses.asdict(plan)
+    assert got == case["plan"], {k: (got[k], case["plan"][k]) for k in got if got[k] != case["plan"][k]}
+    assert plan.explain() == case["explain"]
+
+
+def test_capacity_padding_example():
+    """32 routed rows over 2 local experts pad to 256 rows of 128 (docs/mxfp8_execution.md:61-80)."""
+    cfg = dm.Config(max_num_local_input_tokens=16, hidden_dim=256, intermediate_dim=256, top_k=2, num_experts=4,
+                    max_moe_layers_per_activation_slot=1, block_scaled=dm.BlockScaledConfig())
+    plan = dm.plan_memory(cfg, 2)
+    assert plan.balanced_recv_rows == 32 and plan.device_scratch_capacity_rows == 256
+
+
+def test_config_validation_errors():
+    base = dict(max_num_local_input_tokens=16, hidden_dim=256, intermediate_dim=256, top_k=2, num_experts=8,
+                max_moe_layers_per_activation_slot=1)
+    dm.Config(**base)
+    for bad, exc in [
+        (dict(hidden_dim=100), ValueError),
+        (dict(top_k=9), ValueError),
+        (dict(num_experts=0), ValueError),
+        (dict(max_moe_layers_per_activation_slot=0), ValueError),
+        (dict(activation_slot_bytes=1.5), TypeError),
+        (dict(activation_slot_bytes=10, activation_slot_capacity_factor=1.0), ValueError),
+        (dict(num_activation_slots=0), ValueError),
+        (dict(device_scratch_capacity_factor=0.0), ValueError),
+        (dict(wgrad_dtype=torch.float16), TypeError),
+        (dict(activation="gelu"), ValueError),
+        (dict(bf16_grouped_gemm_preset="nope"), ValueError),
+        (dict(inference=True, activation_slot_capacity_factor=1.0), ValueError),
+        (dict(block_scaled=dm.BlockScaledConfig(format=dm.BlockScaledFormat.NVFP4)), ValueError),  # NVFP4 => inference
+    ]:
+        with pytest.raises(exc):
+            dm.Config(**{**base, **bad})
+    with pytest.raises(ValueError):
+        dm.BlockScaledConfig(format=dm.BlockScaledFormat.NVFP4, fast_math=True)
+    with pytest.raises(ValueError):
+        dm.plan_memory(dm.Config(**base), 0)
+    with pytest.raises(ValueError):
+        dm.plan_memory(dm.Config(**base, activation_slot_bytes=8), 2)
+    with pytest.raises(TypeError):
+        dm.Context()
+    with pytest.raises(TypeError):
+        dm.PreparedWeight()
+
+
+def test_public_names_match_the_reference_surface():
+    assert sorted(dm.__all__) == sorted([
+        "Bf16GroupedGemmPreset", "BlockScaledConfig", "BlockScaledFormat", "BlockScaledKernelConfig", "Config",
+        "Context", "ExecutionOptions", "MemoryPlan", "PreparedWeight", "RMSNormPostprocess", "VmmConfig",
+        "create_context", "plan_memory", "prepare_block_scaled_weight", "routed_experts",
+        "supports_fused_post_expert_rmsnorm",
+    ])

@@ -172,6 +172,8 @@ def _wgrad_destination(param: torch.Tensor, shape, options: ExecutionOptions, cf
         target = owner if owner is not None else param
         if target.grad is None:
             dtype = cfg.wgrad_dtype or getattr(target, "grad_dtype", None) or target.dtype
+            if dtype != target.dtype and hasattr(target, "grad_dtype"):
+                target.grad_dtype = dtype
             target.grad = torch.zeros_like(target, dtype=dtype)
         grad = target.grad
         if not grad.is_contiguous() or grad.dtype not in (torch.bfloat16, torch.float32):

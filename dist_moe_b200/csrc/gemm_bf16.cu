@@ -38,7 +38,8 @@ constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 1024;  // + slack for 1024-byte alignment
+constexpr uint32_t kStagingBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
+constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 4 * kStagingBytes + 1024;  // + slack for 1024-byte alignment
 
 enum GemmMode : int { kFprop = 0, kDgrad = 1, kWgrad = 2 };
 
@@ -64,6 +65,32 @@ struct GemmParams {
   int accumulate;
   ActParams act;
 };
+
+// Staging tile of one epilogue warp: row r is 128 bytes, its 16-byte chunk j sits at j ^ (r & 7).
+__device__ __forceinline__ void stage_put(uint8_t* stg, int row, int chunk, uint4 v) {
+  reinterpret_cast<uint4*>(stg + row * 128)[chunk ^ (row & 7)] = v;
+}
+__device__ __forceinline__ uint4 stage_get(const uint8_t* stg, int row, int chunk) {
+  return reinterpret_cast<const uint4*>(stg + row * 128)[chunk ^ (row & 7)];
+}
+__device__ __forceinline__ uint4 pack8_bf16(const uint32_t* r) {
+  return make_uint4(pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                    pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                    pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                    pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+}
+
+// 16-byte fire-and-forget reductions performed by L2 (each output tile has one owner CTA).
+__device__ __forceinline__ void red_add_f32x4(uint64_t addr, uint4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void red_add_bf16x8(uint64_t addr, uint4 v) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
 
 struct Tile {
   int e, m_blk, n_blk, row0, row_end, k_iters;
@@ -290,8 +317,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     }
   } else {
     // ======================= epilogue =======================
+    // Each warp owns 32 accumulator rows.  A lane reads its own row from TMEM, the warp
+    // transposes 128-byte row segments through a private 4 KiB staging tile (16-byte chunks
+    // XOR-swizzled by row so that both directions are bank-conflict free) and then stores
+    // whole 128-byte segments: 8 lanes per row, 4 rows per instruction.
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32)
     const int row_in_tile = quad * 32 + lane;
+    uint8_t* stg = smem + kStages * kStageBytes + (warp - 2) * kStagingBytes;
     int e = 0;
     int it = 0;
     bool ok = true;
@@ -308,117 +340,156 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;
 
       if (kMode == kWgrad) {
-        const int out_row = t.m_blk * kBM + row_in_tile;       // row of dW[e]
-        const bool row_ok = out_row < p.N;
+        const int out_row = t.m_blk * kBM + row_in_tile;  // row of dW[e]
         const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kd;
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
-          uint32_t r[32];
-          if (t.k_iters > 0) {
-            tmem_ld_32x32(taddr + c0, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0u;
-          }
-          const int col = t.n_blk * kBN + c0;
-          if (row_ok && col < p.Kd) {
-            if (p.out_fp32) {
-              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c_base) + row_elems + col);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (col + 4 * j + 4 <= p.Kd) {
-                  float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                  if (p.accumulate) {
-                    const float4 o = dst[j];
-                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                  }
-                  dst[j] = v;
-                }
-              }
+        const uint64_t my_row =
+            out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
+        if (p.out_fp32) {
+          for (int c0 = 0; c0 < kBN; c0 += 32) {
+            uint32_t r[32];
+            if (t.k_iters > 0) {
+              tmem_ld_32x32(taddr + c0, r);
+              tmem_ld_wait();
             } else {
-              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c_base) + row_elems + col);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (col + 8 * j + 8 <= p.Kd) {
-                  float f[8];
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
 #pragma unroll
-                  for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[8 * j + q]);
-                  if (p.accumulate) {
-                    const uint4 o = dst[j];
-                    const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+            for (int j = 0; j < 8; ++j)
+              stage_put(stg, lane, j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+            __syncwarp();
+            const int col = t.n_blk * kBN + c0;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                      f[2 * q] += __uint_as_float(w[q] << 16);
-                      f[2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u);
-                    }
-                  }
-                  dst[j] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
-                                      pack_bf16x2(f[6], f[7]));
-                }
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), j = lane & 7;
+              uint4 v = stage_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+              if (rp != 0 && col + 4 * j + 4 <= p.Kd) {
+                const uint64_t dst = rp + static_cast<uint64_t>(col + 4 * j) * 4;
+                if (p.accumulate)
+                  red_add_f32x4(dst, v);
+                else
+                  *reinterpret_cast<uint4*>(dst) = v;
               }
             }
+            __syncwarp();
+          }
+        } else {
+          for (int c0 = 0; c0 < kBN; c0 += 64) {
+            uint32_t r0[32], r1[32];
+            if (t.k_iters > 0) {
+              tmem_ld_32x32(taddr + c0, r0);
+              tmem_ld_32x32(taddr + c0 + 32, r1);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+            }
+            const int col = t.n_blk * kBN + c0;
+            // Accumulation rounds the fp32 accumulator to bf16 and lets L2 add it to the stored
+            // gradient (a 16-byte reduction per lane): no read round trip through the SM.
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              stage_put(stg, lane, j, pack8_bf16(r0 + 8 * j));
+              stage_put(stg, lane, j + 4, pack8_bf16(r1 + 8 * j));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), j = lane & 7;
+              const uint4 v = stage_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+              if (rp != 0 && col + 8 * j + 8 <= p.Kd) {
+                const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
+                if (p.accumulate)
+                  red_add_bf16x8(dst, v);
+                else
+                  *reinterpret_cast<uint4*>(dst) = v;
+              }
+            }
+            __syncwarp();
           }
         }
       } else {
         const int row = t.row0 + row_in_tile;
         const bool row_ok = row < t.row_end;
-        uint8_t* out_row = nullptr;
+        uint64_t my_row = 0;
         if (row_ok) {
           if (p.scatter_ptrs != nullptr)
-            out_row = reinterpret_cast<uint8_t*>(p.scatter_ptrs[row]);
+            my_row = static_cast<uint64_t>(p.scatter_ptrs[row]);
           else
-            out_row = p.c_base + c_off + static_cast<int64_t>(row) * p.N * 2;
+            my_row = reinterpret_cast<uint64_t>(p.c_base) + c_off + static_cast<uint64_t>(row) * p.N * 2;
         }
         if (kMode == kFprop && p.fused) {
           const int F = p.N / 2;
-          uint8_t* h2_row = row_ok ? p.h2_base + h2_off + static_cast<int64_t>(row) * F * 2 : nullptr;
-          for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
-            uint32_t g[32], u[32];
-            tmem_ld_32x32(taddr + c0, g);
-            tmem_ld_32x32(taddr + kBN / 2 + c0, u);
-            tmem_ld_wait();
-            const int col = t.n_blk * (kBN / 2) + c0;  // column inside the gate (and up) half
-            if (out_row != nullptr) {
+          const uint64_t my_h2 =
+              row_ok ? reinterpret_cast<uint64_t>(p.h2_base) + h2_off + static_cast<uint64_t>(row) * F * 2 : 0ull;
+          for (int c0 = 0; c0 < kBN / 2; c0 += 64) {
+            uint4 gp[8], up[8], zp[8];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t g[32], u[32];
+              tmem_ld_32x32(taddr + c0 + half * 32, g);
+              tmem_ld_32x32(taddr + kBN / 2 + c0 + half * 32, u);
+              tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                uint32_t gp[4], up[4], zp[4];
+                uint32_t gw[4], uw[4], zw[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  gp[q] = pack_bf16x2(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(g[8 * j + 2 * q + 1]));
-                  up[q] = pack_bf16x2(__uint_as_float(u[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q + 1]));
-                  const float z0 = swiglu_f32(__uint_as_float(gp[q] << 16), __uint_as_float(up[q] << 16), p.act);
+                  gw[q] = pack_bf16x2(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(g[8 * j + 2 * q + 1]));
+                  uw[q] = pack_bf16x2(__uint_as_float(u[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q + 1]));
+                  const float z0 = swiglu_f32(__uint_as_float(gw[q] << 16), __uint_as_float(uw[q] << 16), p.act);
                   const float z1 =
-                      swiglu_f32(__uint_as_float(gp[q] & 0xffff0000u), __uint_as_float(up[q] & 0xffff0000u), p.act);
-                  zp[q] = pack_bf16x2(z0, z1);
+                      swiglu_f32(__uint_as_float(gw[q] & 0xffff0000u), __uint_as_float(uw[q] & 0xffff0000u), p.act);
+                  zw[q] = pack_bf16x2(z0, z1);
                 }
-                if (col + 8 * j + 8 <= F) {
-                  *reinterpret_cast<uint4*>(out_row + (col + 8 * j) * 2) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
-                  *reinterpret_cast<uint4*>(out_row + (F + col + 8 * j) * 2) = make_uint4(up[0], up[1], up[2], up[3]);
-                  *reinterpret_cast<uint4*>(h2_row + (col + 8 * j) * 2) = make_uint4(zp[0], zp[1], zp[2], zp[3]);
-                }
+                gp[half * 4 + j] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+                up[half * 4 + j] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+                zp[half * 4 + j] = make_uint4(zw[0], zw[1], zw[2], zw[3]);
               }
+            }
+            const int col = t.n_blk * (kBN / 2) + c0;  // column inside the gate (and up) half
+#pragma unroll
+            for (int which = 0; which < 3; ++which) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) stage_put(stg, lane, j, which == 0 ? gp[j] : (which == 1 ? up[j] : zp[j]));
+              __syncwarp();
+              const uint64_t base = which == 2 ? my_h2 : my_row;
+              const int col_out = which == 1 ? F + col : col;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + (lane >> 3), j = lane & 7;
+                const uint4 v = stage_get(stg, rr, j);
+                const uint64_t rp = __shfl_sync(0xffffffffu, base, rr);
+                if (rp != 0 && col + 8 * j + 8 <= F)
+                  *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col_out + 8 * j) * 2) = v;
+              }
+              __syncwarp();
             }
           }
         } else {
-          for (int c0 = 0; c0 < kBN; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + c0, r);
+          for (int c0 = 0; c0 < kBN; c0 += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + c0, r0);
+            tmem_ld_32x32(taddr + c0 + 32, r1);
             tmem_ld_wait();
-            const int col = t.n_blk * kBN + c0;
-            if (out_row != nullptr && col < p.N) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (col + 8 * j + 8 <= p.N) {
-                  uint4 v;
-                  v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-                  v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-                  v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-                  v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-                  *reinterpret_cast<uint4*>(out_row + (col + 8 * j) * 2) = v;
-                }
-              }
+            for (int j = 0; j < 4; ++j) {
+              stage_put(stg, lane, j, pack8_bf16(r0 + 8 * j));
+              stage_put(stg, lane, j + 4, pack8_bf16(r1 + 8 * j));
             }
+            __syncwarp();
+            const int col = t.n_blk * kBN + c0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), j = lane & 7;
+              const uint4 v = stage_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+              if (rp != 0 && col + 8 * j + 8 <= p.N)
+                *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
+            }
+            __syncwarp();
           }
         }
       }

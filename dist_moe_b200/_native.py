@@ -58,6 +58,12 @@ _SIGNATURES = {
         + [_P] * 7
         + [c_int64, _P, _P],
     ),
+    "dm_route_static": (
+        c_int,
+        [_P, _P, _P, c_int, c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int64, c_int64]
+        + [_P] * 6
+        + [_P, _P],
+    ),
     "dm_plan_fwd_bf16": (
         c_int,
         [_P] * 10 + [c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, _P, _P],
@@ -87,7 +93,7 @@ for _name, (_res, _args) in _SIGNATURES.items():
 
 # Kernel launches issued through this binding (benchmarks report the count).
 LAUNCHES = [0]
-_LAUNCHES_PER_CALL = {"dm_route": 3}
+_LAUNCHES_PER_CALL = {"dm_route": 3, "dm_route_static": 3}
 
 
 def check(rc: int, what: str) -> None:

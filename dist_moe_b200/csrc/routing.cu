@@ -324,7 +324,7 @@ extern "C" int64_t dm_route_workspace_words(int64_t T, int ep, int E) {
   return 2 * ep * chunks * e_local + E;
 }
 
-extern "C" int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
+static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
                         int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
                         int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,
                         int64_t capacity_rows, int64_t ptrs_size, int32_t* counts, int32_t* per_rank,
@@ -377,6 +377,58 @@ extern "C" int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
   route_scan_kernel<<<1, 1024, sizeof(int32_t) * (2 * p.e_local + 1), st>>>(p);
   route_fill_kernel<<<grid, kChunkTokens, smem_fill, st>>>(p);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
+                        int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
+                        int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,
+                        int64_t capacity_rows, int64_t ptrs_size, int32_t* counts, int32_t* per_rank,
+                        int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
+                        int64_t* scatter_ptrs, int32_t* workspace, int64_t workspace_words, int* status,
+                        void* stream) {
+  return route_launch(routing_ptrs, dispatch_ptrs, combine_ptrs, rank, ep, T, K, E, gather_stride_bytes,
+                      bwd_gather_stride_bytes, scatter_stride_bytes, m_multiple_of, capacity_rows, ptrs_size, counts,
+                      per_rank, expert_offsets, fwd_gather_ptrs, bwd_gather_ptrs, scatter_ptrs, workspace,
+                      workspace_words, status, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Routing for callers that cannot allocate: the chunk counters, chunk offsets and the
+// expert histogram live in a fixed array that is part of the library image.
+// ---------------------------------------------------------------------------
+namespace dm {
+constexpr int64_t kStaticRouteWords = DM_ROUTE_STATIC_MAX_WORDS;
+static __device__ __align__(256) int32_t g_route_scratch[kStaticRouteWords];
+constexpr int kMaxDevices = 64;
+static int32_t* g_route_scratch_addr[kMaxDevices];  // device address of the array, per device
+}  // namespace dm
+
+extern "C" int dm_route_static(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs,
+                               const uint64_t* combine_ptrs, int rank, int ep, int64_t T, int K, int E,
+                               int64_t gather_stride_bytes, int64_t bwd_gather_stride_bytes,
+                               int64_t scatter_stride_bytes, int m_multiple_of, int64_t capacity_rows,
+                               int64_t ptrs_size, int32_t* counts, int32_t* per_rank, int32_t* expert_offsets,
+                               int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs, int64_t* scatter_ptrs, int* status,
+                               void* stream) {
+  const int64_t need = dm_route_workspace_words(T, ep, E);
+  if (need <= 0) return kRcBadArg;
+  if (need > kStaticRouteWords) return kRcTooLarge;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (dev < 0 || dev >= kMaxDevices) return kRcTooLarge;
+  if (g_route_scratch_addr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the kernels need its address on the current device.
+    void* addr = nullptr;
+    err = cudaGetSymbolAddress(&addr, g_route_scratch);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (addr == nullptr) return kRcBadArg;
+    g_route_scratch_addr[dev] = static_cast<int32_t*>(addr);
+  }
+  return route_launch(routing_ptrs, dispatch_ptrs, combine_ptrs, rank, ep, T, K, E, gather_stride_bytes,
+                      bwd_gather_stride_bytes, scatter_stride_bytes, m_multiple_of, capacity_rows, ptrs_size, counts,
+                      per_rank, expert_offsets, fwd_gather_ptrs, bwd_gather_ptrs, scatter_ptrs,
+                      g_route_scratch_addr[dev], kStaticRouteWords, status, stream);
 }
 
 extern "C" int dm_gather_rows(const int64_t* ptrs, const int32_t* num_rows, void* dst_base, const int64_t* dst_offset,

@@ -92,6 +92,37 @@ int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const 
              void* stream);
 
 /* ---------------------------------------------------------------------------
+ * dm_route_static: the same routing metadata without a caller-provided workspace.
+ * (No counterpart in the reference: its launcher allocates seven temporaries per call.)
+ *
+ * Some hosts may not allocate device memory at the point where they route: code that
+ * runs inside a memory-pool-free region of a serving loop, a plugin whose allocator
+ * belongs to the embedding framework, or a process that has already handed all free
+ * HBM to a KV cache.  For them the intermediate counters live in one fixed array inside
+ * the library image, DM_ROUTE_STATIC_MAX_WORDS int32 words (256 KiB); every GPU that
+ * loads the library carries that array until the process exits.
+ *
+ * Limits and rules:
+ *   - the shape must satisfy dm_route_workspace_words(T, ep, E) <= DM_ROUTE_STATIC_MAX_WORDS,
+ *     otherwise the call returns DM_RC_TOO_LARGE and launches nothing;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture;
+ *   - the call itself performs no cudaMalloc/cudaFree and calls no allocating routine;
+ *     inputs and outputs are still the caller's;
+ *   - all calls on a device share the array.  Each call clears the part that must start
+ *     at zero and overwrites the rest, so back-to-back calls on one stream are fine, but
+ *     two calls whose kernels overlap on the GPU (different streams) race on it.
+ * Outputs are identical to dm_route's.
+ * ------------------------------------------------------------------------- */
+#define DM_ROUTE_STATIC_MAX_WORDS 65536
+int dm_route_static(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
+                    int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
+                    int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,
+                    int64_t capacity_rows, int64_t ptrs_size, int32_t* counts, int32_t* per_rank,
+                    int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
+                    int64_t* scatter_ptrs, int* status, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Activation-arena planner, BF16
  * (dist_moe/_activation_buffer.py:2318-2591 `get_forward_plan`/`get_backward_plan`;
  * kernels dist_moe/_activation_buffer_planner_kernel.py:1068-1477).

@@ -1,0 +1,91 @@
+"""Worker for the multi-rank parity tests: one process per GPU (NCCL) runs ``routed_experts``
+forward + backward on its tokens and local experts; every rank checks its outputs and
+gradients against the single-process CPU oracle over all ranks' tokens and all experts.
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/multi_rank_worker.py
+"""
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+from oracle import moe as oracle_moe  # noqa: E402
+from tests.helpers import BF16_FWD, BF16_GRAD, BF16_WGRAD, assert_close  # noqa: E402
+
+
+def inputs(world, T, D, F, K, E, quickstart):
+    g = torch.Generator().manual_seed(17)
+    xs = [torch.randn(T, D, generator=g).bfloat16() for _ in range(world)]
+    w13 = (torch.randn(E, 2, F, D, generator=g) * D**-0.5).bfloat16()
+    w2 = (torch.randn(E, D, F, generator=g) * F**-0.5).bfloat16()
+    ids, scores = [], []
+    for r in range(world):
+        if quickstart:  # ids (global_token*K + k) % E, scores 1/K (the reference's example inputs)
+            tok = r * T + torch.arange(T)
+            ids.append((tok[:, None] * K + torch.arange(K)[None, :]) % E)
+            scores.append(torch.full((T, K), 1.0 / K))
+        else:
+            top = torch.topk(torch.softmax(torch.randn(T, E, generator=g), -1), K)
+            ids.append(top.indices)
+            scores.append((top.values / top.values.sum(-1, keepdim=True)).float())
+    return xs, ids, scores, w13, w2
+
+
+def run_case(dm, group, rank, world, dev, T, D, F, K, E, quickstart, slot_factor):
+    xs, ids, scores, w13, w2 = inputs(world, T, D, F, K, E, quickstart)
+    el = E // world
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, activation_slot_capacity_factor=slot_factor,
+                    device_scratch_capacity_factor=float(world))
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    try:
+        # oracle: every rank's tokens through all experts; the loss is the sum over all ranks' outputs
+        xr = [x.clone().requires_grad_(True) for x in xs]
+        sr = [s.clone().requires_grad_(True) for s in scores]
+        a = w13.clone().requires_grad_(True)
+        b = w2.clone().requires_grad_(True)
+        refs = [oracle_moe.moe_forward(xr[r], ids[r], sr[r], a, b) for r in range(world)]
+        sum(o.float().sum() for o in refs).backward()
+        for attempt in range(2):
+            x = xs[rank].to(dev).requires_grad_(True)
+            s = scores[rank].to(dev).requires_grad_(True)
+            wa = w13[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
+            wb = w2[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
+            out = dm.routed_experts(x, ids[rank].to(dev), s, wa, wb, ctx)
+            out.float().sum().backward()
+            ctx.check_status()
+            tag = f"rank {rank} T{T} D{D} F{F} K{K} E{E} #{attempt}"
+            assert_close(out, refs[rank], what=f"{tag} output", **BF16_FWD)
+            assert_close(x.grad, xr[rank].grad, what=f"{tag} grad x", **BF16_GRAD)
+            assert_close(s.grad, sr[rank].grad, what=f"{tag} grad scores", **BF16_GRAD)
+            assert_close(wa.grad, a.grad[rank * el:(rank + 1) * el], what=f"{tag} grad w13", **BF16_WGRAD)
+            assert_close(wb.grad, b.grad[rank * el:(rank + 1) * el], what=f"{tag} grad w2", **BF16_WGRAD)
+    finally:
+        ctx.close()
+
+
+def main():
+    import dist_moe_b200 as dm
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD
+    run_case(dm, group, rank, world, dev, 16, 256, 256, 2, 4 * world, True, None)    # quick-start layer, recompute
+    run_case(dm, group, rank, world, dev, 128, 1024, 1024, 2, 2 * world, False, 1.0)  # reference's two-rank shape, saved
+    run_case(dm, group, rank, world, dev, 300, 512, 384, 4, 8 * world, False, 1.0)
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_RANK_OK", world, flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

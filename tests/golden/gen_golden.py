@@ -227,13 +227,86 @@ def gen_routing(ref):
         print("routing", name, "ok")
 
 
+PLANNER_SCENARIOS = {
+    # name: (EP, T, K, D, F, slots, layers, slot_factor, ops); ops: ("f", slot, R, per_rank, scratch_only) / ("b", index of f)
+    "two_layers_saved": (2, 64, 2, 256, 256, 1, 2, 1.0,
+                         [("f", 0, 120, [120, 136], False), ("f", 0, 100, [100, 156], False), ("b", 1), ("b", 0)]),
+    "recompute_when_full": (2, 64, 2, 256, 512, 1, 3, 0.4,
+                            [("f", 0, 128, [128, 128], False), ("f", 0, 200, [200, 56], False),
+                             ("f", 0, 90, [90, 166], False), ("b", 2), ("b", 1), ("b", 0)]),
+    "two_slots_and_no_grad": (4, 32, 4, 512, 128, 2, 1, None,
+                              [("f", 0, 100, [100, 140, 160, 112], False), ("f", 1, 33, [33, 200, 150, 129], False),
+                               ("f", 1, 64, [64, 64, 64, 64], True), ("b", 1), ("b", 0)]),
+    "hidden_le_inter": (1, 16, 2, 128, 1024, 1, 1, 1.0, [("f", 0, 32, [32], False), ("b", 0)]),
+}
+
+
+def gen_planner(ref):
+    import numpy as np
+    import torch
+    import triton.language as tl
+    from triton.runtime.interpreter import TensorHandle
+
+    import dist_moe
+    from dist_moe import _activation_buffer_planner_kernel as P
+
+    _shim(P, np, tl, TensorHandle)
+    out = {}
+    for name, (EP, T, K, D, F, slots, layers, factor, ops) in PLANNER_SCENARIOS.items():
+        cfg = dist_moe.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K,
+                              num_experts=4 * EP, max_moe_layers_per_activation_slot=layers,
+                              num_activation_slots=slots, activation_slot_capacity_factor=factor,
+                              device_scratch_capacity_factor=float(EP))
+        plan = dist_moe.plan_memory(cfg, EP)
+        slot_bytes, arena = plan.activation_slot_bytes, plan.total_device_buffer_bytes
+        i64 = lambda v: torch.tensor(v, dtype=torch.int64)  # noqa: E731
+        buffer_offsets = i64([i * slot_bytes for i in range(slots)] + [arena])
+        saved = torch.zeros(slots * EP, dtype=torch.int64)
+        peak = i64([slot_bytes] * slots + [arena - slots * slot_bytes])
+        layer = torch.zeros(slots, dtype=torch.int64)
+        steps, fwd_records = [], []
+        for op in ops:
+            if op[0] == "f":
+                _, slot, R, per_rank, scratch_only = op
+                need = torch.zeros(1, dtype=torch.bool)
+                fwd_state = torch.zeros(6, dtype=torch.int64)
+                sel = i64([slot])
+                P._triton_get_forward_plan[(1,)](
+                    torch.tensor([R], dtype=torch.int32), torch.tensor(per_rank, dtype=torch.int32), None, saved,
+                    buffer_offsets, peak, need, fwd_state, EP=EP, num_tokens=T, topk=K, element_size=2, hidden_dim=D,
+                    intermediate_dim=F, microbatch_id_ptr=sel, activation_slot_bytes=slot_bytes, buffer_size=arena,
+                    num_activation_slots=slots, moe_layer_id_ptr=layer, num_moe_layers=layers,
+                    scratch_only=scratch_only)
+                rec = dict(op="f", slot=slot, R=R, per_rank=per_rank, scratch_only=scratch_only, need=bool(need[0]),
+                           fwd_state=fwd_state.tolist())
+                fwd_records.append(rec)
+            else:
+                f = [r for r in fwd_records][op[1]]
+                bwd = torch.zeros(6, dtype=torch.int64)
+                fs = i64(f["fwd_state"])
+                P._triton_get_backward_plan[(1,)](
+                    torch.tensor([f["R"]], dtype=torch.int32), buffer_offsets, peak, torch.tensor([f["need"]]),
+                    fs[0:1], fs[1:2], fs[2:3], saved, torch.tensor(f["per_rank"], dtype=torch.int32), bwd, EP=EP,
+                    num_tokens=T, topk=K, element_size=2, hidden_dim=D, intermediate_dim=F,
+                    microbatch_id_ptr=fs[5:6], activation_slot_bytes=slot_bytes, buffer_size=arena,
+                    num_activation_slots=slots, moe_layer_id_ptr=layer)
+                rec = dict(op="b", of=op[1], bwd_offsets=bwd.tolist())
+            rec["state"] = dict(buffer_offsets=buffer_offsets.tolist(), saved=saved.tolist(), peak=peak.tolist(),
+                                layer=layer.tolist())
+            steps.append(rec)
+        out[name] = dict(EP=EP, T=T, K=K, D=D, F=F, slots=slots, layers=layers, slot_bytes=slot_bytes,
+                         arena_bytes=arena, steps=steps)
+    (HERE / "planner_bf16.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+    print("planner_bf16.json:", len(out), "scenarios")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
-    steps = {"plan": gen_plan_memory, "routing": gen_routing}
+    steps = {"plan": gen_plan_memory, "routing": gen_routing, "planner": gen_planner}
     for name, fn in steps.items():
         if not args.only or name in args.only.split(","):
             fn(args.reference)

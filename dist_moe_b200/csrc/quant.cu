@@ -1,0 +1,400 @@
+// Block-scaled quantisers: MXFP8 E4M3 (E8M0 scale per 32 elements) and NVFP4 (E2M1 data,
+// E4M3 scale per 16 elements, fp32 per-token or per-expert scale).  All HBM bound:
+// 16-byte loads, byte-exact hardware conversions (cvt.rp.ue8m0, cvt.rn.satfinite.e4m3x2,
+// cvt.rn.satfinite.e2m1x2 through the cuda_fp8/cuda_fp4 intrinsics), no fast-math.
+//
+// Numerics follow the reference's quantisers step by step
+// (dist_moe/kernels/blockscaled_quantization_common.py:120-257, 739-752;
+//  dist_moe/kernels/triton_quantization/blockscaled_quantize.py:296-493):
+//   MXFP8: s = amax * fl(1/448); byte = round-up-to-power-of-two(s); recip = 2^(127-byte);
+//          q = e4m3_rn_satfinite(x * recip); a non-finite block gets byte 0xFF and NaN data.
+//   NVFP4: raw = (amax * scale) * fl(1/6) clamped to [2^-9, 448]; byte = e4m3_rn(raw);
+//          mult = div_rn(scale, f32(byte)); codes = e2m1_rn_satfinite(x * mult), even element
+//          in the low nibble.
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "../../include/dist_moe_b200.h"
+
+namespace dm {
+
+__device__ __forceinline__ float amax_nonfinite(float acc, float v) {
+  const float a = fabsf(v);
+  return (a != a) ? __int_as_float(0x7f800000) : fmaxf(acc, a);
+}
+
+__device__ __forceinline__ uint8_t e8m0_round_up(float s) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_e8m0(s, __NV_NOSAT, cudaRoundPosInf));
+}
+
+__device__ __forceinline__ float e8m0_recip(uint8_t byte) {
+  return byte == 0xFF ? __int_as_float(0x7fc00000) : __int_as_float((254 - static_cast<int>(byte)) << 23);
+}
+
+// Scale byte and reciprocal of one MXFP8 block from its amax.
+__device__ __forceinline__ uint8_t mxfp8_scale(float amax, float& recip) {
+  const float s = amax * (1.0f / 448.0f);
+  const uint8_t byte = e8m0_round_up(s);
+  recip = (s < __int_as_float(0x7f800000)) ? e8m0_recip(byte) : __int_as_float(0x7fc00000);
+  return byte;
+}
+
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+__device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ int64_t blocked_offset(int64_t row, int col, int n_col_atoms) {
+  const int64_t atom = (row >> 7) * n_col_atoms + (col >> 2);
+  return atom * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (col & 3);
+}
+
+// ---------------------------------------------------------------------------
+// MXFP8 row mode: 1x32 blocks along the contiguous dimension.  8 elements per
+// thread, 4 threads per block.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) mxfp8_row_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
+                                                        int64_t max_rows, int vec_per_row, uint2* __restrict__ q,
+                                                        uint8_t* __restrict__ scales, int blocked, int n_col_atoms) {
+  int64_t rows = num_rows ? *num_rows : max_rows;
+  if (rows > max_rows) rows = max_rows;
+  const int64_t total = rows * vec_per_row;
+  const int64_t start = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // The bound is rounded up to a whole warp so that every lane takes part in the shuffles.
+  for (int64_t i = start; i < (total + 31) / 32 * 32; i += step) {
+    const bool live = i < total;
+    float f[8];
+    if (live) {
+      unpack8f(x[i], f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = amax_nonfinite(amax, f[j]);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float recip;
+    const uint8_t byte = mxfp8_scale(amax, recip);
+    if (!live) continue;
+    q[i] = make_uint2(e4m3x4(f[0] * recip, f[1] * recip, f[2] * recip, f[3] * recip),
+                      e4m3x4(f[4] * recip, f[5] * recip, f[6] * recip, f[7] * recip));
+    if ((i & 3) == 0) {
+      const int64_t r = i / vec_per_row;
+      const int blk = static_cast<int>(i - r * vec_per_row) >> 2;
+      if (blocked)
+        scales[blocked_offset(r, blk, n_col_atoms)] = byte;
+      else
+        scales[r * (vec_per_row >> 2) + blk] = byte;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// MXFP8 column mode (32x1 blocks along the rows) and 32x32 tile mode.
+// One CTA handles a 32-row x 256-column slab staged in shared memory.
+//   col mode : scale[c][r/32]           (natural: [C][ceil(R/32)], or blocked with rows = C)
+//   tile mode: one scale per 32x32 tile, written for both GEMM orientations:
+//              row_scales[n][k/32] (forward) and col_scales[k][n/32] (input gradient).
+// ---------------------------------------------------------------------------
+template <bool kTile>
+__global__ void __launch_bounds__(256) mxfp8_slab_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* num_rows,
+                                                         int64_t max_rows, int C, uint8_t* __restrict__ q,
+                                                         uint8_t* __restrict__ s0, uint8_t* __restrict__ s1,
+                                                         int blocked, int s0_col_atoms, int s1_col_atoms,
+                                                         int64_t batch_rows) {
+  __shared__ float tile[32][257];
+  __shared__ float col_amax[256];
+  int64_t rows = num_rows ? *num_rows : max_rows;
+  if (rows > max_rows) rows = max_rows;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.y) * 32;
+  const int col0 = blockIdx.x * 256;
+  if (row0 >= rows) return;
+  const int t = threadIdx.x;
+  for (int i = t; i < 32 * 256; i += 256) {
+    const int r = i >> 8, c = i & 255;
+    float v = 0.f;
+    if (row0 + r < rows && col0 + c < C) v = __bfloat162float(x[(row0 + r) * C + col0 + c]);
+    tile[r][c] = v;
+  }
+  __syncthreads();
+  {
+    float a = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < 32; ++r) a = amax_nonfinite(a, tile[r][t]);
+    col_amax[t] = a;
+  }
+  __syncthreads();
+  float amax = col_amax[t];
+  if (kTile) {
+    const int g = t & ~31;
+    amax = 0.f;
+    for (int j = 0; j < 32; ++j) {
+      const float v = col_amax[g + j];
+      amax = (v != v || amax != amax) ? __int_as_float(0x7f800000) : fmaxf(amax, v);
+    }
+  }
+  float recip;
+  const uint8_t byte = mxfp8_scale(amax, recip);
+  const int c = col0 + t;
+  if (c < C) {
+    if (kTile) {
+      // batch_rows = rows of one expert: scale tensors are per-expert blocked groups.
+      const int64_t e = row0 / batch_rows, rl = row0 - e * batch_rows;
+      if ((t & 31) == 0) {
+        // forward orientation: 32 rows share the byte for k-block c/32
+        for (int r = 0; r < 32 && row0 + r < rows; ++r) {
+          const int64_t rr = row0 + r;
+          if (blocked) {
+            const int64_t grp = (batch_rows + 127) / 128 * 128 * static_cast<int64_t>(s0_col_atoms) * 4;
+            s0[e * grp + blocked_offset(rl + r, c >> 5, s0_col_atoms)] = byte;
+          } else {
+            s0[rr * ((C + 31) / 32) + (c >> 5)] = byte;
+          }
+        }
+      }
+      if (s1 != nullptr) {
+        // input-gradient orientation: row index = k (this column), column = n-block
+        const int64_t nb = rl >> 5;
+        if (blocked) {
+          const int64_t grp = (static_cast<int64_t>(C) + 127) / 128 * 128 * static_cast<int64_t>(s1_col_atoms) * 4;
+          s1[e * grp + blocked_offset(c, static_cast<int>(nb), s1_col_atoms)] = byte;
+        } else {
+          s1[(e * C + c) * ((batch_rows + 31) / 32) + nb] = byte;
+        }
+      }
+    } else {
+      const int64_t rb = row0 >> 5;
+      if (blocked)
+        s0[blocked_offset(c, static_cast<int>(rb), s0_col_atoms)] = byte;
+      else
+        s0[static_cast<int64_t>(c) * ((max_rows + 31) / 32) + rb] = byte;
+    }
+  }
+  // every thread converts one column of the slab: 32 rows, written as bytes into shared memory first
+  __syncthreads();
+  for (int r = 0; r < 32; ++r) tile[r][t] = tile[r][t] * recip;
+  __syncthreads();
+  for (int i = t; i < 32 * 64; i += 256) {
+    const int r = i >> 6, c4 = (i & 63) * 4;
+    if (row0 + r < rows && col0 + c4 < C) {
+      const uint32_t w = e4m3x4(tile[r][c4], tile[r][c4 + 1], tile[r][c4 + 2], tile[r][c4 + 3]);
+      *reinterpret_cast<uint32_t*>(q + (row0 + r) * C + col0 + c4) = w;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint8_t nvfp4_block_scale(float amax, float scale, float& mult) {
+  if (amax == __int_as_float(0x7f800000)) amax = __int_as_float(0x7fc00000);
+  float raw = (amax * scale) * (1.0f / 6.0f);
+  raw = raw < 0.001953125f ? 0.001953125f : raw;
+  raw = raw > 448.0f ? 448.0f : raw;
+  const uint8_t byte =
+      static_cast<uint8_t>(__nv_cvt_float2_to_fp8x2(make_float2(raw, 0.f), __NV_SATFINITE, __NV_E4M3) & 0xFF);
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(byte, __NV_E4M3);
+  const float sf = __half2float(*reinterpret_cast<const __half*>(&h));
+  mult = byte != 0 ? __fdiv_rn(scale, sf) : 0.f;
+  return byte;
+}
+
+__device__ __forceinline__ uint32_t e2m1x8(const float (&f)[8], float m) {
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t b = __nv_cvt_float2_to_fp4x2(make_float2(f[2 * i] * m, f[2 * i + 1] * m), __NV_E2M1, cudaRoundNearest);
+    out |= (b & 0xFF) << (8 * i);
+  }
+  return out;
+}
+
+// One CTA (128 threads) per token row: row amax, then 16-element blocks (2 threads each).
+__global__ void __launch_bounds__(128) nvfp4_token_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
+                                                          int64_t max_rows, int vec_per_row, uint8_t* q,
+                                                          int64_t q_stride, uint8_t* s, int64_t s_stride,
+                                                          uint8_t* inv, int64_t inv_stride) {
+  __shared__ float red[4];
+  int64_t rows = num_rows ? *num_rows : max_rows;
+  if (rows > max_rows) rows = max_rows;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* xr = x + r * vec_per_row;
+    float amax = 0.f;
+    for (int v = threadIdx.x; v < vec_per_row; v += 128) {
+      float f[8];
+      unpack8f(xr[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float row_scale = 2688.0f * __frcp_rn(fmaxf(amax, 1e-8f));
+    if (threadIdx.x == 0 && inv != nullptr) *reinterpret_cast<float*>(inv + r * inv_stride) = __frcp_rn(row_scale);
+    for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+      const int v = v0 + threadIdx.x;
+      float f[8];
+      float bmax = 0.f;
+      if (v < vec_per_row) {
+        unpack8f(xr[v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bmax = amax_nonfinite(bmax, f[j]);
+      }
+      const float other = __shfl_xor_sync(0xffffffffu, bmax, 1);
+      bmax = (other != other) ? other : fmaxf(bmax, other);
+      float mult;
+      const uint8_t byte = nvfp4_block_scale(bmax, row_scale, mult);
+      if (v < vec_per_row) {
+        *reinterpret_cast<uint32_t*>(q + r * q_stride + v * 4) = e2m1x8(f, mult);
+        if ((v & 1) == 0) s[r * s_stride + (v >> 1)] = byte;
+      }
+    }
+  }
+}
+
+// Weights: per-expert global scale given; rows of K elements; scales natural or blocked per expert.
+__global__ void __launch_bounds__(256) nvfp4_weight_kernel(const uint4* __restrict__ w, const float* __restrict__ gs,
+                                                           int64_t rows_per_expert, int64_t total_rows,
+                                                           int vec_per_row, uint32_t* __restrict__ q,
+                                                           uint8_t* __restrict__ s, int blocked, int n_col_atoms) {
+  const int64_t total = total_rows * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < (total + 31) / 32 * 32;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const bool live = i < total;
+    const int64_t r = live ? i / vec_per_row : 0;
+    const int64_t e = r / rows_per_expert;
+    float f[8];
+    float bmax = 0.f;
+    if (live) {
+      unpack8f(w[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bmax = amax_nonfinite(bmax, f[j]);
+    }
+    const float other = __shfl_xor_sync(0xffffffffu, bmax, 1);
+    bmax = (other != other) ? other : fmaxf(bmax, other);
+    if (!live) continue;
+    float g = gs[e];
+    g = g > 1e-12f ? g : 1e-12f;
+    float mult;
+    const uint8_t byte = nvfp4_block_scale(bmax, g, mult);
+    q[i] = e2m1x8(f, mult);
+    if ((i & 1) == 0) {
+      const int blk = static_cast<int>(i - r * vec_per_row) >> 1;
+      if (blocked) {
+        const int64_t rl = r - e * rows_per_expert;
+        const int64_t grp = (rows_per_expert + 127) / 128 * 128 * static_cast<int64_t>(n_col_atoms) * 4;
+        s[e * grp + blocked_offset(rl, blk, n_col_atoms)] = byte;
+      } else {
+        s[r * (vec_per_row >> 1) + blk] = byte;
+      }
+    }
+  }
+}
+
+// natural [rows][cols] scale bytes -> blocked atoms (padding entries are written as 0)
+__global__ void sf_swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows, int cols,
+                                  int64_t padded_rows, int n_col_atoms) {
+  const int64_t total = padded_rows * n_col_atoms * 4;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / (n_col_atoms * 4);
+    const int c = static_cast<int>(i - r * (n_col_atoms * 4));
+    dst[blocked_offset(r, c, n_col_atoms)] = (r < rows && c < cols) ? src[r * cols + c] : 0;
+  }
+}
+
+static int blocks_for(int64_t items, int threads, int cap) {
+  int64_t b = (items + threads - 1) / threads;
+  if (b > cap) b = cap;
+  return b < 1 ? 1 : static_cast<int>(b);
+}
+
+}  // namespace dm
+
+using namespace dm;
+
+extern "C" int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+                                  void* scales, int blocked, void* stream) {
+  if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 32) != 0) return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  const int vec = static_cast<int>(C / 8);
+  const int atoms = static_cast<int>((C / 32 + 3) / 4);
+  mxfp8_row_kernel<<<blocks_for(max_rows * vec, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), num_rows, max_rows, vec, static_cast<uint2*>(q), static_cast<uint8_t*>(scales),
+      blocked, atoms);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+                                  void* scales, int blocked, void* stream) {
+  if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 4) != 0) return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
+  const int atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  mxfp8_slab_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q),
+      static_cast<uint8_t*>(scales), nullptr, blocked, atoms, 0, max_rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
+                                     void* col_scales, int blocked, void* stream) {
+  if (!w || !q || !row_scales || experts <= 0 || N <= 0 || K <= 0 || (N % 32) != 0 || (K % 32) != 0) return kRcBadArg;
+  const int64_t rows = experts * N;
+  const dim3 grid(static_cast<unsigned>((K + 255) / 256), static_cast<unsigned>(rows / 32));
+  mxfp8_slab_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), nullptr, rows, static_cast<int>(K), static_cast<uint8_t*>(q),
+      static_cast<uint8_t*>(row_scales), static_cast<uint8_t*>(col_scales), blocked,
+      static_cast<int>((K / 32 + 3) / 4), static_cast<int>((N / 32 + 3) / 4), N);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+                                    int64_t q_row_stride, void* scales, int64_t scale_row_stride, void* scale_inv,
+                                    int64_t inv_row_stride, void* stream) {
+  if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 16) != 0 || (q_row_stride % 4) != 0) return kRcBadArg;
+  if (scale_inv && (inv_row_stride % 4) != 0) return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  nvfp4_token_kernel<<<blocks_for(max_rows, 1, 148 * 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C / 8), static_cast<uint8_t*>(q),
+      q_row_stride, static_cast<uint8_t*>(scales), scale_row_stride, static_cast<uint8_t*>(scale_inv),
+      inv_row_stride);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_nvfp4_weight(const void* w, const float* global_scale, int64_t experts, int64_t N, int64_t K,
+                                     void* q, void* scales, int blocked, void* stream) {
+  if (!w || !global_scale || !q || !scales || experts <= 0 || N <= 0 || K <= 0 || (K % 16) != 0) return kRcBadArg;
+  const int vec = static_cast<int>(K / 8);
+  nvfp4_weight_kernel<<<blocks_for(experts * N * vec, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(w), global_scale, N, experts * N, vec, static_cast<uint32_t*>(q),
+      static_cast<uint8_t*>(scales), blocked, static_cast<int>((K / 16 + 3) / 4));
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_sf_swizzle(const void* natural, void* blocked_out, int64_t rows, int64_t cols, void* stream) {
+  if (!natural || !blocked_out || rows <= 0 || cols <= 0) return kRcBadArg;
+  const int64_t padded_rows = (rows + 127) / 128 * 128;
+  const int atoms = static_cast<int>((cols + 3) / 4);
+  sf_swizzle_kernel<<<blocks_for(padded_rows * atoms * 4, 256, 148 * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(natural), static_cast<uint8_t*>(blocked_out), rows, static_cast<int>(cols),
+      padded_rows, atoms);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -230,6 +230,39 @@ int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int ac
                   const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
                   int64_t Kd, int num_sms, int* status, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Block-scaled quantisers (dist_moe/_quantization.py:66-133 `quantize_for_format`;
+ * dist_moe/kernels/blockscaled_quantize.py:5219 `quantize_block_scaled`, 5451
+ * `quantize_block_scaled_axes`, 5080 `_quantize_nvfp4_per_token`;
+ * dist_moe/kernels/scale_factor_layout.py:414 `natural_to_cublas_blocked`).
+ * Inputs are bf16, row-major.  Scale bytes are written in natural row-major order or, with
+ * blocked != 0, in 128x4 atoms: atom*512 + (row%32)*16 + (row/32%4)*4 + col%4, atoms ordered
+ * (row atom, column atom), rows padded to 128 and scale columns to 4.
+ *   dm_quant_mxfp8_row    1x32 blocks along C: q[R,C] e4m3, scales [R, C/32] e8m0.
+ *   dm_quant_mxfp8_col    32x1 blocks along the rows: q[R,C], scales [C, ceil(max_rows/32)].
+ *   dm_quant_mxfp8_tile32 32x32 tiles of W[experts*N, K]: shared q, row_scales [experts*N, K/32]
+ *                         and (optional) col_scales [experts*K, N/32]; blocked groups are per expert.
+ *   dm_quant_nvfp4_token  per-token NVFP4: packed e2m1 pairs (even element in the low nibble),
+ *                         e4m3 scales per 16 elements and the fp32 inverse row scale, each with its
+ *                         own byte stride so that the packed dispatch row [q | scales | inv | pad]
+ *                         (dist_moe/_blockscaled.py:408-507) and dense outputs use the same kernel.
+ *   dm_quant_nvfp4_weight per-expert NVFP4 with a given fp32 global scale per expert.
+ *   dm_sf_swizzle         natural scale bytes -> blocked atoms.
+ * num_rows (device int32, may be NULL) bounds the rows that are processed.
+ * ------------------------------------------------------------------------- */
+int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q, void* scales,
+                       int blocked, void* stream);
+int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q, void* scales,
+                       int blocked, void* stream);
+int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
+                          void* col_scales, int blocked, void* stream);
+int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+                         int64_t q_row_stride, void* scales, int64_t scale_row_stride, void* scale_inv,
+                         int64_t inv_row_stride, void* stream);
+int dm_quant_nvfp4_weight(const void* w, const float* global_scale, int64_t experts, int64_t N, int64_t K, void* q,
+                          void* scales, int blocked, void* stream);
+int dm_sf_swizzle(const void* natural, void* blocked_out, int64_t rows, int64_t cols, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

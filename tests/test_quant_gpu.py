@@ -1,0 +1,158 @@
+"""CUDA quantisers through the C ABI, bit-exact against the CPU oracle (`oracle/quant.py`), which
+is itself held to the reference's Triton quantiser for MXFP8.  Sizes up to the full C3 row width."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant as Q
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _nat():
+    from dist_moe_b200 import _native
+
+    return _native
+
+
+def _data(rows, cols, seed, spread=True, specials=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    if spread:
+        x = x * torch.logspace(-4, 3, rows)[:, None]
+    x = x.bfloat16()
+    if specials and rows > 4:
+        x[0, :32] = 0
+        x[1, 7] = float("inf")
+        x[2, 40] = float("nan")
+        x[3, :32] = 448.0
+    return x
+
+
+@pytest.mark.parametrize("rows,cols,blocked", [(37, 256, 0), (200, 384, 1), (1000, 4096, 1), (1, 32, 0)])
+def test_mxfp8_row(rows, cols, blocked):
+    nat = _nat()
+    x = _data(rows, cols, rows)
+    xd = x.to(DEV)
+    q = torch.zeros(rows, cols, dtype=torch.uint8, device=DEV)
+    sc = cols // 32
+    atoms = (sc + 3) // 4
+    n_s = ((rows + 127) // 128 * 128) * atoms * 4 if blocked else rows * sc
+    s = torch.full((n_s,), 0xEE, dtype=torch.uint8, device=DEV)
+    cnt = torch.tensor([rows], dtype=torch.int32, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_row(xd.data_ptr(), cnt.data_ptr(), rows, cols, q.data_ptr(), s.data_ptr(), blocked,
+                                         nat.stream_ptr()), "mxfp8_row")
+    torch.cuda.synchronize()
+    rq, rs = Q.mxfp8_row(x)
+    got_s = s.cpu().numpy()
+    if blocked:
+        r, c = np.meshgrid(np.arange(rows), np.arange(sc), indexing="ij")
+        got_s = got_s[Q.blocked_scale_offset(r, c, atoms)]
+    else:
+        got_s = got_s.reshape(rows, sc)
+    np.testing.assert_array_equal(got_s, rs)
+    finite = np.repeat(rs != 255, 32, axis=1)
+    gq = q.cpu().numpy()
+    np.testing.assert_array_equal(gq[finite], rq[finite])
+    assert ((gq[~finite] & 0x7F) == 0x7F).all()
+
+
+@pytest.mark.parametrize("rows,cols", [(96, 64), (333, 520), (4096, 1536)])
+def test_mxfp8_col(rows, cols):
+    nat = _nat()
+    x = _data(rows, cols, rows + 1, specials=False)
+    q = torch.zeros(rows, cols, dtype=torch.uint8, device=DEV)
+    rb = (rows + 31) // 32
+    s = torch.zeros(cols * rb, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_col(x.to(DEV).data_ptr(), None, rows, cols, q.data_ptr(), s.data_ptr(), 0,
+                                         nat.stream_ptr()), "mxfp8_col")
+    torch.cuda.synchronize()
+    rq, rs = Q.mxfp8_col(x)
+    np.testing.assert_array_equal(s.cpu().numpy().reshape(cols, rb), rs)
+    np.testing.assert_array_equal(q.cpu().numpy(), rq)
+
+
+@pytest.mark.parametrize("experts,n,k,blocked", [(2, 64, 96, 0), (3, 256, 512, 1)])
+def test_mxfp8_tile32_weights(experts, n, k, blocked):
+    nat = _nat()
+    w = _data(experts * n, k, 11, spread=False, specials=False) * 0.02
+    w = w.bfloat16()
+    q = torch.zeros(experts * n, k, dtype=torch.uint8, device=DEV)
+    a0, a1 = (k // 32 + 3) // 4, (n // 32 + 3) // 4
+    g0 = (n + 127) // 128 * 128 * a0 * 4 if blocked else n * (k // 32)
+    g1 = (k + 127) // 128 * 128 * a1 * 4 if blocked else k * (n // 32)
+    s0 = torch.zeros(experts * g0, dtype=torch.uint8, device=DEV)
+    s1 = torch.zeros(experts * g1, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_tile32(w.to(DEV).data_ptr(), experts, n, k, q.data_ptr(), s0.data_ptr(),
+                                            s1.data_ptr(), blocked, nat.stream_ptr()), "tile32")
+    torch.cuda.synchronize()
+    gq, g0s, g1s = q.cpu().numpy(), s0.cpu().numpy().reshape(experts, -1), s1.cpu().numpy().reshape(experts, -1)
+    for e in range(experts):
+        rq, rs = Q.mxfp8_tile32(w[e * n:(e + 1) * n])
+        np.testing.assert_array_equal(gq[e * n:(e + 1) * n], rq)
+        row_s = np.repeat(rs, 32, axis=0)            # [n, k/32]
+        col_s = np.repeat(rs.T, 32, axis=0)          # [k, n/32]
+        if blocked:
+            r, c = np.meshgrid(np.arange(n), np.arange(k // 32), indexing="ij")
+            np.testing.assert_array_equal(g0s[e][Q.blocked_scale_offset(r, c, a0)], row_s)
+            r, c = np.meshgrid(np.arange(k), np.arange(n // 32), indexing="ij")
+            np.testing.assert_array_equal(g1s[e][Q.blocked_scale_offset(r, c, a1)], col_s)
+        else:
+            np.testing.assert_array_equal(g0s[e].reshape(n, k // 32), row_s)
+            np.testing.assert_array_equal(g1s[e].reshape(k, n // 32), col_s)
+
+
+@pytest.mark.parametrize("rows,cols", [(33, 256), (128, 7168), (5, 2880 - 2880 % 16)])
+def test_nvfp4_token_dense_and_packed_rows(rows, cols):
+    nat = _nat()
+    x = _data(rows, cols, rows + 2, specials=False)
+    xd = x.to(DEV)
+    rp, rs, rinv = Q.nvfp4_token_rows(x)
+    # dense outputs
+    q = torch.zeros(rows, cols // 2, dtype=torch.uint8, device=DEV)
+    s = torch.zeros(rows, cols // 16, dtype=torch.uint8, device=DEV)
+    inv = torch.zeros(rows, dtype=torch.float32, device=DEV)
+    nat.check(nat.lib.dm_quant_nvfp4_token(xd.data_ptr(), None, rows, cols, q.data_ptr(), cols // 2, s.data_ptr(),
+                                           cols // 16, inv.data_ptr(), 4, nat.stream_ptr()), "nvfp4_token")
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(inv.cpu().numpy().view(np.uint32), rinv.view(np.uint32))
+    np.testing.assert_array_equal(s.cpu().numpy(), rs)
+    np.testing.assert_array_equal(q.cpu().numpy(), rp)
+    # packed dispatch row [q | scales | inv | pad16]: bit-identical to the dense call
+    stride = (cols // 2 + cols // 16 + 4 + 15) // 16 * 16
+    packed = torch.zeros(rows, stride, dtype=torch.uint8, device=DEV)
+    base = packed.data_ptr()
+    nat.check(nat.lib.dm_quant_nvfp4_token(xd.data_ptr(), None, rows, cols, base, stride, base + cols // 2, stride,
+                                           base + cols // 2 + cols // 16, stride, nat.stream_ptr()), "nvfp4_token")
+    torch.cuda.synchronize()
+    p = packed.cpu().numpy()
+    np.testing.assert_array_equal(p[:, : cols // 2], rp)
+    np.testing.assert_array_equal(p[:, cols // 2 : cols // 2 + cols // 16], rs)
+    got_inv = np.ascontiguousarray(p[:, cols // 2 + cols // 16 : cols // 2 + cols // 16 + 4]).view(np.uint32)[:, 0]
+    np.testing.assert_array_equal(got_inv, rinv.view(np.uint32))
+
+
+def test_nvfp4_weight_and_swizzle():
+    nat = _nat()
+    experts, n, k = 3, 160, 256
+    g = torch.Generator().manual_seed(7)
+    w = (torch.randn(experts, n, k, generator=g) * 0.02).bfloat16()
+    rp, rs, gs, gsi = Q.nvfp4_weight(w)
+    wd = w.to(DEV)
+    amax = torch.linalg.vector_norm(wd, ord=float("inf"), dim=(-2, -1), dtype=torch.float32).clamp(min=1e-12)
+    gsd = 2688.0 * torch.reciprocal(amax)
+    np.testing.assert_array_equal(gsd.cpu().numpy().view(np.uint32), gs.view(np.uint32))
+    q = torch.zeros(experts, n, k // 2, dtype=torch.uint8, device=DEV)
+    s = torch.zeros(experts * n, k // 16, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_quant_nvfp4_weight(wd.data_ptr(), gsd.data_ptr(), experts, n, k, q.data_ptr(), s.data_ptr(), 0,
+                                            nat.stream_ptr()), "nvfp4_weight")
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(s.cpu().numpy().reshape(experts, n, k // 16), rs)
+    np.testing.assert_array_equal(q.cpu().numpy(), rp)
+    # swizzle natural -> blocked equals the oracle's layout, padding zeroed
+    sw = torch.full(((n + 127) // 128 * 128 * 4 * 4,), 0xEE, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_sf_swizzle(s[:n].contiguous().data_ptr(), sw.data_ptr(), n, k // 16, nat.stream_ptr()), "swz")
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(sw.cpu().numpy(), Q.to_blocked(rs[0]))

@@ -231,6 +231,24 @@ int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int ac
                   int64_t Kd, int num_sms, int* status, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Fused post-expert RMSNorm + weighted top-k reduction
+ * (dist_moe/kernels/norm/fused_rmsnorm_combine.py:576-765 forward, 802-1018 backward,
+ *  427-466 the unfused composition that defines the numerics):
+ *   y = cast_norm(g * h3 * rstd), rstd = rsqrt(mean((g*h3)^2) + eps), out = bf16(sum_k s_k * y_k);
+ *   g = gamma + gain_center when gamma (bf16[D]) is given, else 1.  rstd_out (fp32[T,K], may be
+ *   NULL) receives rstd (0 for skipped routes).  save_* as in dm_scale_and_sum.
+ *   Backward writes grad_h3 (may alias h3) and grad_scores; rstd == NULL recomputes it from h3.
+ * ------------------------------------------------------------------------- */
+int dm_rmsnorm_combine_fwd(const void* h3, const void* scores, int scores_are_bf16, const void* ids,
+                           int ids_are_int64, const void* gamma, float gain_center, float eps, int norm_is_bf16,
+                           void* out, float* rstd_out, int64_t T, int K, int64_t D, void* save_base,
+                           const int64_t* save_offset, const int* save_cond, int save_expect, void* stream);
+int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
+                           int ids_are_int64, const void* h3_base, const int64_t* h3_offset, const float* rstd,
+                           float eps, int norm_is_bf16, void* grad_h3, float* grad_scores, int64_t T, int K,
+                           int64_t D, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Block-scaled quantisers (dist_moe/_quantization.py:66-133 `quantize_for_format`;
  * dist_moe/kernels/blockscaled_quantize.py:5219 `quantize_block_scaled`, 5451
  * `quantize_block_scaled_axes`, 5080 `_quantize_nvfp4_per_token`;

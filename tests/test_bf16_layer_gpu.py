@@ -146,3 +146,59 @@ def test_clip_stats_and_inference_context():
             dm.routed_experts(x.to(dev).requires_grad_(True), ids.to(dev), scores.to(dev), w13.to(dev), w2.to(dev), ctx)
     finally:
         ctx.close()
+
+
+@pytest.mark.parametrize("norm_dtype,recompute_rstd,slot_factor", [(torch.float32, False, 1.0), (torch.bfloat16, True, None)])
+def test_fused_rmsnorm_postprocess_forward_backward(norm_dtype, recompute_rstd, slot_factor):
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 100, 512, 256, 2, 8
+    x, ids, scores, w13, w2 = make_case(T, D, F, K, E, seed=21, drop=0.05, w_scale=D**-0.5)
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, activation_slot_capacity_factor=slot_factor)
+    ctx = dm.create_context(group=None, config=cfg, device=0)
+    try:
+        post = dm.RMSNormPostprocess(eps=1e-6, norm_output_dtype=norm_dtype, output_dtype=torch.bfloat16,
+                                     require_bitwise=False, recompute_rstd=recompute_rstd)
+        got = run_ours(dm, ctx, x, ids, scores, w13, w2, options=dm.ExecutionOptions(experts_output_postprocess=post))
+        xs = x.clone().requires_grad_(True)
+        ss = scores.clone().requires_grad_(True)
+        a = w13.clone().requires_grad_(True)
+        b = w2.clone().requires_grad_(True)
+        h3 = oracle_moe.expert_outputs(xs, ids, a.reshape(E, 2 * F, D), b)
+        h3 = torch.where((ids >= 0)[:, :, None], h3, torch.zeros_like(h3))
+        hf = h3.float()
+        rstd = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * (ids >= 0)[:, :, None]
+        y = (hf * rstd).to(norm_dtype).float()
+        ref = (y * ss[:, :, None]).sum(1).to(torch.bfloat16)
+        ref.float().sum().backward()
+        assert_close(got[0], ref, what="rmsnorm output", **BF16_FWD)
+        assert_close(got[1].grad, xs.grad, what="rmsnorm grad x", **BF16_GRAD)
+        assert_close(got[2].grad, ss.grad, what="rmsnorm grad scores", **BF16_GRAD)
+        assert_close(got[3].grad, a.grad, what="rmsnorm grad w13", **BF16_WGRAD)
+        assert_close(got[4].grad, b.grad, what="rmsnorm grad w2", **BF16_WGRAD)
+    finally:
+        ctx.close()
+
+
+def test_rmsnorm_gamma_inference():
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 40, 256, 256, 8, 16
+    x, ids, scores, w13, w2 = make_case(T, D, F, K, E, seed=22, w_scale=D**-0.5)
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0)
+    ctx = dm.create_context(group=None, config=cfg, device=0)
+    try:
+        dev = torch.device("cuda", 0)
+        gamma = (torch.randn(D) * 0.1).bfloat16()
+        post = dm.RMSNormPostprocess(eps=1e-5, norm_output_dtype=torch.float32, output_dtype=torch.bfloat16,
+                                     weight=gamma.to(dev), gain_center=1.0)
+        out = dm.routed_experts(x.to(dev), ids.to(dev), scores.to(dev), w13.to(dev), w2.to(dev), ctx,
+                                options=dm.ExecutionOptions(experts_output_postprocess=post))
+        ctx.check_status()
+        h3 = oracle_moe.expert_outputs(x, ids, w13.reshape(E, 2 * F, D), w2)
+        ref = oracle_moe.rmsnorm_combine(h3, scores, 1e-5, torch.bfloat16, weight=gamma, gain_center=1.0)
+        assert_close(out, ref, what="gamma rmsnorm", **BF16_FWD)
+    finally:
+        ctx.close()

@@ -151,6 +151,14 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, in
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), no multicast.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -195,6 +203,53 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       "}\n"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// Block-scaled MMAs: scale factors live in TMEM (copied there by tcgen05.cp from shared memory).
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void umma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Copy one 128-row x 4-scale atom (32 rows x 16 bytes in shared memory) into 4 TMEM columns, replicated
+// over the four 32-lane sub-partitions.
+__device__ __forceinline__ void tmem_cp_sf_atom(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Shared-memory descriptor of a scale atom: no swizzle, rows 16 bytes apart, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>(16 >> 4) << 16;
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+// Instruction descriptor of the block-scaled kinds (M128, K-major operands).
+//   fp4 == 0: kind::mxf8f6f4, E4M3 data, UE8M0 scales, sf ids select the scale byte of the K=32 step.
+//   fp4 != 0: kind::mxf4nvf4, E2M1 data, UE4M3 scales (4 per K=64 step).
+__host__ __device__ constexpr uint32_t umma_idesc_blockscaled(int n, int fp4, int a_sf_id, int b_sf_id) {
+  return (static_cast<uint32_t>(b_sf_id) << 4) | (static_cast<uint32_t>(fp4 ? 1 : 0) << 7) |
+         (static_cast<uint32_t>(fp4 ? 1 : 0) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(fp4 ? 0 : 1) << 23) | (static_cast<uint32_t>(128 >> 4) << 24) |
+         (static_cast<uint32_t>(a_sf_id) << 29);
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp reads TMEM lane

@@ -21,10 +21,7 @@
 //   dgrad  C[r,n]  = sum_k A[r,k] W[e][k][n]     A K-major, W N-major
 //   wgrad  dW[e][n][k] (+)= sum_r dY[r,n] X[r,k] both operands MN-major; the ragged last
 //          64-row chunk of an expert is zeroed in shared memory before the MMA reads it.
-#include <cuda.h>
-
-#include "common.cuh"
-#include "../../include/dist_moe_b200.h"
+#include "gemm_common.cuh"
 
 namespace dm {
 
@@ -38,7 +35,6 @@ constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kStagingBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
 constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 4 * kStagingBytes + 1024;  // + slack for 1024-byte alignment
 
 enum GemmMode : int { kFprop = 0, kDgrad = 1, kWgrad = 2 };
@@ -65,32 +61,6 @@ struct GemmParams {
   int accumulate;
   ActParams act;
 };
-
-// Staging tile of one epilogue warp: row r is 128 bytes, its 16-byte chunk j sits at j ^ (r & 7).
-__device__ __forceinline__ void stage_put(uint8_t* stg, int row, int chunk, uint4 v) {
-  reinterpret_cast<uint4*>(stg + row * 128)[chunk ^ (row & 7)] = v;
-}
-__device__ __forceinline__ uint4 stage_get(const uint8_t* stg, int row, int chunk) {
-  return reinterpret_cast<const uint4*>(stg + row * 128)[chunk ^ (row & 7)];
-}
-__device__ __forceinline__ uint4 pack8_bf16(const uint32_t* r) {
-  return make_uint4(pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
-                    pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
-                    pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
-                    pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
-}
-
-// 16-byte fire-and-forget reductions performed by L2 (each output tile has one owner CTA).
-__device__ __forceinline__ void red_add_f32x4(uint64_t addr, uint4 v) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
-               : "memory");
-}
-__device__ __forceinline__ void red_add_bf16x8(uint64_t addr, uint4 v) {
-  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
 
 struct Tile {
   int e, m_blk, n_blk, row0, row_end, k_iters;
@@ -507,68 +477,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-}
-
-// ---------------------------------------------------------------------------
-// Host side: tensor-map encoding through the driver entry point (no link-time
-// dependency on libcuda) and launch.
-// ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
-// bf16 matrix [rows][cols], cols contiguous; box = box_rows x 64 columns.
-static int encode_2d(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return kRcNoDriver;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
-}
-
-// Arena view: element (c0, line, row) lives at base + 2*c0 + 128*line + pitch*row.
-// `line` spans the whole allocation, so an operand at byte offset o is reached
-// with line = o/128 + column/64; rows may run `guard` rows past the operand.
-static int encode_arena(CUtensorMap* tm, const dm_operand& op, int64_t pitch_bytes, int64_t rows, int box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return kRcNoDriver;
-  const int64_t lines = op.bytes / 128;
-  if (lines <= 0 || (pitch_bytes % 128) != 0 || (reinterpret_cast<uintptr_t>(op.base) % 128) != 0) return kRcBadArg;
-  cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(lines), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(pitch_bytes)};
-  cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, op.base, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
-}
-
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
 }
 
 template <int kMode>

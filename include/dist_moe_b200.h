@@ -231,6 +231,27 @@ int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int ac
                   int64_t Kd, int num_sms, int* status, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Block-scaled grouped GEMM on tcgen05 with scale factors in TMEM
+ * (dist_moe/_blockscaled_ops.py:172-932: `dist_blockscaled_grouped_gemm_fprop_dispatch`,
+ *  `..._fprop_swiglu_fwd_combine`; kernels dist_moe/kernels/dist_blockscaled_grouped_gemm_kernel.py).
+ *   format 0 = MXFP8 (E4M3 data, E8M0 scale per 32), 1 = NVFP4 (packed E2M1 data, E4M3 scale per 16).
+ *   A   [rows, Kd] quantised, row-major, with blocked scales `sfa` (rows padded to 128);
+ *   W   [e_local, N, Kd] quantised with blocked scales `sfb`, one blocked group per expert;
+ *   C   bf16 [rows, N] = dequant(A) * dequant(W)^T, optionally times row_scale_inv[row] (fp32, per
+ *       token) and expert_scale_inv[e] (fp32) in that order (the NVFP4 global scales);
+ *   scatter_ptrs != NULL sends row r of C to scatter_ptrs[r] instead;
+ *   swiglu_interleaved != 0: W is W13 with rows interleaved in groups of 8 gate / 8 up rows
+ *       (dist_moe/_blockscaled_weight.py:16-39); writes h2 = bf16(SwiGLU(bf16 gate, bf16 up)) [rows, N/2]
+ *       and, when C is given, h1 = [gate | up] in the canonical (not interleaved) column order.
+ * Every expert's row range must start on a multiple of 128 (routing with m_multiple_of = 128).
+ * ------------------------------------------------------------------------- */
+int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w, const void* sfb, dm_operand c,
+                        dm_operand h2, const int64_t* scatter_ptrs, dm_operand row_scale_inv,
+                        const float* expert_scale_inv, const int32_t* expert_offsets, int e_local, int64_t max_rows,
+                        int64_t N, int64_t Kd, int swiglu_interleaved, int clamped, float alpha, float limit,
+                        const int* cond, int num_sms, int* status, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Fused post-expert RMSNorm + weighted top-k reduction
  * (dist_moe/kernels/norm/fused_rmsnorm_combine.py:576-765 forward, 802-1018 backward,
  *  427-466 the unfused composition that defines the numerics):

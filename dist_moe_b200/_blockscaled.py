@@ -1,0 +1,301 @@
+"""Block-scaled (MXFP8 E4M3 / NVFP4) execution: weight preparation and the forward path.
+
+Launch order of the forward (mirrors the reference's staged block-scaled forward,
+dist_moe/_blockscaled.py:1309-1931, with static inference storage):
+
+  quantise x into the packed symmetric dispatch row [q | scales | inverse row scale | pad]
+  -> publish ids -> barrier -> route (per-expert rows padded to 128, packed row stride)
+  -> gather packed rows (peer loads) into dense q rows + blocked scales
+  -> W13 block-scaled GEMM with fused SwiGLU (interleaved prepared W13) -> bf16 h2
+  -> quantise h2 rows -> W2 block-scaled GEMM, rows scattered to the owners' combine buffers
+  -> barrier -> weighted top-k reduction (or fused RMSNorm).
+
+Weight preparation follows dist_moe/_blockscaled.py:798-882 (MXFP8) and 140-196 (NVFP4):
+MXFP8 training weights use 32x32 tiles with one shared qdata and two scale orientations,
+MXFP8 inference weights 1x32 rows, NVFP4 a per-expert fp32 global scale ``2688 / amax``.
+``fuse_swiglu`` interleaves W13 rows in groups of 8 gate / 8 up rows
+(dist_moe/_blockscaled_weight.py:16-39) so that one 128-row tile holds matching pairs.
+
+The MXFP8 *backward* (block-scaled dgrad/wgrad) is not implemented in this revision:
+``routed_experts`` raises ``NotImplementedError`` when autograd state would be needed.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from . import _native as nat
+from ._execution import ExecutionOptions, PreparedWeight, RMSNormPostprocess
+from .formats import BlockScaledFormat
+
+
+def _fmt_id(fmt: BlockScaledFormat) -> int:
+    return 1 if fmt is BlockScaledFormat.NVFP4 else 0
+
+
+def _geometry(fmt: BlockScaledFormat, dim: int) -> tuple[int, int]:
+    """(quantised bytes per row, scale columns per row) of a [*, dim] operand."""
+    if fmt is BlockScaledFormat.NVFP4:
+        return dim // 2, dim // 16
+    return dim, dim // 32
+
+
+def packed_row_stride(fmt: BlockScaledFormat, dim: int) -> int:
+    q, sc = _geometry(fmt, dim)
+    raw = q + sc + (4 if fmt is BlockScaledFormat.NVFP4 else 0)
+    return (raw + 15) // 16 * 16
+
+
+def interleave_index(F: int, device) -> torch.Tensor:
+    """Row order gate[0:8], up[0:8], gate[8:16], up[8:16], ... of a canonical [gate F | up F] W13."""
+    g = torch.arange(F, device=device).reshape(-1, 8)
+    return torch.stack([g, g + F], dim=1).reshape(-1)
+
+
+def _blocked_group_bytes(rows: int, scale_cols: int) -> int:
+    return (rows + 127) // 128 * 128 * ((scale_cols + 3) // 4) * 4
+
+
+def prepare_weight(weight: torch.Tensor, config, *, fuse_swiglu: bool = False, inference: bool = False,
+                   out: PreparedWeight | None = None) -> PreparedWeight:
+    if config.block_scaled is None:
+        raise ValueError("prepare_block_scaled_weight needs a config with a block_scaled policy")
+    fmt = config.block_scaled.format
+    if not isinstance(weight, torch.Tensor) or weight.device.type != "cuda" or weight.dtype != torch.bfloat16:
+        raise TypeError("weight must be a CUDA bfloat16 tensor")
+    if not weight.is_contiguous():
+        raise ValueError("weight must be contiguous")
+    if fmt is BlockScaledFormat.NVFP4 and not inference:
+        raise ValueError("NVFP4 weights are inference-only; pass inference=True")
+    D, F = config.hidden_dim, config.intermediate_dim
+    w = weight.detach()
+    if w.ndim == 4:
+        w = w.reshape(w.shape[0], w.shape[1] * w.shape[2], w.shape[3])
+    elif w.ndim == 2:
+        if D == F:
+            raise ValueError("a flattened 2-D weight is ambiguous when hidden_dim == intermediate_dim; pass it as 3-D")
+        w = w.reshape(-1, 2 * F if w.shape[1] == D else D, w.shape[1])
+    if w.ndim != 3:
+        raise ValueError("weight must be [E_local, N, K] (or one of the accepted W13/W2 layouts)")
+    E, N, K = w.shape
+    is_w13 = (N, K) == (2 * F, D)
+    if not is_w13 and (N, K) != (D, F):
+        raise ValueError(f"weight shape {tuple(weight.shape)} matches neither W13 [E, 2F, D] nor W2 [E, D, F]")
+    if fuse_swiglu:
+        if not is_w13:
+            raise ValueError("fuse_swiglu applies to the W13 projection only")
+        if not inference:
+            raise ValueError("fuse_swiglu (interleaved W13) is an inference-only layout")
+        if F % 64 != 0:
+            raise ValueError("fuse_swiglu needs intermediate_dim to be a multiple of 64")
+        w = w.index_select(1, interleave_index(F, w.device)).contiguous()
+    vec = 16 if fmt is BlockScaledFormat.NVFP4 else 32
+    if K % (256 if fmt is BlockScaledFormat.NVFP4 else 128) or N % 128:
+        raise ValueError("block-scaled weights need N % 128 == 0 and K % 128 == 0 (K % 256 for NVFP4)")
+    dev, st = w.device, nat.stream_ptr()
+    qb, sc = _geometry(fmt, K)
+    grp = _blocked_group_bytes(N, sc)
+
+    def storage(name, shape, dtype):
+        if out is not None:
+            t = getattr(out, name)
+            if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
+                raise ValueError(f"out.{name} does not match the prepared layout")
+            return t
+        return torch.zeros(shape, dtype=dtype, device=dev)
+
+    fprop_data = storage("fprop_data", (E, N, qb), torch.uint8)
+    fprop_scale = storage("fprop_scale", (E * grp,), torch.uint8)
+    dgrad_data = dgrad_scale = gs = gsi = None
+    if fmt is BlockScaledFormat.NVFP4:
+        amax = torch.linalg.vector_norm(w, ord=float("inf"), dim=(-2, -1), dtype=torch.float32).clamp(min=1e-12)
+        gs_new = 2688.0 * torch.reciprocal(amax)
+        gs = storage("global_scale", (E,), torch.float32)
+        gsi = storage("global_scale_inv", (E,), torch.float32)
+        gs.copy_(gs_new)
+        gsi.copy_(torch.reciprocal(gs_new))
+        nat.check(nat.lib.dm_quant_nvfp4_weight(w.data_ptr(), gs.data_ptr(), E, N, K, fprop_data.data_ptr(),
+                                                fprop_scale.data_ptr(), 1, st), "dm_quant_nvfp4_weight")
+    elif inference:
+        for e in range(E):
+            nat.check(nat.lib.dm_quant_mxfp8_row(w[e].data_ptr(), None, N, K, fprop_data[e].data_ptr(), 0,
+                                                 fprop_scale[e * grp:].data_ptr(), 0, 1, st), "dm_quant_mxfp8_row")
+    else:
+        grp_d = _blocked_group_bytes(K, N // 32)
+        dgrad_scale = storage("dgrad_scale", (E * grp_d,), torch.uint8)
+        nat.check(nat.lib.dm_quant_mxfp8_tile32(w.data_ptr(), E, N, K, fprop_data.data_ptr(), fprop_scale.data_ptr(),
+                                                dgrad_scale.data_ptr(), 1, st), "dm_quant_mxfp8_tile32")
+        dgrad_data = fprop_data
+    if out is not None:
+        return out
+    return PreparedWeight._create(source=weight, format=fmt, fprop_data=fprop_data, fprop_scale=fprop_scale,
+                                  dgrad_data=dgrad_data, dgrad_scale=dgrad_scale, global_scale=gs,
+                                  global_scale_inv=gsi, interleaved_fc13=bool(fuse_swiglu))
+
+
+class _Layout:
+    """Static carve of the scratch arena for the forward-only block-scaled path (capacity rows)."""
+
+    def __init__(self, state):
+        cfg, fmt = state.config, state.config.block_scaled.format
+        D, F, R = cfg.hidden_dim, cfg.intermediate_dim, state.capacity_rows
+        a128 = lambda v: (v + 127) // 128 * 128  # noqa: E731
+        self.fp4 = fmt is BlockScaledFormat.NVFP4
+        xq, xs = _geometry(fmt, D)
+        hq, hs = _geometry(fmt, F)
+        off = 0
+        self.x_q, off = off, off + a128(R * xq)
+        self.x_sf, off = off, off + a128(_blocked_group_bytes(R, xs))
+        self.x_inv, off = off, off + a128(R * 4)
+        self.h_q, off = off, off + a128(R * hq)
+        self.h_sf, off = off, off + a128(_blocked_group_bytes(R, hs))
+        self.h_inv, off = off, off + a128(R * 4)
+        self.dense, off = off, off + a128(R * 2 * F * 2)   # h1 [R, 2F] (unfused) or h2 [R, F] (fused)
+        self.h2_dense, off = off, off + a128(R * F * 2)    # only used by the unfused path
+        self.total = off + 256 * max(D, 2 * F) * 2
+
+
+def _workspace(state):
+    ws = getattr(state, "_bs_workspace", None)
+    if ws is None:
+        lay = _Layout(state)
+        if lay.total <= state.arena.numel():
+            buf = state.arena
+        else:  # the reference aliases x and h2 row slots; this layout keeps them apart and may need more room
+            buf = torch.zeros(lay.total, dtype=torch.uint8, device=state.device)
+        ws = (lay, buf)
+        state._bs_workspace = ws
+    return ws
+
+
+def _view(buf: torch.Tensor, offset: int) -> nat.Operand:
+    return nat.Operand(buf.data_ptr() + offset, buf.numel() - offset, None)
+
+
+def _weights_for_call(w13, w2, state, cfg):
+    """Prepared operands of this call; raw bf16 weights are quantised on the fly (row mode)."""
+    if isinstance(w13, PreparedWeight):
+        if w13.format is not cfg.block_scaled.format or w2.format is not cfg.block_scaled.format:
+            raise ValueError("prepared weights use a different block-scaled format than the context")
+        return w13, w2
+    if cfg.block_scaled.format is BlockScaledFormat.NVFP4:
+        raise ValueError("NVFP4 requires weights from prepare_block_scaled_weight()")
+    p13 = prepare_weight(w13, cfg, fuse_swiglu=cfg.intermediate_dim % 64 == 0, inference=True)
+    p2 = prepare_weight(w2, cfg, inference=True)
+    return p13, p2
+
+
+def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, options: ExecutionOptions, *,
+                     save_for_backward: bool) -> torch.Tensor:
+    state = context._state
+    cfg = state.config
+    fmt = cfg.block_scaled.format
+    if save_for_backward:
+        raise NotImplementedError(
+            "dist_moe_b200 implements the block-scaled forward only; the MXFP8 backward "
+            "(block-scaled dgrad/wgrad) is not available yet")
+    if options.requires_eager:
+        raise NotImplementedError("Python callbacks are not supported by dist_moe_b200")
+    D, F, K, E = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k, cfg.num_experts
+    if D % 128 or F % 128:
+        raise ValueError("block-scaled execution needs hidden_dim and intermediate_dim to be multiples of 128")
+    x, scores = x.detach(), scores.detach()
+    T = x.shape[0]
+    p13, p2 = _weights_for_call(w13_weight, w2_weight, state, cfg)
+    lay, buf = _workspace(state)
+    f, st, status = _fmt_id(fmt), nat.stream_ptr(), state.status.data_ptr()
+    dev, el, ep = x.device, state.e_local, state.ep
+    clamped = 1 if cfg.activation == "swiglu_clamped" else 0
+    alpha, limit = float(cfg.swiglu_alpha), float(cfg.swiglu_limit)
+    xq, xs = _geometry(fmt, D)
+    hq, hs = _geometry(fmt, F)
+    stride = packed_row_stride(fmt, D)
+    dispatch = state.dispatch.local().data_ptr()
+    # ---- publish: quantise straight into the packed symmetric dispatch rows ----------------
+    if lay.fp4:
+        nat.check(nat.lib.dm_quant_nvfp4_token(x.data_ptr(), None, T, D, dispatch, stride, dispatch + xq, stride, 0,
+                                               dispatch + xq + xs, stride, st), "dm_quant_nvfp4_token")
+    else:
+        nat.check(nat.lib.dm_quant_mxfp8_row(x.data_ptr(), None, T, D, dispatch, stride, dispatch + xq, stride, 0, st),
+                  "dm_quant_mxfp8_row")
+    nat.check(nat.lib.dm_publish(None, ids.data_ptr(), int(ids.dtype == torch.int64), None,
+                                 state.routing.local().data_ptr(), T, 0, K, E, int(options.validate_expert_ids),
+                                 status, st), "dm_publish")
+    state.barrier(state.dispatch)
+    # ---- routing (rows of every expert padded to 128) -----------------------------------------
+    size = (ep * T * min(K, el) + el * 127 + 127) // 128 * 128
+    size = max(size, 128)
+    counts = torch.empty(el, dtype=torch.int32, device=dev)
+    per_rank = torch.empty(ep, dtype=torch.int32, device=dev)
+    offsets = torch.empty(el + 1, dtype=torch.int32, device=dev)
+    fwd = torch.empty(size, dtype=torch.int64, device=dev)
+    sct = torch.empty(size, dtype=torch.int64, device=dev)
+    max_rows = min(size, state.capacity_rows)
+    nat.check(nat.lib.dm_route(state.routing.peer_ptrs.data_ptr(), state.dispatch.peer_ptrs.data_ptr(),
+                               state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride, D * 2, 128,
+                               state.capacity_rows, size, counts.data_ptr(), per_rank.data_ptr(), offsets.data_ptr(),
+                               fwd.data_ptr(), None, sct.data_ptr(), state.route_workspace.data_ptr(),
+                               state.route_workspace_words, status, st), "dm_route")
+    recv = offsets[el:]
+    # ---- gather + unpack -----------------------------------------------------------------------
+    none = nat.Operand(None, 0, None)
+    nat.check(nat.lib.dm_gather_packed_rows(fwd.data_ptr(), recv.data_ptr(), max_rows, xq, xs, int(lay.fp4),
+                                            _view(buf, lay.x_q), _view(buf, lay.x_sf),
+                                            _view(buf, lay.x_inv) if lay.fp4 else none, None, st),
+              "dm_gather_packed_rows")
+    # ---- W13 (+SwiGLU) ---------------------------------------------------------------------------
+    fused = bool(p13._interleaved_fc13)
+    row_inv = _view(buf, lay.x_inv) if lay.fp4 else none
+    if fused:
+        h2_dense = lay.dense
+        nat.check(nat.lib.dm_gemm_blockscaled(f, _view(buf, lay.x_q), _view(buf, lay.x_sf), p13.fprop_data.data_ptr(),
+                                              p13.fprop_scale.data_ptr(), none, _view(buf, h2_dense), None, row_inv,
+                                              nat.ptr(p13.global_scale_inv), offsets.data_ptr(), el, max_rows, 2 * F,
+                                              D, 1, clamped, alpha, limit, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled(w13+swiglu)")
+    else:
+        h2_dense = lay.h2_dense
+        nat.check(nat.lib.dm_gemm_blockscaled(f, _view(buf, lay.x_q), _view(buf, lay.x_sf), p13.fprop_data.data_ptr(),
+                                              p13.fprop_scale.data_ptr(), _view(buf, lay.dense), none, None, row_inv,
+                                              nat.ptr(p13.global_scale_inv), offsets.data_ptr(), el, max_rows, 2 * F,
+                                              D, 0, 0, 1.0, 0.0, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled(w13)")
+        nat.check(nat.lib.dm_swiglu_fwd(buf.data_ptr() + lay.dense, None, buf.data_ptr() + h2_dense, None,
+                                        recv.data_ptr(), max_rows, F, clamped, alpha, limit, None, 0.0, None, st),
+                  "dm_swiglu_fwd")
+    # ---- quantise h2 rows --------------------------------------------------------------------------
+    h2_ptr = buf.data_ptr() + h2_dense
+    if lay.fp4:
+        nat.check(nat.lib.dm_quant_nvfp4_token(h2_ptr, recv.data_ptr(), max_rows, F, buf.data_ptr() + lay.h_q, hq,
+                                               buf.data_ptr() + lay.h_sf, 0, 1, buf.data_ptr() + lay.h_inv, 4, st),
+                  "dm_quant_nvfp4_token(h2)")
+    else:
+        nat.check(nat.lib.dm_quant_mxfp8_row(h2_ptr, recv.data_ptr(), max_rows, F, buf.data_ptr() + lay.h_q, 0,
+                                             buf.data_ptr() + lay.h_sf, 0, 1, st), "dm_quant_mxfp8_row(h2)")
+    # ---- W2 + scatter to the owners' combine buffers ---------------------------------------------
+    nat.check(nat.lib.dm_gemm_blockscaled(f, _view(buf, lay.h_q), _view(buf, lay.h_sf), p2.fprop_data.data_ptr(),
+                                          p2.fprop_scale.data_ptr(), none, none, sct.data_ptr(),
+                                          _view(buf, lay.h_inv) if lay.fp4 else none, nat.ptr(p2.global_scale_inv),
+                                          offsets.data_ptr(), el, max_rows, D, F, 0, 0, 1.0, 0.0, None, state.num_sms,
+                                          status, st), "dm_gemm_blockscaled(w2)")
+    state.barrier(state.combine)
+    out = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+    post = options.experts_output_postprocess
+    if isinstance(post, RMSNormPostprocess):
+        from ._postprocess import validate_rmsnorm
+
+        validate_rmsnorm(post, config=cfg, training=False, x_dtype=out.dtype)
+        nat.check(nat.lib.dm_rmsnorm_combine_fwd(
+            state.combine.local().data_ptr(), scores.data_ptr(), int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+            int(ids.dtype == torch.int64), nat.ptr(post.weight), float(post.gain_center), float(post.eps),
+            int(post.norm_output_dtype == torch.bfloat16), out.data_ptr(), None, T, K, D, None, None, None, 0, st),
+            "dm_rmsnorm_combine_fwd")
+    else:
+        nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
+                                           int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                           int(ids.dtype == torch.int64), out.data_ptr(), T, K, D, None, None, None, 0,
+                                           st), "dm_scale_and_sum")
+    state.last_recv = recv
+    return out

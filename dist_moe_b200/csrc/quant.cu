@@ -65,8 +65,9 @@ __device__ __forceinline__ int64_t blocked_offset(int64_t row, int col, int n_co
 // thread, 4 threads per block.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) mxfp8_row_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
-                                                        int64_t max_rows, int vec_per_row, uint2* __restrict__ q,
-                                                        uint8_t* __restrict__ scales, int blocked, int n_col_atoms) {
+                                                        int64_t max_rows, int vec_per_row, uint8_t* __restrict__ q,
+                                                        int64_t q_stride, uint8_t* __restrict__ scales,
+                                                        int64_t s_stride, int blocked, int n_col_atoms) {
   int64_t rows = num_rows ? *num_rows : max_rows;
   if (rows > max_rows) rows = max_rows;
   const int64_t total = rows * vec_per_row;
@@ -90,15 +91,17 @@ __global__ void __launch_bounds__(256) mxfp8_row_kernel(const uint4* __restrict_
     float recip;
     const uint8_t byte = mxfp8_scale(amax, recip);
     if (!live) continue;
-    q[i] = make_uint2(e4m3x4(f[0] * recip, f[1] * recip, f[2] * recip, f[3] * recip),
-                      e4m3x4(f[4] * recip, f[5] * recip, f[6] * recip, f[7] * recip));
-    if ((i & 3) == 0) {
-      const int64_t r = i / vec_per_row;
-      const int blk = static_cast<int>(i - r * vec_per_row) >> 2;
+    const int64_t r = i / vec_per_row;
+    const int v = static_cast<int>(i - r * vec_per_row);
+    *reinterpret_cast<uint2*>(q + r * q_stride + v * 8) =
+        make_uint2(e4m3x4(f[0] * recip, f[1] * recip, f[2] * recip, f[3] * recip),
+                   e4m3x4(f[4] * recip, f[5] * recip, f[6] * recip, f[7] * recip));
+    if ((v & 3) == 0) {
+      const int blk = v >> 2;
       if (blocked)
         scales[blocked_offset(r, blk, n_col_atoms)] = byte;
       else
-        scales[r * (vec_per_row >> 2) + blk] = byte;
+        scales[r * s_stride + blk] = byte;
     }
   }
 }
@@ -227,7 +230,7 @@ __device__ __forceinline__ uint32_t e2m1x8(const float (&f)[8], float m) {
 __global__ void __launch_bounds__(128) nvfp4_token_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
                                                           int64_t max_rows, int vec_per_row, uint8_t* q,
                                                           int64_t q_stride, uint8_t* s, int64_t s_stride,
-                                                          uint8_t* inv, int64_t inv_stride) {
+                                                          uint8_t* inv, int64_t inv_stride, int blocked_atoms) {
   __shared__ float red[4];
   int64_t rows = num_rows ? *num_rows : max_rows;
   if (rows > max_rows) rows = max_rows;
@@ -263,7 +266,12 @@ __global__ void __launch_bounds__(128) nvfp4_token_kernel(const uint4* __restric
       const uint8_t byte = nvfp4_block_scale(bmax, row_scale, mult);
       if (v < vec_per_row) {
         *reinterpret_cast<uint32_t*>(q + r * q_stride + v * 4) = e2m1x8(f, mult);
-        if ((v & 1) == 0) s[r * s_stride + (v >> 1)] = byte;
+        if ((v & 1) == 0) {
+          if (blocked_atoms > 0)
+            s[blocked_offset(r, v >> 1, blocked_atoms)] = byte;
+          else
+            s[r * s_stride + (v >> 1)] = byte;
+        }
       }
     }
   }
@@ -320,6 +328,45 @@ __global__ void sf_swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __re
   }
 }
 
+// Packed dispatch rows [q | natural scales | fp32 inverse scale | pad] fetched through a pointer table
+// (sources may be peer memory) and unpacked into GEMM operand form: dense q rows, blocked scales,
+// per-row inverse scales.  A null pointer yields a zero row.
+__global__ void __launch_bounds__(256) gather_packed_kernel(const int64_t* __restrict__ ptrs,
+                                                            const int32_t* __restrict__ num_rows, int64_t max_rows,
+                                                            int q_vecs, int scale_cols, int has_inv, uint8_t* q_base,
+                                                            const int64_t* q_off, uint8_t* sf_base,
+                                                            const int64_t* sf_off, uint8_t* inv_base,
+                                                            const int64_t* inv_off, const int* cond) {
+  if (cond != nullptr && *cond == 0) return;
+  int64_t rows = *num_rows;
+  if (rows > max_rows) rows = max_rows;
+  uint4* q = reinterpret_cast<uint4*>(q_base + (q_off ? *q_off : 0));
+  uint8_t* sf = sf_base + (sf_off ? *sf_off : 0);
+  float* inv = has_inv ? reinterpret_cast<float*>(inv_base + (inv_off ? *inv_off : 0)) : nullptr;
+  const int atoms = (scale_cols + 3) / 4;
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int64_t r = blockIdx.x * static_cast<int64_t>(wpb) + (threadIdx.x >> 5); r < rows;
+       r += static_cast<int64_t>(gridDim.x) * wpb) {
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(ptrs[r]);
+    for (int v = lane; v < q_vecs; v += 32)
+      q[r * q_vecs + v] = src ? __ldcg(reinterpret_cast<const uint4*>(src) + v) : make_uint4(0, 0, 0, 0);
+    const uint8_t* ssrc = src ? src + static_cast<int64_t>(q_vecs) * 16 : nullptr;
+    for (int c4 = lane; c4 < atoms; c4 += 32) {
+      uint32_t w = 0;
+      if (ssrc) {
+        if (c4 * 4 + 4 <= scale_cols) {
+          w = __ldcg(reinterpret_cast<const uint32_t*>(ssrc) + c4);
+        } else {
+          for (int j = 0; c4 * 4 + j < scale_cols; ++j) w |= static_cast<uint32_t>(ssrc[c4 * 4 + j]) << (8 * j);
+        }
+      }
+      *reinterpret_cast<uint32_t*>(sf + blocked_offset(r, c4 * 4, atoms)) = w;
+    }
+    if (inv != nullptr && lane == 0)
+      inv[r] = src ? __ldcg(reinterpret_cast<const float*>(ssrc + scale_cols)) : 0.f;
+  }
+}
+
 static int blocks_for(int64_t items, int threads, int cap) {
   int64_t b = (items + threads - 1) / threads;
   if (b > cap) b = cap;
@@ -331,14 +378,18 @@ static int blocks_for(int64_t items, int threads, int cap) {
 using namespace dm;
 
 extern "C" int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
-                                  void* scales, int blocked, void* stream) {
+                                  int64_t q_row_stride, void* scales, int64_t scale_row_stride, int blocked,
+                                  void* stream) {
   if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 32) != 0) return kRcBadArg;
+  if (q_row_stride == 0) q_row_stride = C;
+  if (scale_row_stride == 0) scale_row_stride = C / 32;
+  if ((q_row_stride % 8) != 0) return kRcBadArg;
   if (max_rows == 0) return kRcOk;
   const int vec = static_cast<int>(C / 8);
   const int atoms = static_cast<int>((C / 32 + 3) / 4);
   mxfp8_row_kernel<<<blocks_for(max_rows * vec, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x), num_rows, max_rows, vec, static_cast<uint2*>(q), static_cast<uint8_t*>(scales),
-      blocked, atoms);
+      static_cast<const uint4*>(x), num_rows, max_rows, vec, static_cast<uint8_t*>(q), q_row_stride,
+      static_cast<uint8_t*>(scales), scale_row_stride, blocked, atoms);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -367,15 +418,15 @@ extern "C" int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, 
 }
 
 extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
-                                    int64_t q_row_stride, void* scales, int64_t scale_row_stride, void* scale_inv,
-                                    int64_t inv_row_stride, void* stream) {
+                                    int64_t q_row_stride, void* scales, int64_t scale_row_stride, int scales_blocked,
+                                    void* scale_inv, int64_t inv_row_stride, void* stream) {
   if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 16) != 0 || (q_row_stride % 4) != 0) return kRcBadArg;
   if (scale_inv && (inv_row_stride % 4) != 0) return kRcBadArg;
   if (max_rows == 0) return kRcOk;
   nvfp4_token_kernel<<<blocks_for(max_rows, 1, 148 * 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C / 8), static_cast<uint8_t*>(q),
       q_row_stride, static_cast<uint8_t*>(scales), scale_row_stride, static_cast<uint8_t*>(scale_inv),
-      inv_row_stride);
+      inv_row_stride, scales_blocked ? static_cast<int>((C / 16 + 3) / 4) : 0);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -396,5 +447,20 @@ extern "C" int dm_sf_swizzle(const void* natural, void* blocked_out, int64_t row
   sf_swizzle_kernel<<<blocks_for(padded_rows * atoms * 4, 256, 148 * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(natural), static_cast<uint8_t*>(blocked_out), rows, static_cast<int>(cols),
       padded_rows, atoms);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_gather_packed_rows(const int64_t* ptrs, const int32_t* num_rows, int64_t max_rows, int64_t q_bytes,
+                                     int64_t scale_cols, int has_inv, dm_operand q, dm_operand scales_blocked,
+                                     dm_operand scale_inv, const int* cond, void* stream) {
+  if (!ptrs || !num_rows || !q.base || !scales_blocked.base || q_bytes <= 0 || (q_bytes % 16) != 0 || scale_cols <= 0 ||
+      (scale_cols % 4) != 0 || max_rows < 0)
+    return kRcBadArg;
+  if (has_inv && !scale_inv.base) return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  gather_packed_kernel<<<blocks_for(max_rows * 32, 256, 148 * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ptrs, num_rows, max_rows, static_cast<int>(q_bytes / 16), static_cast<int>(scale_cols), has_inv,
+      static_cast<uint8_t*>(q.base), q.offset, static_cast<uint8_t*>(scales_blocked.base), scales_blocked.offset,
+      static_cast<uint8_t*>(scale_inv.base), scale_inv.offset, cond);
   return static_cast<int>(cudaGetLastError());
 }

@@ -277,7 +277,8 @@ int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, int scores_
  * Inputs are bf16, row-major.  Scale bytes are written in natural row-major order or, with
  * blocked != 0, in 128x4 atoms: atom*512 + (row%32)*16 + (row/32%4)*4 + col%4, atoms ordered
  * (row atom, column atom), rows padded to 128 and scale columns to 4.
- *   dm_quant_mxfp8_row    1x32 blocks along C: q[R,C] e4m3, scales [R, C/32] e8m0.
+ *   dm_quant_mxfp8_row    1x32 blocks along C: q[R,C] e4m3, scales [R, C/32] e8m0; row strides in bytes
+ *                         (0 = dense) let it fill the packed inference dispatch row [q | scales | pad].
  *   dm_quant_mxfp8_col    32x1 blocks along the rows: q[R,C], scales [C, ceil(max_rows/32)].
  *   dm_quant_mxfp8_tile32 32x32 tiles of W[experts*N, K]: shared q, row_scales [experts*N, K/32]
  *                         and (optional) col_scales [experts*K, N/32]; blocked groups are per expert.
@@ -287,20 +288,27 @@ int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, int scores_
  *                         (dist_moe/_blockscaled.py:408-507) and dense outputs use the same kernel.
  *   dm_quant_nvfp4_weight per-expert NVFP4 with a given fp32 global scale per expert.
  *   dm_sf_swizzle         natural scale bytes -> blocked atoms.
+ *   dm_gather_packed_rows rows [q | natural scales | fp32 inverse scale] fetched through a pointer table
+ *                         (peer memory allowed; the gather half of the block-scaled dispatch,
+ *                         dist_moe/kernels/dispatch_quant.py:1437-1560) and unpacked into dense q rows,
+ *                         blocked scales and a per-row inverse-scale vector; null pointers give zero rows.
  * num_rows (device int32, may be NULL) bounds the rows that are processed.
  * ------------------------------------------------------------------------- */
-int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q, void* scales,
-                       int blocked, void* stream);
+int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+                       int64_t q_row_stride, void* scales, int64_t scale_row_stride, int blocked, void* stream);
 int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q, void* scales,
                        int blocked, void* stream);
 int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
                           void* col_scales, int blocked, void* stream);
 int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
-                         int64_t q_row_stride, void* scales, int64_t scale_row_stride, void* scale_inv,
-                         int64_t inv_row_stride, void* stream);
+                         int64_t q_row_stride, void* scales, int64_t scale_row_stride, int scales_blocked,
+                         void* scale_inv, int64_t inv_row_stride, void* stream);
 int dm_quant_nvfp4_weight(const void* w, const float* global_scale, int64_t experts, int64_t N, int64_t K, void* q,
                           void* scales, int blocked, void* stream);
 int dm_sf_swizzle(const void* natural, void* blocked_out, int64_t rows, int64_t cols, void* stream);
+int dm_gather_packed_rows(const int64_t* ptrs, const int32_t* num_rows, int64_t max_rows, int64_t q_bytes,
+                          int64_t scale_cols, int has_inv, dm_operand q, dm_operand scales_blocked,
+                          dm_operand scale_inv, const int* cond, void* stream);
 
 #ifdef __cplusplus
 }

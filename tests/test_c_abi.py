@@ -24,7 +24,7 @@ def test_argument_errors_do_not_need_a_gpu():
 
     assert _native.lib.dm_route_workspace_words(4096, 8, 64) == 2 * 8 * 16 * 8 + 64
     assert _native.lib.dm_publish(None, None, 0, None, None, 0, 0, 0, 0, 0, None, None) == -1
-    assert _native.lib.dm_quant_mxfp8_row(None, None, 1, 32, None, None, 0, None) == -1
+    assert _native.lib.dm_quant_mxfp8_row(None, None, 1, 32, None, 0, None, 0, 0, None) == -1
 
 
 def test_product_package_does_not_import_the_oracle():

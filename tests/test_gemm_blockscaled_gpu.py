@@ -35,14 +35,14 @@ def _quant_act(nat, x, fmt):
         q = torch.zeros(R + 256, K, dtype=torch.uint8, device=DEV)
         atoms = (K // 32 + 3) // 4
         s = torch.zeros((R + 127) // 128 * 128 * atoms * 4, dtype=torch.uint8, device=DEV)
-        nat.check(nat.lib.dm_quant_mxfp8_row(x.data_ptr(), None, R, K, q.data_ptr(), s.data_ptr(), 1, nat.stream_ptr()), "q")
+        nat.check(nat.lib.dm_quant_mxfp8_row(x.data_ptr(), None, R, K, q.data_ptr(), 0, s.data_ptr(), 0, 1, nat.stream_ptr()), "q")
         qn, sn = Q.mxfp8_row(x.cpu())
         deq = torch.from_numpy(Q.mxfp8_dequant_row(qn, sn).reshape(R, K).astype(np.float32))
         return q, s, deq, None
     q = torch.zeros(R + 256, K // 2, dtype=torch.uint8, device=DEV)
     nat_s = torch.zeros(R, K // 16, dtype=torch.uint8, device=DEV)
     inv = torch.zeros(R, dtype=torch.float32, device=DEV)
-    nat.check(nat.lib.dm_quant_nvfp4_token(x.data_ptr(), None, R, K, q.data_ptr(), K // 2, nat_s.data_ptr(), K // 16,
+    nat.check(nat.lib.dm_quant_nvfp4_token(x.data_ptr(), None, R, K, q.data_ptr(), K // 2, nat_s.data_ptr(), K // 16, 0,
                                            inv.data_ptr(), 4, nat.stream_ptr()), "q")
     atoms = (K // 16 + 3) // 4
     s = torch.zeros((R + 127) // 128 * 128 * atoms * 4, dtype=torch.uint8, device=DEV)
@@ -61,8 +61,8 @@ def _quant_w(nat, w, fmt):
         s = torch.zeros(E * ((N + 127) // 128 * 128) * atoms * 4, dtype=torch.uint8, device=DEV)
         for e in range(E):  # row mode per expert so that every expert is its own blocked group
             grp = (N + 127) // 128 * 128 * atoms * 4
-            nat.check(nat.lib.dm_quant_mxfp8_row(w[e].data_ptr(), None, N, K, q[e * N:].data_ptr(),
-                                                 s[e * grp:].data_ptr(), 1, nat.stream_ptr()), "qw")
+            nat.check(nat.lib.dm_quant_mxfp8_row(w[e].data_ptr(), None, N, K, q[e * N:].data_ptr(), 0,
+                                                 s[e * grp:].data_ptr(), 0, 1, nat.stream_ptr()), "qw")
         qn, sn = Q.mxfp8_row(w.reshape(E * N, K).cpu())
         deq = torch.from_numpy(Q.mxfp8_dequant_row(qn, sn).reshape(E, N, K).astype(np.float32))
         return q, s, deq, None

@@ -42,7 +42,7 @@ def test_mxfp8_row(rows, cols, blocked):
     n_s = ((rows + 127) // 128 * 128) * atoms * 4 if blocked else rows * sc
     s = torch.full((n_s,), 0xEE, dtype=torch.uint8, device=DEV)
     cnt = torch.tensor([rows], dtype=torch.int32, device=DEV)
-    nat.check(nat.lib.dm_quant_mxfp8_row(xd.data_ptr(), cnt.data_ptr(), rows, cols, q.data_ptr(), s.data_ptr(), blocked,
+    nat.check(nat.lib.dm_quant_mxfp8_row(xd.data_ptr(), cnt.data_ptr(), rows, cols, q.data_ptr(), 0, s.data_ptr(), 0, blocked,
                                          nat.stream_ptr()), "mxfp8_row")
     torch.cuda.synchronize()
     rq, rs = Q.mxfp8_row(x)
@@ -115,7 +115,7 @@ def test_nvfp4_token_dense_and_packed_rows(rows, cols):
     s = torch.zeros(rows, cols // 16, dtype=torch.uint8, device=DEV)
     inv = torch.zeros(rows, dtype=torch.float32, device=DEV)
     nat.check(nat.lib.dm_quant_nvfp4_token(xd.data_ptr(), None, rows, cols, q.data_ptr(), cols // 2, s.data_ptr(),
-                                           cols // 16, inv.data_ptr(), 4, nat.stream_ptr()), "nvfp4_token")
+                                           cols // 16, 0, inv.data_ptr(), 4, nat.stream_ptr()), "nvfp4_token")
     torch.cuda.synchronize()
     np.testing.assert_array_equal(inv.cpu().numpy().view(np.uint32), rinv.view(np.uint32))
     np.testing.assert_array_equal(s.cpu().numpy(), rs)
@@ -124,7 +124,7 @@ def test_nvfp4_token_dense_and_packed_rows(rows, cols):
     stride = (cols // 2 + cols // 16 + 4 + 15) // 16 * 16
     packed = torch.zeros(rows, stride, dtype=torch.uint8, device=DEV)
     base = packed.data_ptr()
-    nat.check(nat.lib.dm_quant_nvfp4_token(xd.data_ptr(), None, rows, cols, base, stride, base + cols // 2, stride,
+    nat.check(nat.lib.dm_quant_nvfp4_token(xd.data_ptr(), None, rows, cols, base, stride, base + cols // 2, stride, 0,
                                            base + cols // 2 + cols // 16, stride, nat.stream_ptr()), "nvfp4_token")
     torch.cuda.synchronize()
     p = packed.cpu().numpy()

@@ -1,12 +1,12 @@
 // Persistent grouped BF16 GEMMs on tcgen05 tensor cores (sm_100a).
 //
-// One CTA per SM, 192 threads, warp-specialised:
+// One CTA per SM, 320 threads, warp-specialised:
 //   warp 0      TMA producer: fills a 4-stage shared-memory ring (A 128x64, B 256x64 bf16,
 //               128-byte swizzle) with cp.async.bulk.tensor loads, no multicast.
 //   warp 1      MMA issuer: owns the TMEM allocation (512 columns = two 128x256 fp32
 //               accumulators), issues tcgen05.mma (M128 N256 K16) from one lane and
 //               releases stages / publishes accumulators with tcgen05.commit.
-//   warps 2..5  epilogue: tcgen05.ld their 32 TMEM lanes, convert and store (plain rows,
+//   warps 2..9  epilogue (two per TMEM lane quadrant): tcgen05.ld their 32 TMEM lanes, convert and store (plain rows,
 //               fused SwiGLU, per-row scatter to peer memory, or weight-gradient
 //               read-modify-write) while the next tile's main loop already runs.
 //
@@ -29,13 +29,13 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int kMaxGroups = 256;
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 4 * kStagingBytes + 1024;  // + slack for 1024-byte alignment
+constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 8 * kStaging64Bytes + 1024;  // + slack for 1024-byte alignment
 
 enum GemmMode : int { kFprop = 0, kDgrad = 1, kWgrad = 2 };
 
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 4);
+      mbar_init(&tmem_empty_bar[b], 8);
     }
     mbar_fence_init();
   }
@@ -287,13 +287,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     }
   } else {
     // ======================= epilogue =======================
-    // Each warp owns 32 accumulator rows.  A lane reads its own row from TMEM, the warp
-    // transposes 128-byte row segments through a private 4 KiB staging tile (16-byte chunks
-    // XOR-swizzled by row so that both directions are bank-conflict free) and then stores
-    // whole 128-byte segments: 8 lanes per row, 4 rows per instruction.
-    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32)
+    // Eight warps: two per TMEM lane quadrant, each owning half of the tile's columns.  A lane reads
+    // its own accumulator row from TMEM 32 columns at a time; the warp transposes the 32x32 block
+    // through a private staging tile (32 rows x 64 bytes, 16-byte chunks XOR-swizzled so that both
+    // directions are bank-conflict free) and stores 64-byte row segments: 4 lanes per row, 8 rows
+    // per instruction.
+    const int ew = warp - 2;            // 0..7
+    const int quad = warp & 3;          // TMEM lanes [32*quad, 32*quad+32)
+    const int half = ew >> 2;           // column half of the tile
     const int row_in_tile = quad * 32 + lane;
-    uint8_t* stg = smem + kStages * kStageBytes + (warp - 2) * kStagingBytes;
+    uint8_t* stg = smem + kStages * kStageBytes + ew * kStaging64Bytes;
     int e = 0;
     int it = 0;
     bool ok = true;
@@ -314,60 +317,51 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kd;
         const uint64_t my_row =
             out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
-        if (p.out_fp32) {
-          for (int c0 = 0; c0 < kBN; c0 += 32) {
-            uint32_t r[32];
-            if (t.k_iters > 0) {
-              tmem_ld_32x32(taddr + c0, r);
-              tmem_ld_wait();
-            } else {
+        for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
+          uint32_t r[32];
+          if (t.k_iters > 0) {
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = 0u;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              stage_put(stg, lane, j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
-            __syncwarp();
-            const int col = t.n_blk * kBN + c0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + (lane >> 3), j = lane & 7;
-              uint4 v = stage_get(stg, rr, j);
-              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-              if (rp != 0 && col + 4 * j + 4 <= p.Kd) {
-                const uint64_t dst = rp + static_cast<uint64_t>(col + 4 * j) * 4;
-                if (p.accumulate)
-                  red_add_f32x4(dst, v);
-                else
-                  *reinterpret_cast<uint4*>(dst) = v;
-              }
-            }
-            __syncwarp();
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
-        } else {
-          for (int c0 = 0; c0 < kBN; c0 += 64) {
-            uint32_t r0[32], r1[32];
-            if (t.k_iters > 0) {
-              tmem_ld_32x32(taddr + c0, r0);
-              tmem_ld_32x32(taddr + c0 + 32, r1);
-              tmem_ld_wait();
-            } else {
+          const int col = t.n_blk * kBN + c0;
+          if (p.out_fp32) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+            for (int sub = 0; sub < 2; ++sub) {  // 16 fp32 columns = 64 bytes per row
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                stage64_put(stg, lane, j,
+                            make_uint4(r[16 * sub + 4 * j], r[16 * sub + 4 * j + 1], r[16 * sub + 4 * j + 2],
+                                       r[16 * sub + 4 * j + 3]));
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = i * 8 + (lane >> 2), j = lane & 3;
+                const uint4 v = stage64_get(stg, rr, j);
+                const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+                const int cc = col + 16 * sub + 4 * j;
+                if (rp != 0 && cc + 4 <= p.Kd) {
+                  const uint64_t dst = rp + static_cast<uint64_t>(cc) * 4;
+                  if (p.accumulate)
+                    red_add_f32x4(dst, v);
+                  else
+                    *reinterpret_cast<uint4*>(dst) = v;
+                }
+              }
+              __syncwarp();
             }
-            const int col = t.n_blk * kBN + c0;
+          } else {
             // Accumulation rounds the fp32 accumulator to bf16 and lets L2 add it to the stored
             // gradient (a 16-byte reduction per lane): no read round trip through the SM.
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              stage_put(stg, lane, j, pack8_bf16(r0 + 8 * j));
-              stage_put(stg, lane, j + 4, pack8_bf16(r1 + 8 * j));
-            }
+            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
             __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + (lane >> 3), j = lane & 7;
-              const uint4 v = stage_get(stg, rr, j);
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), j = lane & 3;
+              const uint4 v = stage64_get(stg, rr, j);
               const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
               if (rp != 0 && col + 8 * j + 8 <= p.Kd) {
                 const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
@@ -394,43 +388,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           const int F = p.N / 2;
           const uint64_t my_h2 =
               row_ok ? reinterpret_cast<uint64_t>(p.h2_base) + h2_off + static_cast<uint64_t>(row) * F * 2 : 0ull;
-          for (int c0 = 0; c0 < kBN / 2; c0 += 64) {
-            uint4 gp[8], up[8], zp[8];
+          for (int c0 = half * (kBN / 4); c0 < (half + 1) * (kBN / 4); c0 += 32) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(taddr + c0, g);
+            tmem_ld_32x32(taddr + kBN / 2 + c0, u);
+            tmem_ld_wait();
+            uint4 gp[4], up[4], zp[4];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              uint32_t g[32], u[32];
-              tmem_ld_32x32(taddr + c0 + half * 32, g);
-              tmem_ld_32x32(taddr + kBN / 2 + c0 + half * 32, u);
-              tmem_ld_wait();
+            for (int j = 0; j < 4; ++j) {
+              uint32_t gw[4], uw[4], zw[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint32_t gw[4], uw[4], zw[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  gw[q] = pack_bf16x2(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(g[8 * j + 2 * q + 1]));
-                  uw[q] = pack_bf16x2(__uint_as_float(u[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q + 1]));
-                  const float z0 = swiglu_f32(__uint_as_float(gw[q] << 16), __uint_as_float(uw[q] << 16), p.act);
-                  const float z1 =
-                      swiglu_f32(__uint_as_float(gw[q] & 0xffff0000u), __uint_as_float(uw[q] & 0xffff0000u), p.act);
-                  zw[q] = pack_bf16x2(z0, z1);
-                }
-                gp[half * 4 + j] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
-                up[half * 4 + j] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
-                zp[half * 4 + j] = make_uint4(zw[0], zw[1], zw[2], zw[3]);
+              for (int q = 0; q < 4; ++q) {
+                gw[q] = pack_bf16x2(__uint_as_float(g[8 * j + 2 * q]), __uint_as_float(g[8 * j + 2 * q + 1]));
+                uw[q] = pack_bf16x2(__uint_as_float(u[8 * j + 2 * q]), __uint_as_float(u[8 * j + 2 * q + 1]));
+                const float z0 = swiglu_f32(__uint_as_float(gw[q] << 16), __uint_as_float(uw[q] << 16), p.act);
+                const float z1 =
+                    swiglu_f32(__uint_as_float(gw[q] & 0xffff0000u), __uint_as_float(uw[q] & 0xffff0000u), p.act);
+                zw[q] = pack_bf16x2(z0, z1);
               }
+              gp[j] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+              up[j] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+              zp[j] = make_uint4(zw[0], zw[1], zw[2], zw[3]);
             }
             const int col = t.n_blk * (kBN / 2) + c0;  // column inside the gate (and up) half
 #pragma unroll
             for (int which = 0; which < 3; ++which) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) stage_put(stg, lane, j, which == 0 ? gp[j] : (which == 1 ? up[j] : zp[j]));
+              for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, which == 0 ? gp[j] : (which == 1 ? up[j] : zp[j]));
               __syncwarp();
               const uint64_t base = which == 2 ? my_h2 : my_row;
               const int col_out = which == 1 ? F + col : col;
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int rr = i * 4 + (lane >> 3), j = lane & 7;
-                const uint4 v = stage_get(stg, rr, j);
+              for (int i = 0; i < 4; ++i) {
+                const int rr = i * 8 + (lane >> 2), j = lane & 3;
+                const uint4 v = stage64_get(stg, rr, j);
                 const uint64_t rp = __shfl_sync(0xffffffffu, base, rr);
                 if (rp != 0 && col + 8 * j + 8 <= F)
                   *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col_out + 8 * j) * 2) = v;
@@ -439,22 +430,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             }
           }
         } else {
-          for (int c0 = 0; c0 < kBN; c0 += 64) {
-            uint32_t r0[32], r1[32];
-            tmem_ld_32x32(taddr + c0, r0);
-            tmem_ld_32x32(taddr + c0 + 32, r1);
+          for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              stage_put(stg, lane, j, pack8_bf16(r0 + 8 * j));
-              stage_put(stg, lane, j + 4, pack8_bf16(r1 + 8 * j));
-            }
+            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
             __syncwarp();
             const int col = t.n_blk * kBN + c0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + (lane >> 3), j = lane & 7;
-              const uint4 v = stage_get(stg, rr, j);
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), j = lane & 3;
+              const uint4 v = stage64_get(stg, rr, j);
               const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
               if (rp != 0 && col + 8 * j + 8 <= p.N)
                 *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;

@@ -9,7 +9,8 @@
 
 namespace dm {
 
-constexpr uint32_t kStagingBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
+constexpr uint32_t kStagingBytes = 32 * 128;   // per epilogue warp: 32 rows x 128 bytes
+constexpr uint32_t kStaging64Bytes = 32 * 64;  // per epilogue warp: 32 rows x 64 bytes
 
 // Staging tile of one epilogue warp: row r is 128 bytes, its 16-byte chunk j sits at j ^ (r & 7).
 __device__ __forceinline__ void stage_put(uint8_t* stg, int row, int chunk, uint4 v) {
@@ -17,6 +18,13 @@ __device__ __forceinline__ void stage_put(uint8_t* stg, int row, int chunk, uint
 }
 __device__ __forceinline__ uint4 stage_get(const uint8_t* stg, int row, int chunk) {
   return reinterpret_cast<const uint4*>(stg + row * 128)[chunk ^ (row & 7)];
+}
+// 64-byte variant: row r is 64 bytes, its 16-byte chunk j sits at j ^ ((r >> 1) & 3).
+__device__ __forceinline__ void stage64_put(uint8_t* stg, int row, int chunk, uint4 v) {
+  reinterpret_cast<uint4*>(stg + row * 64)[chunk ^ ((row >> 1) & 3)] = v;
+}
+__device__ __forceinline__ uint4 stage64_get(const uint8_t* stg, int row, int chunk) {
+  return reinterpret_cast<const uint4*>(stg + row * 64)[chunk ^ ((row >> 1) & 3)];
 }
 __device__ __forceinline__ uint4 pack8_bf16(const uint32_t* r) {
   return make_uint4(pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),

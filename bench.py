@@ -31,7 +31,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 T, D, F, E, K = 4096, 2048, 1408, 64, 6
-CPU_SAMPLE_TOKENS = 256
+CPU_SAMPLE_TOKENS = int(os.environ.get("DIST_MOE_BENCH_CPU_TOKENS", "256"))  # bounded CPU sample
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 

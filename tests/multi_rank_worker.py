@@ -70,6 +70,34 @@ def run_case(dm, group, rank, world, dev, T, D, F, K, E, quickstart, slot_factor
         ctx.close()
 
 
+def run_block_scaled_case(dm, group, rank, world, dev, fmt, T, D, F, K, E):
+    """Inference forward with prepared block-scaled weights across ranks (packed dispatch rows travel over
+    NVLink); bounds are the reference's relative-L2 / cosine limits for the format."""
+    xs, ids, scores, w13, w2 = inputs(world, T, D, F, K, E, False)
+    xs = [(x.float() * 0.1).bfloat16() for x in xs]
+    el = E // world
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0,
+                    device_scratch_capacity_factor=float(world),
+                    block_scaled=dm.BlockScaledConfig(format=getattr(dm.BlockScaledFormat, fmt)))
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    try:
+        p13 = dm.prepare_block_scaled_weight(w13[rank * el:(rank + 1) * el].contiguous().to(dev), cfg, fuse_swiglu=True,
+                                             inference=True)
+        p2 = dm.prepare_block_scaled_weight(w2[rank * el:(rank + 1) * el].contiguous().to(dev), cfg, inference=True)
+        ref = oracle_moe.moe_forward(xs[rank], ids[rank], scores[rank], w13, w2).float()
+        for _ in range(2):
+            out = dm.routed_experts(xs[rank].to(dev), ids[rank].to(dev), scores[rank].to(dev), p13, p2, ctx)
+            ctx.check_status()
+            got = out.float().cpu()
+            l2 = ((got - ref).norm() / ref.norm()).item()
+            cos = torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item()
+            bound = (0.075, 0.9975) if fmt == "MXFP8_E4M3" else (0.29, 0.955)
+            assert l2 < bound[0] and cos > bound[1], (fmt, rank, l2, cos)
+    finally:
+        ctx.close()
+
+
 def main():
     import dist_moe_b200 as dm
 
@@ -81,6 +109,8 @@ def main():
     run_case(dm, group, rank, world, dev, 16, 256, 256, 2, 4 * world, True, None)    # quick-start layer, recompute
     run_case(dm, group, rank, world, dev, 128, 1024, 1024, 2, 2 * world, False, 1.0)  # reference's two-rank shape, saved
     run_case(dm, group, rank, world, dev, 300, 512, 384, 4, 8 * world, False, 1.0)
+    run_block_scaled_case(dm, group, rank, world, dev, "MXFP8_E4M3", 200, 512, 256, 4, 4 * world)
+    run_block_scaled_case(dm, group, rank, world, dev, "NVFP4", 130, 512, 256, 2, 4 * world)
     dist.barrier()
     if rank == 0:
         print("MULTI_RANK_OK", world, flush=True)

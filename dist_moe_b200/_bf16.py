@@ -45,7 +45,28 @@ def _profiled(fn):
 
 _gemm_fprop = _profiled(nat.lib.dm_gemm_fprop)
 _gemm_dgrad = _profiled(nat.lib.dm_gemm_dgrad)
+_gemm_fprop_dispatch = _profiled(nat.lib.dm_gemm_fprop_dispatch)
+_gemm_dgrad_dispatch = _profiled(nat.lib.dm_gemm_dgrad_dispatch)
 _gemm_wgrad = _profiled(nat.lib.dm_gemm_wgrad)
+
+
+# Fused dispatch pulls the routed rows inside the W13 / W2-dgrad GEMM launches (gather warps overlap the peer
+# transfer with the tensor cores).  With False the rows are gathered by a separate kernel first.
+FUSED_DISPATCH = True
+
+
+def _dispatch_fprop(state, ptrs, a_op_off, w, c_op, h2_op, c, N, Kd, fuse, act, condp, what):
+    clamped, alpha, limit = act
+    st, status = nat.stream_ptr(), state.status.data_ptr()
+    if FUSED_DISPATCH:
+        _gemm_fprop_dispatch(ptrs.data_ptr(), state.gather_flags.data_ptr(), _op(state, a_op_off), w.data_ptr(), c_op,
+                             h2_op, c.offsets.data_ptr(), state.e_local, c.max_rows, N, Kd, int(fuse), clamped, alpha,
+                             limit, condp, state.num_sms, status, st, what=what)
+        return
+    nat.check(nat.lib.dm_gather_rows(ptrs.data_ptr(), c.recv_rows.data_ptr(), state.arena.data_ptr(),
+                                     a_op_off.data_ptr(), Kd * 2, c.max_rows, condp, st), "dm_gather_rows")
+    _gemm_fprop(_op(state, a_op_off), w.data_ptr(), c_op, h2_op, None, c.offsets.data_ptr(), state.e_local,
+                c.max_rows, N, Kd, int(fuse), clamped, alpha, limit, condp, state.num_sms, status, st, what=what)
 
 
 class _Call:
@@ -116,12 +137,9 @@ def _expert_forward(state, c: _Call, w13, w2, xg_off, h1_off, h2_off, *, fuse: b
     st, status = nat.stream_ptr(), state.status.data_ptr()
     clamped, alpha, limit = _act(cfg)
     condp = nat.ptr(cond)
-    nat.check(nat.lib.dm_gather_rows(c.fwd.data_ptr(), c.recv_rows.data_ptr(), state.arena.data_ptr(),
-                                     xg_off.data_ptr(), D * 2, c.max_rows, condp, st), "dm_gather_rows")
-    _gemm_fprop(_op(state, xg_off), w13.data_ptr(), _op(state, h1_off),
-                                    _op(state, h2_off) if fuse else _none(), None, c.offsets.data_ptr(), el,
-                                    c.max_rows, 2 * F, D, int(fuse), clamped, alpha, limit, condp, state.num_sms,
-                                    status, st, what="gemm_fprop(w13)")
+    # dispatch + W13: gather warps pull the routed rows (peer loads) while the tensor cores run
+    _dispatch_fprop(state, c.fwd, xg_off, w13, _op(state, h1_off), _op(state, h2_off) if fuse else _none(), c, 2 * F, D,
+                    fuse, (clamped, alpha, limit), condp, "gemm_fprop_dispatch(w13)")
     if not fuse:
         nat.check(nat.lib.dm_swiglu_fwd(state.arena.data_ptr(), h1_off.data_ptr(), state.arena.data_ptr(),
                                         h2_off.data_ptr(), c.recv_rows.data_ptr(), c.max_rows, F, clamped, alpha,
@@ -206,11 +224,8 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     nat.check(nat.lib.dm_cond_copy(arena, fs[0:1].data_ptr(), state.dispatch.local().data_ptr(), None, T * D * 2,
                                    cond.data_ptr(), 1, st), "dm_cond_copy(republish x)")
     state.barrier(state.dispatch, cond)
-    nat.check(nat.lib.dm_gather_rows(c.fwd.data_ptr(), c.recv_rows.data_ptr(), arena, bo[0:1].data_ptr(), D * 2,
-                                     c.max_rows, cond.data_ptr(), st), "dm_gather_rows(recompute)")
-    _gemm_fprop(_op(state, bo[0:1]), w13.data_ptr(), _op(state, bo[1:2]), _none(), None,
-                                    c.offsets.data_ptr(), el, c.max_rows, 2 * F, D, 0, clamped, alpha, limit,
-                                    cond.data_ptr(), state.num_sms, status, st, what="gemm_fprop(w13 recompute)")
+    _dispatch_fprop(state, c.fwd, bo[0:1], w13, _op(state, bo[1:2]), _none(), c, 2 * F, D, False,
+                    (clamped, alpha, limit), cond.data_ptr(), "gemm_fprop_dispatch(w13 recompute)")
     # h2 is always rebuilt from h1: only x_gathered, h1 and h3 are ever saved.
     nat.check(nat.lib.dm_swiglu_fwd(arena, bo[1:2].data_ptr(), arena, bo[2:3].data_ptr(), c.recv_rows.data_ptr(),
                                     c.max_rows, F, clamped, alpha, limit, None, 0.0, None, st), "dm_swiglu_fwd(bwd)")
@@ -237,10 +252,15 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
                   "dm_broadcast_and_scale")
     state.barrier(state.combine)
     # ---- W2: input gradient and weight gradient ----------------------------------
-    nat.check(nat.lib.dm_gather_rows(c.sct.data_ptr(), c.recv_rows.data_ptr(), arena, bo[4:5].data_ptr(), D * 2,
-                                     c.max_rows, None, st), "dm_gather_rows(grad_h3)")
-    _gemm_dgrad(_op(state, bo[4:5]), w2.data_ptr(), _op(state, bo[3:4]), None,
-                                    c.offsets.data_ptr(), el, c.max_rows, F, D, None, state.num_sms, status, st, what="gemm_dgrad(w2)")
+    if FUSED_DISPATCH:
+        _gemm_dgrad_dispatch(c.sct.data_ptr(), state.gather_flags.data_ptr(), _op(state, bo[4:5]), w2.data_ptr(),
+                             _op(state, bo[3:4]), c.offsets.data_ptr(), el, c.max_rows, F, D, None, state.num_sms,
+                             status, st, what="gemm_dgrad_dispatch(w2)")
+    else:
+        nat.check(nat.lib.dm_gather_rows(c.sct.data_ptr(), c.recv_rows.data_ptr(), arena, bo[4:5].data_ptr(), D * 2,
+                                         c.max_rows, None, st), "dm_gather_rows(grad_h3)")
+        _gemm_dgrad(_op(state, bo[4:5]), w2.data_ptr(), _op(state, bo[3:4]), None, c.offsets.data_ptr(), el,
+                    c.max_rows, F, D, None, state.num_sms, status, st, what="gemm_dgrad(w2)")
     grad_w13 = grad_w2 = None
     owners = options.wgrad_parameter_owners or (None, None)
     if need_w2:

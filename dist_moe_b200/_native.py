@@ -99,6 +99,12 @@ _SIGNATURES = {
         c_int,
         [Operand, _P, Operand, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
+    "dm_gemm_fprop_dispatch": (
+        c_int,
+        [_P, _P, Operand, _P, Operand, Operand, _P, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_float, c_float, _P,
+         c_int, _P, _P],
+    ),
+    "dm_gemm_dgrad_dispatch": (c_int, [_P, _P, Operand, _P, Operand, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P]),
     "dm_gemm_dgrad": (c_int, [Operand, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P]),
     "dm_gemm_wgrad": (c_int, [Operand, Operand, _P, c_int, c_int, _P, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
 }

@@ -93,6 +93,8 @@ class ContextState:
             words = nat.lib.dm_route_workspace_words(T, ep_size, config.num_experts)
             self.route_workspace = torch.zeros(max(1, words), dtype=torch.int32, device=device)
             self.route_workspace_words = words
+            self.gather_flags = torch.zeros(self.capacity_rows // 128 + 8 + ep_size * self.e_local * T // 128,
+                                            dtype=torch.int32, device=device)
             self.reset()
         if config.block_scaled is not None:
             ob, vpe, sb, vec, gs = format_constants(config.block_scaled.format)

@@ -29,7 +29,8 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kStages = 4;
-constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, eight epilogue warps
+constexpr int kGemmThreads = 448;  // TMA warp, MMA warp, eight epilogue warps, four gather warps
+constexpr int kGatherWarps = 4;
 constexpr int kMaxGroups = 256;
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KiB
@@ -49,6 +50,9 @@ struct GemmParams {
   uint8_t* c_base;
   uint8_t* h2_base;
   const int64_t* scatter_ptrs;
+  const int64_t* gather_ptrs;  // fused dispatch: row r of A is pulled from gather_ptrs[r] (may be peer memory)
+  int* gather_flags;           // one counter per 128-row block of A, zero before the launch
+  uint8_t* a_base;             // where the pulled rows land (the A operand itself)
   const int32_t* expert_offsets;
   const int* cond;
   int* status;
@@ -165,8 +169,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     const int a_line0 = static_cast<int>(a_off >> 7);
     const int b_line0 = static_cast<int>(b_off >> 7);
     bool ok = true;
+    int ready_blocks = 0;  // row blocks [0, ready_blocks) are known to have landed
+    const int total_rows = s_off[p.e_local];
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
+      if (kMode != kWgrad && p.gather_flags != nullptr && lane == 0) {
+        // Rows of this tile are pulled by the gather warps of some CTA; wait (bounded) for their blocks.
+        int last = (t.row0 + kBM - 1) >> 7;
+        const int nblocks = (total_rows + 127) >> 7;
+        if (last > nblocks - 1) last = nblocks - 1;
+        if (last >= ready_blocks) {
+          const uint64_t t0 = globaltimer_ns();
+          for (int b = ready_blocks > (t.row0 >> 7) ? ready_blocks : (t.row0 >> 7); b <= last && ok; ++b) {
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(p.gather_flags + b) < kGatherWarps) {
+              if ((++spins & 0xff) == 0 && (abort_flag || globaltimer_ns() - t0 > 2000000000ull)) {
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (ok) ready_blocks = last + 1;
+          fence_proxy_async_all();  // rows were written with ordinary stores, TMA reads them through the async proxy
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
       for (int kb = 0; kb < t.k_iters; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
@@ -284,6 +313,53 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           mbar_arrive(&tmem_full_bar[buf]);
       }
       __syncwarp();
+    }
+  } else if (warp >= 10) {
+    // ======================= gather (fused dispatch) =======================
+    // Row blocks of 128 rows are dealt round-robin to the CTAs in ascending order, the order in which
+    // the tiles consume them.  Each warp pulls 32 rows with 16-byte loads (peer memory allowed) into
+    // the A operand and then bumps the block's counter; the TMA producer of whichever CTA needs the
+    // block waits for the counter to reach the number of gather warps.  Gather warps wait on nothing.
+    if (kMode != kWgrad && p.gather_flags != nullptr) {
+      const int gw = warp - 10;
+      const int total_rows = s_off[p.e_local];
+      const int nblocks = (total_rows + 127) >> 7;
+      const int vec_per_row = p.Kd / 8;
+      uint4* dst_base = reinterpret_cast<uint4*>(p.a_base + a_off);
+      // Units of 32 rows are dealt so that consecutive units go to different SMs: the rows the first
+      // tiles need are pulled by many SMs at once.  Two rows x eight 16-byte loads are in flight per lane.
+      for (int u = gw * gridDim.x + blockIdx.x; u < nblocks * 4; u += kGatherWarps * gridDim.x) {
+        const int blk = u >> 2;
+        const int r_begin = blk * 128 + (u & 3) * 32;
+        for (int rr = 0; rr < 32; rr += 2) {
+          const int r0 = r_begin + rr, r1 = r0 + 1;
+          if (r0 >= total_rows) break;
+          const uint4* src0 = reinterpret_cast<const uint4*>(p.gather_ptrs[r0]);
+          const uint4* src1 = r1 < total_rows ? reinterpret_cast<const uint4*>(p.gather_ptrs[r1]) : nullptr;
+          uint4* dst0 = dst_base + static_cast<int64_t>(r0) * vec_per_row;
+          uint4* dst1 = dst_base + static_cast<int64_t>(r1) * vec_per_row;
+          for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+            uint4 b0[8], b1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int v = v0 + j * 32 + lane;
+              b0[j] = (src0 != nullptr && v < vec_per_row) ? __ldcg(src0 + v) : make_uint4(0, 0, 0, 0);
+              b1[j] = (src1 != nullptr && v < vec_per_row) ? __ldcg(src1 + v) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int v = v0 + j * 32 + lane;
+              if (v < vec_per_row) {
+                dst0[v] = b0[j];
+                if (r1 < total_rows) dst1[v] = b1[j];
+              }
+            }
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) red_release_gpu_add(p.gather_flags + blk, 1);
+      }
     }
   } else {
     // ======================= epilogue =======================
@@ -484,10 +560,21 @@ static int launch(const GemmParams& p, int num_sms, cudaStream_t st) {
 
 using namespace dm;
 
-extern "C" int dm_gemm_fprop(dm_operand a, const void* w, dm_operand c, dm_operand h2, const int64_t* scatter_ptrs,
-                             const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
-                             int fuse_swiglu, int clamped, float alpha, float limit, const int* cond, int num_sms,
-                             int* status, void* stream) {
+static int setup_gather(GemmParams& p, const dm_operand& a, const int64_t* gather_ptrs, int32_t* gather_flags,
+                        int64_t max_rows, cudaStream_t st) {
+  if (gather_ptrs == nullptr) return kRcOk;
+  if (gather_flags == nullptr) return kRcBadArg;
+  p.gather_ptrs = gather_ptrs;
+  p.gather_flags = gather_flags;
+  p.a_base = static_cast<uint8_t*>(a.base);
+  const cudaError_t e = cudaMemsetAsync(gather_flags, 0, sizeof(int32_t) * static_cast<size_t>((max_rows + 127) / 128 + 1), st);
+  return static_cast<int>(e);
+}
+
+static int fprop_impl(dm_operand a, const void* w, dm_operand c, dm_operand h2, const int64_t* scatter_ptrs,
+                      const int64_t* gather_ptrs, int32_t* gather_flags, const int32_t* expert_offsets, int e_local,
+                      int64_t max_rows, int64_t N, int64_t Kd, int fuse_swiglu, int clamped, float alpha, float limit,
+                      const int* cond, int num_sms, int* status, void* stream) {
   if (!a.base || !w || !expert_offsets || e_local <= 0 || max_rows < 0 || N <= 0 || Kd <= 0) return kRcBadArg;
   if (!c.base && !scatter_ptrs) return kRcBadArg;
   if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
@@ -514,12 +601,33 @@ extern "C" int dm_gemm_fprop(dm_operand a, const void* w, dm_operand c, dm_opera
   p.Kd = static_cast<int>(Kd);
   p.fused = fuse_swiglu ? 1 : 0;
   p.act = ActParams{clamped, alpha, limit};
+  rc = setup_gather(p, a, gather_ptrs, gather_flags, max_rows, static_cast<cudaStream_t>(stream));
+  if (rc != kRcOk) return rc;
   return launch<kFprop>(p, num_sms, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int dm_gemm_dgrad(dm_operand a, const void* w, dm_operand c, const int64_t* scatter_ptrs,
+extern "C" int dm_gemm_fprop(dm_operand a, const void* w, dm_operand c, dm_operand h2, const int64_t* scatter_ptrs,
                              const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
-                             const int* cond, int num_sms, int* status, void* stream) {
+                             int fuse_swiglu, int clamped, float alpha, float limit, const int* cond, int num_sms,
+                             int* status, void* stream) {
+  return fprop_impl(a, w, c, h2, scatter_ptrs, nullptr, nullptr, expert_offsets, e_local, max_rows, N, Kd, fuse_swiglu,
+                    clamped, alpha, limit, cond, num_sms, status, stream);
+}
+
+extern "C" int dm_gemm_fprop_dispatch(const int64_t* gather_ptrs, int32_t* gather_flags, dm_operand a, const void* w,
+                                      dm_operand c, dm_operand h2, const int32_t* expert_offsets, int e_local,
+                                      int64_t max_rows, int64_t N, int64_t Kd, int fuse_swiglu, int clamped,
+                                      float alpha, float limit, const int* cond, int num_sms, int* status,
+                                      void* stream) {
+  if (!gather_ptrs || !gather_flags) return kRcBadArg;
+  return fprop_impl(a, w, c, h2, nullptr, gather_ptrs, gather_flags, expert_offsets, e_local, max_rows, N, Kd,
+                    fuse_swiglu, clamped, alpha, limit, cond, num_sms, status, stream);
+}
+
+static int dgrad_impl(dm_operand a, const void* w, dm_operand c, const int64_t* scatter_ptrs,
+                      const int64_t* gather_ptrs, int32_t* gather_flags, const int32_t* expert_offsets, int e_local,
+                      int64_t max_rows, int64_t N, int64_t Kd, const int* cond, int num_sms, int* status,
+                      void* stream) {
   if (!a.base || !w || !expert_offsets || e_local <= 0 || max_rows < 0 || N <= 0 || Kd <= 0) return kRcBadArg;
   if (!c.base && !scatter_ptrs) return kRcBadArg;
   if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
@@ -542,7 +650,24 @@ extern "C" int dm_gemm_dgrad(dm_operand a, const void* w, dm_operand c, const in
   p.max_rows = static_cast<int>(max_rows);
   p.N = static_cast<int>(N);
   p.Kd = static_cast<int>(Kd);
+  rc = setup_gather(p, a, gather_ptrs, gather_flags, max_rows, static_cast<cudaStream_t>(stream));
+  if (rc != kRcOk) return rc;
   return launch<kDgrad>(p, num_sms, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dm_gemm_dgrad(dm_operand a, const void* w, dm_operand c, const int64_t* scatter_ptrs,
+                             const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
+                             const int* cond, int num_sms, int* status, void* stream) {
+  return dgrad_impl(a, w, c, scatter_ptrs, nullptr, nullptr, expert_offsets, e_local, max_rows, N, Kd, cond, num_sms,
+                    status, stream);
+}
+
+extern "C" int dm_gemm_dgrad_dispatch(const int64_t* gather_ptrs, int32_t* gather_flags, dm_operand a, const void* w,
+                                      dm_operand c, const int32_t* expert_offsets, int e_local, int64_t max_rows,
+                                      int64_t N, int64_t Kd, const int* cond, int num_sms, int* status, void* stream) {
+  if (!gather_ptrs || !gather_flags) return kRcBadArg;
+  return dgrad_impl(a, w, c, nullptr, gather_ptrs, gather_flags, expert_offsets, e_local, max_rows, N, Kd, cond,
+                    num_sms, status, stream);
 }
 
 extern "C" int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int accumulate,

@@ -226,6 +226,19 @@ int dm_gemm_fprop(dm_operand a, const void* w, dm_operand c, dm_operand h2, cons
 int dm_gemm_dgrad(dm_operand a, const void* w, dm_operand c, const int64_t* scatter_ptrs,
                   const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
                   int64_t Kd, const int* cond, int num_sms, int* status, void* stream);
+/* Fused dispatch: the same GEMMs, but the rows of A are first pulled through `gather_ptrs` (peer memory
+ * allowed) by four extra warps of every CTA of the persistent kernel while the tensor cores already work
+ * on the rows that have landed; `a` names where the pulled rows are kept (x_gathered / grad_h3_gathered,
+ * needed again by the weight-gradient GEMMs).  gather_flags: int32[max_rows/128 + 2] scratch, cleared by
+ * the call.  Replaces dist_grouped_gemm_fprop_dispatch / ..._dgrad_dispatch in one launch
+ * (dist_moe/kernels/dist_grouped_gemm.py:1148-1237, 1441-1489). */
+int dm_gemm_fprop_dispatch(const int64_t* gather_ptrs, int32_t* gather_flags, dm_operand a, const void* w,
+                           dm_operand c, dm_operand h2, const int32_t* expert_offsets, int e_local, int64_t max_rows,
+                           int64_t N, int64_t Kd, int fuse_swiglu, int clamped, float alpha, float limit,
+                           const int* cond, int num_sms, int* status, void* stream);
+int dm_gemm_dgrad_dispatch(const int64_t* gather_ptrs, int32_t* gather_flags, dm_operand a, const void* w,
+                           dm_operand c, const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
+                           int64_t Kd, const int* cond, int num_sms, int* status, void* stream);
 int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int accumulate,
                   const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
                   int64_t Kd, int num_sms, int* status, void* stream);

@@ -248,3 +248,50 @@ def test_fprop_scatter_rows():
         ref[perm[lo:hi]] = a[lo:hi].float() @ w[ei].float().T
     ref[perm[3]] = 0
     _close(dest, ref, "scatter")
+
+
+@pytest.mark.parametrize("mode", ["fprop", "dgrad"])
+def test_fused_dispatch_gathers_rows_inside_the_gemm(mode):
+    """Rows of A are pulled through a pointer table by the kernel's gather warps (null pointer = zero row);
+    the pulled copy must also be left in the A operand for the later weight-gradient GEMM."""
+    nat = _native()
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(6)
+    counts, kd, n = [300, 0, 45, 500], 256, 512
+    e = len(counts)
+    offs_t, off = _offsets(counts, dev)
+    rows = off[-1]
+    src = torch.randn(2000, kd, device=dev).bfloat16()
+    idx = torch.randint(0, 2000, (rows,), device=dev)
+    ptrs = src.data_ptr() + idx.to(torch.int64) * kd * 2
+    ptrs[17] = 0
+    a_ref = src[idx].clone()
+    a_ref[17] = 0
+    w = (torch.randn(e, n, kd, device=dev) * 0.1).bfloat16() if mode == "fprop" else \
+        (torch.randn(e, kd, n, device=dev) * 0.1).bfloat16()
+    a_buf = torch.full(((rows + 300) * kd,), 9.0, device=dev, dtype=torch.bfloat16)
+    out = torch.zeros(rows, n, device=dev, dtype=torch.bfloat16)
+    flags = torch.full((rows // 128 + 8,), 77, dtype=torch.int32, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    a_op = nat.Operand(a_buf.data_ptr(), a_buf.numel() * 2, None)
+    c_op = nat.Operand(out.data_ptr(), out.numel() * 2, None)
+    none = nat.Operand(None, 0, None)
+    for _ in range(2):
+        if mode == "fprop":
+            rc = nat.lib.dm_gemm_fprop_dispatch(ptrs.data_ptr(), flags.data_ptr(), a_op, w.data_ptr(), c_op, none,
+                                                offs_t.data_ptr(), e, rows, n, kd, 0, 0, 1.0, 0.0, None, 0,
+                                                status.data_ptr(), nat.stream_ptr())
+        else:
+            rc = nat.lib.dm_gemm_dgrad_dispatch(ptrs.data_ptr(), flags.data_ptr(), a_op, w.data_ptr(), c_op,
+                                                offs_t.data_ptr(), e, rows, n, kd, None, 0, status.data_ptr(),
+                                                nat.stream_ptr())
+        nat.check(rc, "dispatch gemm")
+        torch.cuda.synchronize()
+        assert status[0].item() == 0, status.tolist()
+        got_a = a_buf[: rows * kd].view(rows, kd)
+        assert torch.equal(got_a.view(torch.int16), a_ref.view(torch.int16)), "gathered rows differ"
+        for ei in range(e):
+            lo, hi = off[ei], off[ei + 1]
+            if hi > lo:
+                wt = w[ei].float().T if mode == "fprop" else w[ei].float()
+                _close(out[lo:hi], a_ref[lo:hi].float() @ wt, f"{mode} dispatch expert {ei}")

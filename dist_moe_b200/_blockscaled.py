@@ -16,8 +16,19 @@ MXFP8 inference weights 1x32 rows, NVFP4 a per-expert fp32 global scale ``2688 /
 ``fuse_swiglu`` interleaves W13 rows in groups of 8 gate / 8 up rows
 (dist_moe/_blockscaled_weight.py:16-39) so that one 128-row tile holds matching pairs.
 
-The MXFP8 *backward* (block-scaled dgrad/wgrad) is not implemented in this revision:
-``routed_experts`` raises ``NotImplementedError`` when autograd state would be needed.
+MXFP8 training (autograd) follows the reference's staged sequence
+(dist_moe/_blockscaled.py:1309-1931 forward, 1951-2541 backward):
+
+  forward   publish bf16 x -> barrier -> route (128-padded) -> gather bf16 rows -> quantise rows (+ the
+            column-quantised copy the weight gradient needs) -> W13 -> bf16 h1 (saved) -> SwiGLU ->
+            quantise h2 rows + columns -> W2, rows scattered -> barrier -> weighted reduce (+ keep h3)
+  backward  grad_h3 / grad_scores -> barrier -> gather grad_h3 -> quantise rows + columns ->
+            W2 dgrad (same qdata, transposed scales) -> W2 wgrad -> SwiGLU bwd -> quantise ->
+            W13 dgrad scattered to the owners -> W13 wgrad -> barrier -> reduce over top-k
+
+Saved activations of the training path live in per-call torch allocations sized for the row capacity
+(h1 in bf16, x and h2 as column-quantised E4M3); the device planner of the BF16 path is not used here.
+NVFP4 has no backward (dist_moe/_blockscaled.py:245-321).
 """
 
 from __future__ import annotations
@@ -192,15 +203,19 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     state = context._state
     cfg = state.config
     fmt = cfg.block_scaled.format
-    if save_for_backward:
-        raise NotImplementedError(
-            "dist_moe_b200 implements the block-scaled forward only; the MXFP8 backward "
-            "(block-scaled dgrad/wgrad) is not available yet")
     if options.requires_eager:
         raise NotImplementedError("Python callbacks are not supported by dist_moe_b200")
     D, F, K, E = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k, cfg.num_experts
     if D % 128 or F % 128:
         raise ValueError("block-scaled execution needs hidden_dim and intermediate_dim to be multiples of 128")
+    if save_for_backward:
+        if fmt is BlockScaledFormat.NVFP4:
+            raise RuntimeError("NVFP4 is inference-only: it has no backward")
+        prepared = isinstance(w13_weight, PreparedWeight)
+        src13 = w13_weight.source if prepared else w13_weight
+        src2 = w2_weight.source if prepared else w2_weight
+        return _Mxfp8Function.apply(x, ids, scores, src13, src2, state, options,
+                                    w13_weight if prepared else None, w2_weight if prepared else None)
     x, scores = x.detach(), scores.detach()
     T = x.shape[0]
     p13, p2 = _weights_for_call(w13_weight, w2_weight, state, cfg)
@@ -299,3 +314,230 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
                                            st), "dm_scale_and_sum")
     state.last_recv = recv
     return out
+
+
+# =============================================================================================
+# MXFP8 training
+# =============================================================================================
+class _Bump:
+    """Carves 256-byte aligned views out of one cached workspace tensor."""
+
+    def __init__(self, buf: torch.Tensor):
+        self.buf, self.off = buf, 0
+
+    def take(self, nbytes: int) -> nat.Operand:
+        start = self.off
+        self.off = (start + nbytes + 255) // 256 * 256
+        if self.off > self.buf.numel():
+            raise RuntimeError("block-scaled training workspace is too small")
+        return nat.Operand(self.buf.data_ptr() + start, self.buf.numel() - start, None)
+
+
+def _sf_rows_bytes(rows: int, dim: int) -> int:
+    """Blocked scales of a row-quantised [rows, dim] operand."""
+    return _blocked_group_bytes(rows, dim // 32)
+
+
+def _sf_cols_bytes(rows: int, dim: int) -> int:
+    """Blocked scales of a column-quantised [rows, dim] operand (feature = row index, rows/32 = column index)."""
+    return _blocked_group_bytes(dim, (rows + 31) // 32)
+
+
+def _train_workspace(state, R: int) -> torch.Tensor:
+    cfg = state.config
+    D, F = cfg.hidden_dim, cfg.intermediate_dim
+    need = R * (2 * D + D + D + 2 * F + 4 * F + 2 * F + 2 * F) \
+        + _sf_rows_bytes(R, D) + _sf_cols_bytes(R, D) + _sf_rows_bytes(R, 2 * F) + _sf_cols_bytes(R, 2 * F) \
+        + 256 * max(D, 2 * F) * 2 + 16 * 256
+    ws = getattr(state, "_bs_train_ws", None)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=state.device)
+        state._bs_train_ws = ws
+    return ws
+
+
+def _ptr(op: nat.Operand) -> int:
+    return op.base
+
+
+def _training_weights(w13_param, w2_param, p13, p2, cfg):
+    """Training operands: one E4M3 qdata per weight (32x32 tiles) with forward and transposed scales."""
+    if p13 is not None:
+        if p13.dgrad_scale is None or p2.dgrad_scale is None or p13._interleaved_fc13:
+            raise ValueError("training needs weights prepared without inference=True / fuse_swiglu")
+        return p13, p2
+    el = w13_param.numel() // (2 * cfg.intermediate_dim * cfg.hidden_dim)
+    w13 = w13_param.detach().reshape(el, 2 * cfg.intermediate_dim, cfg.hidden_dim)
+    w2 = w2_param.detach().reshape(el, cfg.hidden_dim, cfg.intermediate_dim)
+    return prepare_weight(w13, cfg), prepare_weight(w2, cfg)
+
+
+class _TrainCall:
+    __slots__ = ("T", "R", "offsets", "recv", "fwd", "bwd", "sct", "h1", "x_col", "x_col_sf", "h2_col", "h2_col_sf",
+                 "h3", "p13", "p2")
+
+
+def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
+    cfg = state.config
+    D, F, K, E = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k, cfg.num_experts
+    T, dev, el, ep = x.shape[0], x.device, state.e_local, state.ep
+    st, status = nat.stream_ptr(), state.status.data_ptr()
+    clamped = 1 if cfg.activation == "swiglu_clamped" else 0
+    alpha, limit = float(cfg.swiglu_alpha), float(cfg.swiglu_limit)
+    nat.check(nat.lib.dm_publish(x.data_ptr(), ids.data_ptr(), int(ids.dtype == torch.int64),
+                                 state.dispatch.local().data_ptr(), state.routing.local().data_ptr(), T, D, K, E,
+                                 int(options.validate_expert_ids), status, st), "dm_publish")
+    state.barrier(state.dispatch)
+    size = max((ep * T * min(K, el) + el * 127 + 127) // 128 * 128, 128)
+    c = _TrainCall()
+    c.T, c.p13, c.p2 = T, p13, p2
+    R = c.R = min(size, state.capacity_rows // 128 * 128)
+    counts = torch.empty(el, dtype=torch.int32, device=dev)
+    per_rank = torch.empty(ep, dtype=torch.int32, device=dev)
+    c.offsets = torch.empty(el + 1, dtype=torch.int32, device=dev)
+    c.fwd = torch.empty(size, dtype=torch.int64, device=dev)
+    c.bwd = torch.empty(size, dtype=torch.int64, device=dev)
+    c.sct = torch.empty(size, dtype=torch.int64, device=dev)
+    stride = D * 2
+    nat.check(nat.lib.dm_route(state.routing.peer_ptrs.data_ptr(), state.dispatch.peer_ptrs.data_ptr(),
+                               state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride, stride, 128,
+                               state.capacity_rows, size, counts.data_ptr(), per_rank.data_ptr(), c.offsets.data_ptr(),
+                               c.fwd.data_ptr(), c.bwd.data_ptr(), c.sct.data_ptr(), state.route_workspace.data_ptr(),
+                               state.route_workspace_words, status, st), "dm_route")
+    c.recv = c.offsets[el:]
+    recv = c.recv.data_ptr()
+    ws = _Bump(_train_workspace(state, R))
+    xg = ws.take(R * D * 2)
+    xq, xsf = ws.take(R * D), ws.take(_sf_rows_bytes(R, D))
+    h2 = ws.take(R * F * 2)
+    hq, hsf = ws.take(R * F), ws.take(_sf_rows_bytes(R, F))
+    # saved for the backward
+    c.h1 = torch.empty(R, 2 * F, dtype=torch.bfloat16, device=dev)
+    c.x_col = torch.empty(R, D, dtype=torch.uint8, device=dev)
+    c.x_col_sf = torch.empty(_sf_cols_bytes(R, D), dtype=torch.uint8, device=dev)
+    c.h2_col = torch.empty(R, F, dtype=torch.uint8, device=dev)
+    c.h2_col_sf = torch.empty(_sf_cols_bytes(R, F), dtype=torch.uint8, device=dev)
+    none = nat.Operand(None, 0, None)
+    full = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
+    nat.check(nat.lib.dm_gather_rows(c.fwd.data_ptr(), recv, _ptr(xg), None, D * 2, R, None, st), "dm_gather_rows")
+    nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(xg), recv, R, D, _ptr(xq), 0, _ptr(xsf), 0, 1, st), "dm_quant_mxfp8_row(x)")
+    nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(xg), recv, R, D, c.x_col.data_ptr(), c.x_col_sf.data_ptr(), 1, st),
+              "dm_quant_mxfp8_col(x)")
+    nat.check(nat.lib.dm_gemm_blockscaled(0, xq, xsf, p13.fprop_data.data_ptr(), p13.fprop_scale.data_ptr(), full(c.h1),
+                                          none, None, none, None, c.offsets.data_ptr(), el, R, 2 * F, D, 0, 0, 1.0, 0.0,
+                                          None, state.num_sms, status, st), "dm_gemm_blockscaled(w13)")
+    clip = options.swiglu_clip_stats_out_3
+    if clip is not None:
+        clip.zero_()
+    nat.check(nat.lib.dm_swiglu_fwd(c.h1.data_ptr(), None, _ptr(h2), None, recv, R, F, clamped, alpha, limit,
+                                    nat.ptr(clip), float(options.swiglu_clip_limit), None, st), "dm_swiglu_fwd")
+    nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(h2), recv, R, F, _ptr(hq), 0, _ptr(hsf), 0, 1, st), "dm_quant_mxfp8_row(h2)")
+    nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(h2), recv, R, F, c.h2_col.data_ptr(), c.h2_col_sf.data_ptr(), 1, st),
+              "dm_quant_mxfp8_col(h2)")
+    nat.check(nat.lib.dm_gemm_blockscaled(0, hq, hsf, p2.fprop_data.data_ptr(), p2.fprop_scale.data_ptr(), none, none,
+                                          c.sct.data_ptr(), none, None, c.offsets.data_ptr(), el, R, D, F, 0, 0, 1.0,
+                                          0.0, None, state.num_sms, status, st), "dm_gemm_blockscaled(w2)")
+    state.barrier(state.combine)
+    out = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+    c.h3 = torch.empty(T * K * D, dtype=torch.bfloat16, device=dev) if need_h3 else None
+    if options.experts_output_postprocess is not None:
+        raise NotImplementedError("expert-output postprocessing is not available on the MXFP8 training path")
+    nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
+                                       int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                       int(ids.dtype == torch.int64), out.data_ptr(), T, K, D, nat.ptr(c.h3), None, None,
+                                       0, st), "dm_scale_and_sum")
+    state.last_recv = c.recv
+    return out, c
+
+
+def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_param, grad_out, options, needs):
+    from ._bf16 import _wgrad_destination
+
+    cfg = state.config
+    D, F, K = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k
+    T, R, el, dev = c.T, c.R, state.e_local, grad_out.device
+    st, status = nat.stream_ptr(), state.status.data_ptr()
+    clamped = 1 if cfg.activation == "swiglu_clamped" else 0
+    alpha, limit = float(cfg.swiglu_alpha), float(cfg.swiglu_limit)
+    need_x, need_scores, need_w13, need_w2 = needs
+    recv, offs = c.recv.data_ptr(), c.offsets.data_ptr()
+    none = nat.Operand(None, 0, None)
+    full = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
+    ws = _Bump(_train_workspace(state, R))
+    dyg = ws.take(R * D * 2)
+    dyq, dysf = ws.take(R * D), ws.take(_sf_rows_bytes(R, D))
+    dyc, dycsf = ws.take(R * D), ws.take(_sf_cols_bytes(R, D))
+    dh2 = ws.take(R * F * 2)
+    dh1 = ws.take(R * 2 * F * 2)
+    d1q, d1sf = ws.take(R * 2 * F), ws.take(_sf_rows_bytes(R, 2 * F))
+    d1c, d1csf = ws.take(R * 2 * F), ws.take(_sf_cols_bytes(R, 2 * F))
+    combine = state.combine.local().data_ptr()
+    grad_scores = torch.empty(T, K, dtype=torch.float32, device=dev) if need_scores else None
+    nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(), int(scores.dtype == torch.bfloat16),
+                                             ids.data_ptr(), int(ids.dtype == torch.int64),
+                                             c.h3.data_ptr() if need_scores else None, None, combine,
+                                             nat.ptr(grad_scores), T, K, D, st), "dm_broadcast_and_scale")
+    state.barrier(state.combine)
+    # ---- W2 ----------------------------------------------------------------------------------
+    nat.check(nat.lib.dm_gather_rows(c.sct.data_ptr(), recv, _ptr(dyg), None, D * 2, R, None, st),
+              "dm_gather_rows(grad_h3)")
+    nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dyg), recv, R, D, _ptr(dyq), 0, _ptr(dysf), 0, 1, st), "dm_quant_mxfp8_row(dy)")
+    nat.check(nat.lib.dm_gemm_blockscaled_dgrad(dyq, dysf, c.p2.fprop_data.data_ptr(), c.p2.dgrad_scale.data_ptr(), dh2,
+                                                None, offs, el, R, F, D, None, state.num_sms, status, st),
+              "dm_gemm_blockscaled_dgrad(w2)")
+    grad_w13 = grad_w2 = None
+    owners = options.wgrad_parameter_owners or (None, None)
+    if need_w2:
+        nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dyg), recv, R, D, _ptr(dyc), _ptr(dycsf), 1, st), "dm_quant_mxfp8_col(dy)")
+        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1])
+        nat.check(nat.lib.dm_gemm_blockscaled_wgrad(dyc, dycsf, full(c.h2_col), full(c.h2_col_sf), dst.data_ptr(),
+                                                    int(dst.dtype == torch.float32), acc, offs, el, R, D, F, None,
+                                                    state.num_sms, status, st), "dm_gemm_blockscaled_wgrad(w2)")
+        grad_w2 = dst.view(w2_param.shape) if ret else None
+    # ---- SwiGLU backward, W13 ---------------------------------------------------------------
+    nat.check(nat.lib.dm_swiglu_bwd(c.h1.data_ptr(), None, _ptr(dh2), None, _ptr(dh1), None, recv, R, F, clamped, alpha,
+                                    limit, st), "dm_swiglu_bwd")
+    if need_x:
+        nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dh1), recv, R, 2 * F, _ptr(d1q), 0, _ptr(d1sf), 0, 1, st),
+                  "dm_quant_mxfp8_row(dh1)")
+        nat.check(nat.lib.dm_gemm_blockscaled_dgrad(d1q, d1sf, c.p13.fprop_data.data_ptr(),
+                                                    c.p13.dgrad_scale.data_ptr(), none, c.bwd.data_ptr(), offs, el, R, D,
+                                                    2 * F, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled_dgrad(w13)")
+    if need_w13:
+        nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dh1), recv, R, 2 * F, _ptr(d1c), _ptr(d1csf), 1, st),
+                  "dm_quant_mxfp8_col(dh1)")
+        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0])
+        nat.check(nat.lib.dm_gemm_blockscaled_wgrad(d1c, d1csf, full(c.x_col), full(c.x_col_sf), dst.data_ptr(),
+                                                    int(dst.dtype == torch.float32), acc, offs, el, R, 2 * F, D, None,
+                                                    state.num_sms, status, st), "dm_gemm_blockscaled_wgrad(w13)")
+        grad_w13 = dst.view(w13_param.shape) if ret else None
+    grad_x = None
+    if need_x:
+        state.barrier(state.dispatch)
+        grad_x = torch.empty(x_shape, dtype=torch.bfloat16, device=dev)
+        nat.check(nat.lib.dm_scale_and_sum(state.dispatch.local().data_ptr(), None, 0, ids.data_ptr(),
+                                           int(ids.dtype == torch.int64), grad_x.data_ptr(), T, K, D, None, None, None,
+                                           0, st), "dm_scale_and_sum(reduce_from_topk)")
+    if grad_scores is not None and scores.dtype != torch.float32:
+        grad_scores = grad_scores.to(scores.dtype)
+    return grad_x, grad_scores, grad_w13, grad_w2
+
+
+class _Mxfp8Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ids, scores, w13_param, w2_param, state, options, p13, p2):
+        p13, p2 = _training_weights(w13_param, w2_param, p13, p2, state.config)
+        out, call = _mxfp8_forward(state, x.detach().contiguous(), ids, scores.detach(), p13, p2, options,
+                                   need_h3=scores.requires_grad)
+        ctx.state, ctx.call, ctx.options, ctx.x_shape = state, call, options, x.shape
+        ctx.save_for_backward(ids, scores, w13_param, w2_param)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ids, scores, w13_param, w2_param = ctx.saved_tensors
+        needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
+        gx, gs, gw13, gw2 = _mxfp8_backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param, w2_param,
+                                            grad_out.contiguous(), ctx.options, needs)
+        return gx, None, gs, gw13, gw2, None, None, None, None

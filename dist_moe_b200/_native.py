@@ -80,6 +80,14 @@ _SIGNATURES = {
         [c_int, Operand, Operand, _P, _P, Operand, Operand, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64,
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
+    "dm_gemm_blockscaled_dgrad": (
+        c_int,
+        [Operand, Operand, _P, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P],
+    ),
+    "dm_gemm_blockscaled_wgrad": (
+        c_int,
+        [Operand, Operand, Operand, Operand, _P, c_int, c_int, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P],
+    ),
     "dm_rmsnorm_combine_fwd": (
         c_int,
         [_P, _P, c_int, _P, c_int, _P, c_float, c_float, c_int, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int, _P],

@@ -255,8 +255,10 @@ __device__ __forceinline__ uint64_t sf_smem_desc(uint32_t smem_addr) {
 // Instruction descriptor of the block-scaled kinds (M128, K-major operands).
 //   fp4 == 0: kind::mxf8f6f4, E4M3 data, UE8M0 scales, sf ids select the scale byte of the K=32 step.
 //   fp4 != 0: kind::mxf4nvf4, E2M1 data, UE4M3 scales (4 per K=64 step).
-__host__ __device__ constexpr uint32_t umma_idesc_blockscaled(int n, int fp4, int a_sf_id, int b_sf_id) {
-  return (static_cast<uint32_t>(b_sf_id) << 4) | (static_cast<uint32_t>(fp4 ? 1 : 0) << 7) |
+__host__ __device__ constexpr uint32_t umma_idesc_blockscaled(int n, int fp4, int a_sf_id, int b_sf_id,
+                                                              int a_mn_major = 0, int b_mn_major = 0) {
+  return (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(b_sf_id) << 4) | (static_cast<uint32_t>(fp4 ? 1 : 0) << 7) |
          (static_cast<uint32_t>(fp4 ? 1 : 0) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(fp4 ? 0 : 1) << 23) | (static_cast<uint32_t>(128 >> 4) << 24) |
          (static_cast<uint32_t>(a_sf_id) << 29);

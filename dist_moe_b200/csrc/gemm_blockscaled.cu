@@ -53,24 +53,39 @@ struct BsParams {
   int* status;
   int64_t sfb_group_bytes;
   int e_local, max_rows, N, k_iters, fp4, swiglu, a_col_atoms, b_col_atoms;
+  int mode;       // 0 fprop (A, W K-major), 1 dgrad (W N-major), 2 wgrad (both operands MN-major, K = expert rows)
+  int Kw;         // dgrad: rows of one expert's W (the contraction extent); wgrad: dW columns
+  int out_fp32, accumulate;
+  const int64_t* b_off;
+  const int64_t* sfb_off;
   ActParams act;
 };
 
 struct BsTile {
-  int e, m_blk, n_blk, row0, row_end;
+  int e, m_blk, n_blk, row0, row_end, k_iters;
 };
 
-__device__ __forceinline__ BsTile bs_decode(int tile, int& e, const int* tile_start, const int* off) {
+__device__ __forceinline__ BsTile bs_decode(int tile, int& e, const int* tile_start, const int* off, int mode,
+                                            int n_tiles, int k_iters) {
   while (tile >= tile_start[e + 1]) ++e;
   const int local = tile - tile_start[e];
   const int rows = off[e + 1] - off[e];
-  const int m_tiles = (rows + kBsBM - 1) / kBsBM;
   BsTile t;
   t.e = e;
+  if (mode == 2) {
+    t.n_blk = local % n_tiles;
+    t.m_blk = local / n_tiles;
+    t.row0 = off[e];
+    t.row_end = off[e + 1];
+    t.k_iters = (rows + 127) / 128;
+    return t;
+  }
+  const int m_tiles = (rows + kBsBM - 1) / kBsBM;
   t.m_blk = local % m_tiles;
   t.n_blk = local / m_tiles;
   t.row0 = off[e] + t.m_blk * kBsBM;
   t.row_end = off[e + 1];
+  t.k_iters = k_iters;
   return t;
 }
 
@@ -90,7 +105,8 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tiles = (p.N + kBsBN - 1) / kBsBN;
+  const int n_tiles = p.mode == 2 ? (p.Kw + kBsBN - 1) / kBsBN : (p.N + kBsBN - 1) / kBsBN;
+  const int wgrad_m_tiles = (p.N + kBsBM - 1) / kBsBM;
   const int atoms = p.fp4 ? 4 : 1;  // scale atoms per stage and operand
 
   for (int i = threadIdx.x; i <= p.e_local; i += blockDim.x) {
@@ -116,7 +132,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
       s_tile_start[e] = acc;
       const int rows = s_off[e + 1] - s_off[e];
       if ((s_off[e] & 127) != 0) set_status(p.status, kCapacityExceeded, -1, e, s_off[e]);  // rows must be 128-padded
-      acc += ((rows + kBsBM - 1) / kBsBM) * n_tiles;
+      acc += p.mode == 2 ? wgrad_m_tiles * n_tiles : ((rows + kBsBM - 1) / kBsBM) * n_tiles;
     }
     s_tile_start[p.e_local] = acc;
   }
@@ -140,14 +156,24 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
     uint32_t phase = 0;
     int e = 0;
     const int a_line0 = static_cast<int>((p.a_off ? *p.a_off : 0) >> 7);
+    const int b_line0 = static_cast<int>((p.b_off ? *p.b_off : 0) >> 7);
     const uint8_t* sfa = p.sfa_base + (p.sfa_off ? *p.sfa_off : 0);
+    const uint8_t* sfb_dyn = p.sfb + (p.sfb_off ? *p.sfb_off : 0);
     const uint32_t sf_bytes = atoms * 512;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const BsTile t = bs_decode(tile, e, s_tile_start, s_off);
-      const uint8_t* sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
-      const uint8_t* sfb_row = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk) * p.b_col_atoms * 512;
-      for (int kb = 0; kb < p.k_iters; ++kb) {
+      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
+      const uint8_t* sfa_row;
+      const uint8_t* sfb_row;
+      if (p.mode == 2) {
+        // scales of the column-quantised operands: rows = features, columns = 32-row blocks of the packed rows
+        sfa_row = sfa + (static_cast<int64_t>(t.m_blk) * p.a_col_atoms + (t.row0 >> 7)) * 512;
+        sfb_row = sfb_dyn + (static_cast<int64_t>(t.n_blk) * p.b_col_atoms + (t.row0 >> 7)) * 512;
+      } else {
+        sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
+        sfb_row = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk) * p.b_col_atoms * 512;
+      }
+      for (int kb = 0; kb < t.k_iters; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
           if (ok) {
@@ -156,8 +182,16 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
             uint8_t* ssa = sb + kBsBBytes;
             uint8_t* ssb = ssa + kBsSfBytes;
             mbar_arrive_expect_tx(&full_bar[stage], kBsABytes + kBsBBytes + 2 * sf_bytes);
-            tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
-            tma_load_2d(sb, &p.tm_b, kb * 128, t.e * p.N + t.n_blk * kBsBN, &full_bar[stage]);
+            if (p.mode == 2) {
+              tma_load_3d(sa, &p.tm_a, 0, a_line0 + t.m_blk, t.row0 + kb * 128, &full_bar[stage]);
+              tma_load_3d(sb, &p.tm_b, 0, b_line0 + t.n_blk, t.row0 + kb * 128, &full_bar[stage]);
+            } else {
+              tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
+              if (p.mode == 1)
+                tma_load_2d(sb, &p.tm_b, t.n_blk * kBsBN, t.e * p.Kw + kb * 128, &full_bar[stage]);
+              else
+                tma_load_2d(sb, &p.tm_b, kb * 128, t.e * p.N + t.n_blk * kBsBN, &full_bar[stage]);
+            }
             bulk_load(ssa, sfa_row + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
             bulk_load(ssb, sfb_row + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
           }
@@ -178,7 +212,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
     uint32_t kstep = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      bs_decode(tile, e, s_tile_start, s_off);
+      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (lane == 0) ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
@@ -186,7 +220,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t d_tmem = tmem_base + buf * kBsBN;
-      for (int kb = 0; kb < p.k_iters; ++kb, ++kstep) {
+      for (int kb = 0; kb < t.k_iters; ++kb, ++kstep) {
         if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
@@ -203,13 +237,15 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint64_t da = umma_smem_desc(a_addr + j * 32, 16, 1024);
-            const uint64_t db = umma_smem_desc(b_addr + j * 32, 16, 1024);
+            // K-major: 32 bytes of K per step inside the 128-byte row; MN-major: four 8-row groups of 1 KiB.
+            const int a_mn = p.mode == 2, b_mn = p.mode != 0;
+            const uint64_t da = a_mn ? umma_smem_desc(a_addr + j * 4096, 16, 1024) : umma_smem_desc(a_addr + j * 32, 16, 1024);
+            const uint64_t db = b_mn ? umma_smem_desc(b_addr + j * 4096, 16, 1024) : umma_smem_desc(b_addr + j * 32, 16, 1024);
             const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
             if (p.fp4)
               umma_nvf4(d_tmem, da, db, umma_idesc_blockscaled(kBsBN, 1, 0, 0), sfa_t + 4 * j, sfb_t + 4 * j, acc);
             else
-              umma_mxf8(d_tmem, da, db, umma_idesc_blockscaled(kBsBN, 0, j, j), sfa_t, sfb_t, acc);
+              umma_mxf8(d_tmem, da, db, umma_idesc_blockscaled(kBsBN, 0, j, j, a_mn, b_mn), sfa_t, sfb_t, acc);
           }
           tcgen05_commit(&empty_bar[stage]);
         }
@@ -220,7 +256,12 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
         }
       }
       if (!ok) break;
-      if (lane == 0) tcgen05_commit(&tmem_full_bar[buf]);
+      if (lane == 0) {
+        if (t.k_iters > 0)
+          tcgen05_commit(&tmem_full_bar[buf]);
+        else
+          mbar_arrive(&tmem_full_bar[buf]);
+      }
       __syncwarp();
     }
   } else {
@@ -235,7 +276,7 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
     const float* row_inv =
         p.row_inv_base ? reinterpret_cast<const float*>(p.row_inv_base + (p.row_inv_off ? *p.row_inv_off : 0)) : nullptr;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const BsTile t = bs_decode(tile, e, s_tile_start, s_off);
+      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
@@ -243,6 +284,66 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBsBN;
+      if (p.mode == 2) {
+        // weight gradient: dW[e][m][n], overwrite or accumulate (fp32 or bf16 destination)
+        const int out_row = t.m_blk * kBsBM + row_in_tile;
+        const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kw;
+        const uint64_t my_row =
+            out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
+        for (int c0 = 0; c0 < kBsBN; c0 += 32) {
+          uint32_t r[32];
+          if (t.k_iters > 0) {
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          const int col = t.n_blk * kBsBN + c0;
+          if (p.out_fp32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              stage_put(stg, lane, j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), j = lane & 7;
+              const uint4 v = stage_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+              if (rp != 0 && col + 4 * j + 4 <= p.Kw) {
+                const uint64_t dst = rp + static_cast<uint64_t>(col + 4 * j) * 4;
+                if (p.accumulate)
+                  red_add_f32x4(dst, v);
+                else
+                  *reinterpret_cast<uint4*>(dst) = v;
+              }
+            }
+            __syncwarp();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), j = lane & 3;
+              const uint4 v = stage64_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+              if (rp != 0 && col + 8 * j + 8 <= p.Kw) {
+                const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
+                if (p.accumulate)
+                  red_add_bf16x8(dst, v);
+                else
+                  *reinterpret_cast<uint4*>(dst) = v;
+              }
+            }
+            __syncwarp();
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+        continue;
+      }
       const int row = t.row0 + row_in_tile;
       const bool row_ok = row < t.row_end;
       float scale = 1.0f;
@@ -369,6 +470,17 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
 
 using namespace dm;
 
+static int bs_prepare_launch() {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(blockscaled_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kBsSmemBytes));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  return kRcOk;
+}
+
 extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w, const void* sfb,
                                    dm_operand c, dm_operand h2, const int64_t* scatter_ptrs, dm_operand row_scale_inv,
                                    const float* expert_scale_inv, const int32_t* expert_offsets, int e_local,
@@ -384,15 +496,10 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   const int64_t row_bytes = fp4 ? Kd / 2 : Kd;
   if ((row_bytes % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(blockscaled_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kBsSmemBytes));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  int rc = bs_prepare_launch();
+  if (rc != kRcOk) return rc;
   BsParams p{};
-  int rc = encode_arena_u8(&p.tm_a, a, row_bytes, max_rows + 256, kBsBM);
+  rc = encode_arena_u8(&p.tm_a, a, row_bytes, max_rows + 256, kBsBM);
   if (rc != kRcOk) return rc;
   rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kBsBN);
   if (rc != kRcOk) return rc;
@@ -422,6 +529,98 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   p.fp4 = fp4;
   p.swiglu = swiglu_interleaved ? 1 : 0;
   p.act = ActParams{clamped, alpha, limit};
+  const int grid = num_sms > 0 ? num_sms : sm_count();
+  blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Input gradient: C[r, n] = sum_k dY[r, k] * W[e][k, n].  W is the same E4M3 qdata as in the forward
+// ([E, Kd, N] bytes, 32x32-tile quantised) read N-major, with the scales of the transposed orientation
+// ([N rows, Kd/32 columns] per expert, blocked).
+extern "C" int dm_gemm_blockscaled_dgrad(dm_operand dy, dm_operand sf_dy, const void* w, const void* sfb_dgrad,
+                                         dm_operand c, const int64_t* scatter_ptrs, const int32_t* expert_offsets,
+                                         int e_local, int64_t max_rows, int64_t N, int64_t Kd, const int* cond,
+                                         int num_sms, int* status, void* stream) {
+  if (!dy.base || !sf_dy.base || !w || !sfb_dgrad || !expert_offsets || e_local <= 0 || max_rows < 0 || N <= 0 ||
+      Kd <= 0)
+    return kRcBadArg;
+  if (!c.base && !scatter_ptrs) return kRcBadArg;
+  if (e_local > kBsMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
+  if ((Kd % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0) return kRcUnsupportedShape;
+  if (max_rows == 0) return kRcOk;
+  int rc = bs_prepare_launch();
+  if (rc != kRcOk) return rc;
+  BsParams p{};
+  rc = encode_arena_u8(&p.tm_a, dy, Kd, max_rows + 256, kBsBM);
+  if (rc != kRcOk) return rc;
+  rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * Kd, N, kBsBN);
+  if (rc != kRcOk) return rc;
+  p.a_col_atoms = static_cast<int>((Kd / 32 + 3) / 4);
+  p.b_col_atoms = p.a_col_atoms;
+  p.sfb_group_bytes = (N + 127) / 128 * 128 * static_cast<int64_t>(p.b_col_atoms) * 4;
+  p.a_off = dy.offset;
+  p.sfa_off = sf_dy.offset;
+  p.sfa_base = static_cast<const uint8_t*>(sf_dy.base);
+  p.sfb = static_cast<const uint8_t*>(sfb_dgrad);
+  p.c_off = c.offset;
+  p.c_base = static_cast<uint8_t*>(c.base);
+  p.scatter_ptrs = scatter_ptrs;
+  p.expert_offsets = expert_offsets;
+  p.cond = cond;
+  p.status = status;
+  p.e_local = e_local;
+  p.max_rows = static_cast<int>(max_rows);
+  p.N = static_cast<int>(N);
+  p.Kw = static_cast<int>(Kd);
+  p.k_iters = static_cast<int>(Kd / 128);
+  p.mode = 1;
+  p.act = ActParams{0, 1.0f, 0.0f};
+  const int grid = num_sms > 0 ? num_sms : sm_count();
+  blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Weight gradient: dW[e][m, n] (+)= sum_{r in expert e} dY[r, m] * X[r, n].  Both operands are quantised
+// along the row dimension (32 rows share a scale, per column); their scales are blocked with the
+// feature as the row index and the 32-row block as the column index.
+extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col, dm_operand sf_x_col,
+                                         void* dw, int dw_is_fp32, int accumulate, const int32_t* expert_offsets,
+                                         int e_local, int64_t max_rows, int64_t M, int64_t N, const int* cond,
+                                         int num_sms, int* status, void* stream) {
+  if (!dy_col.base || !sf_dy_col.base || !x_col.base || !sf_x_col.base || !dw || !expert_offsets || e_local <= 0 ||
+      max_rows < 0 || M <= 0 || N <= 0)
+    return kRcBadArg;
+  if (e_local > kBsMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
+  if ((M % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0) return kRcUnsupportedShape;
+  int rc = bs_prepare_launch();
+  if (rc != kRcOk) return rc;
+  BsParams p{};
+  // with no rows at all the kernel still runs so that a non-accumulating call zero-fills dW
+  const int64_t rows_extent = max_rows > 0 ? max_rows : 128;
+  rc = encode_arena_u8(&p.tm_a, dy_col, M, rows_extent, 128);
+  if (rc != kRcOk) return rc;
+  rc = encode_arena_u8(&p.tm_b, x_col, N, rows_extent, 128);
+  if (rc != kRcOk) return rc;
+  p.a_col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  p.b_col_atoms = p.a_col_atoms;
+  p.a_off = dy_col.offset;
+  p.b_off = x_col.offset;
+  p.sfa_off = sf_dy_col.offset;
+  p.sfb_off = sf_x_col.offset;
+  p.sfa_base = static_cast<const uint8_t*>(sf_dy_col.base);
+  p.sfb = static_cast<const uint8_t*>(sf_x_col.base);
+  p.c_base = static_cast<uint8_t*>(dw);
+  p.expert_offsets = expert_offsets;
+  p.cond = cond;
+  p.status = status;
+  p.e_local = e_local;
+  p.max_rows = static_cast<int>(max_rows);
+  p.N = static_cast<int>(M);
+  p.Kw = static_cast<int>(N);
+  p.mode = 2;
+  p.out_fp32 = dw_is_fp32 ? 1 : 0;
+  p.accumulate = accumulate ? 1 : 0;
+  p.act = ActParams{0, 1.0f, 0.0f};
   const int grid = num_sms > 0 ? num_sms : sm_count();
   blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
   return static_cast<int>(cudaGetLastError());

@@ -264,6 +264,28 @@ int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w,
                         int64_t N, int64_t Kd, int swiglu_interleaved, int clamped, float alpha, float limit,
                         const int* cond, int num_sms, int* status, void* stream);
 
+/* MXFP8 training backward GEMMs (dist_moe/_blockscaled_ops.py: `dist_blockscaled_grouped_gemm_dgrad_dispatch`,
+ * `..._dgrad_swiglu_bwd_combine`, `blockscaled_grouped_gemm_wgrad`; sequencing dist_moe/_blockscaled.py:2284-2512).
+ *
+ * dm_gemm_blockscaled_dgrad: C[r, n] = sum_k dY[r, k] * W[e][k, n], bf16 rows (or scattered to scatter_ptrs[r];
+ *   a null pointer skips the row).  dY [rows, Kd] is row-quantised E4M3 with blocked scales; W is the SAME
+ *   qdata the forward reads ([e_local, Kd, N], 32x32-tile quantised, dist_moe/_blockscaled.py:858-881), read
+ *   N-major, with the scales of the transposed orientation: per expert a blocked group of N rows x Kd/32 columns.
+ *
+ * dm_gemm_blockscaled_wgrad: dW[e][m, n] (=|+=) sum_{r in expert e} dY[r, m] * X[r, n], fp32 or bf16.
+ *   dY_col [rows, M] and X_col [rows, N] are E4M3 quantised along the row dimension (32 consecutive rows of a
+ *   column share one E8M0 scale); their scales are blocked with the feature as row index and row/32 as column
+ *   index, (max_rows/32 + 3)/4 column atoms per row atom (what dm_quant_mxfp8_col writes for max_rows rows).
+ *   Padding rows of an expert must hold zero data. */
+int dm_gemm_blockscaled_dgrad(dm_operand dy, dm_operand sf_dy, const void* w, const void* sfb_dgrad, dm_operand c,
+                              const int64_t* scatter_ptrs, const int32_t* expert_offsets, int e_local,
+                              int64_t max_rows, int64_t N, int64_t Kd, const int* cond, int num_sms, int* status,
+                              void* stream);
+int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col, dm_operand sf_x_col, void* dw,
+                              int dw_is_fp32, int accumulate, const int32_t* expert_offsets, int e_local,
+                              int64_t max_rows, int64_t M, int64_t N, const int* cond, int num_sms, int* status,
+                              void* stream);
+
 /* ---------------------------------------------------------------------------
  * Fused post-expert RMSNorm + weighted top-k reduction
  * (dist_moe/kernels/norm/fused_rmsnorm_combine.py:576-765 forward, 802-1018 backward,

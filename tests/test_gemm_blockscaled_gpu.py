@@ -147,3 +147,130 @@ def test_blockscaled_gemm_interleaved_swiglu(fmt):
         _close(h1[lo:hi].cpu(), ref, f"h1 fmt {fmt} expert {e}")
         g, u = h1[lo:hi, :F].float().cpu(), h1[lo:hi, F:].float().cpu()
         _close(h2[lo:hi].cpu(), g * torch.sigmoid(g) * u, f"h2 fmt {fmt} expert {e}")
+
+
+# ---------------------------------------------------------------------------------------------
+# MXFP8 training backward: input gradient (W read N-major) and weight gradient (both operands
+# quantised along the row dimension).  Same rule as above: reference = fp32 matmul of dequantised
+# operands, so only accumulation order and the final rounding differ.
+# ---------------------------------------------------------------------------------------------
+def _e8m0(s):
+    return np.exp2(s.astype(np.float32) - 127.0)
+
+
+def _tile32_weight(nat, w):
+    """w bf16 [E, N, K] -> (shared qdata, fprop scales, dgrad scales, dequantised fp32 [E, N, K])."""
+    E, N, K = w.shape
+    q = torch.zeros(E * N, K, dtype=torch.uint8, device=DEV)
+    a0, a1 = (K // 32 + 3) // 4, (N // 32 + 3) // 4
+    s0 = torch.zeros(E * ((N + 127) // 128 * 128) * a0 * 4, dtype=torch.uint8, device=DEV)
+    s1 = torch.zeros(E * ((K + 127) // 128 * 128) * a1 * 4, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_tile32(w.data_ptr(), E, N, K, q.data_ptr(), s0.data_ptr(), s1.data_ptr(), 1,
+                                            nat.stream_ptr()), "tile32")
+    deq = []
+    for e in range(E):
+        qn, sn = Q.mxfp8_tile32(w[e].cpu())
+        full = np.repeat(np.repeat(_e8m0(sn), 32, axis=0), 32, axis=1)
+        deq.append(torch.from_numpy(Q.e4m3_to_f32(qn).astype(np.float32) * full))
+    return q, s0, s1, torch.stack(deq)
+
+
+def _quant_col(nat, x, max_rows):
+    """x bf16 [R, C] -> (q [max_rows, C], blocked scales (feature, row block), dequantised fp32 [R, C])."""
+    R, C = x.shape
+    q = torch.zeros(max_rows, C, dtype=torch.uint8, device=DEV)
+    atoms = ((max_rows + 31) // 32 + 3) // 4
+    s = torch.zeros((C + 127) // 128 * 128 * atoms * 4, dtype=torch.uint8, device=DEV)
+    cnt = torch.tensor([R], dtype=torch.int32, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_col(x.data_ptr(), cnt.data_ptr(), max_rows, C, q.data_ptr(), s.data_ptr(), 1,
+                                         nat.stream_ptr()), "qcol")
+    qn, sn = Q.mxfp8_col(x.cpu())                       # scales [C, R/32]
+    deq = Q.e4m3_to_f32(qn).astype(np.float32) * np.repeat(_e8m0(sn).T, 32, axis=0)[:R]
+    return q, s, torch.from_numpy(deq)
+
+
+def _offsets(counts):
+    off = [0]
+    for c in counts:
+        off.append(off[-1] + c)
+    return off
+
+
+@pytest.mark.parametrize("counts,K,N", [([128, 0, 256], 256, 128), ([384], 128, 384), ([128, 256, 128], 512, 256)])
+@pytest.mark.parametrize("scatter", [False, True])
+def test_blockscaled_dgrad(counts, K, N, scatter):
+    """C[r, n] = sum_k dY[r, k] W[e][k, n]; W stored [E, K, N] (the forward's [E, rows=K, cols=N])."""
+    nat = _nat()
+    torch.manual_seed(K + N)
+    E, off = len(counts), _offsets(counts)
+    R = off[-1]
+    offs = torch.tensor(off, dtype=torch.int32, device=DEV)
+    dy = torch.randn(R, K, device=DEV).bfloat16()
+    w = (torch.randn(E, K, N, device=DEV) * 0.05).bfloat16()
+    qa, sa, da, _ = _quant_act(nat, dy, 0)
+    qw, _, s_dgrad, dw = _tile32_weight(nat, w)
+    out = torch.full((R + 8, N), 5.0, device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    op = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
+    none = nat.Operand(None, 0, None)
+    ptrs = None
+    if scatter:
+        perm = torch.randperm(R, device=DEV)
+        ptrs = out.data_ptr() + perm.to(torch.int64) * (N * 2)
+        ptrs[R - 1] = 0  # a padding row: skipped
+    rc = nat.lib.dm_gemm_blockscaled_dgrad(op(qa), op(sa), qw.data_ptr(), s_dgrad.data_ptr(), none if scatter else op(out),
+                                           nat.ptr(ptrs), offs.data_ptr(), E, R, N, K, None, 0, status.data_ptr(),
+                                           nat.stream_ptr())
+    nat.check(rc, "dm_gemm_blockscaled_dgrad")
+    torch.cuda.synchronize()
+    assert status[0].item() == 0, status.tolist()
+    ref = torch.zeros(R, N)
+    for e in range(E):
+        ref[off[e]:off[e + 1]] = da[off[e]:off[e + 1]] @ dw[e]
+    got = out[:R].cpu()
+    if scatter:
+        p = perm.cpu()
+        _close(got[p[: R - 1]], ref[: R - 1], "dgrad scatter")
+        assert bool((got[p[R - 1]] == 5.0).all())
+    else:
+        _close(got, ref, "dgrad")
+    assert bool((out[R:] == 5.0).all())
+
+
+@pytest.mark.parametrize("counts,M,N", [([128, 0, 256], 128, 256), ([384, 128], 256, 128), ([1024], 384, 128)])
+@pytest.mark.parametrize("fp32,acc", [(1, 0), (1, 1), (0, 0), (0, 1)])
+def test_blockscaled_wgrad(counts, M, N, fp32, acc):
+    nat = _nat()
+    torch.manual_seed(M + 3 * N + fp32)
+    E, off = len(counts), _offsets(counts)
+    R = off[-1]
+    cap = R + 256                                        # capacity larger than the routed rows
+    offs = torch.tensor(off, dtype=torch.int32, device=DEV)
+    dy = torch.randn(R, M, device=DEV).bfloat16()
+    x = torch.randn(R, N, device=DEV).bfloat16()
+    qd, sd, dd = _quant_col(nat, dy, cap)
+    qx, sx, dx = _quant_col(nat, x, cap)
+    dtype = torch.float32 if fp32 else torch.bfloat16
+    base = (torch.randn(E, M, N, device=DEV) * 4).to(dtype) if acc else torch.full((E, M, N), 7.0, device=DEV, dtype=dtype)
+    dw = base.clone()
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    op = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
+    rc = nat.lib.dm_gemm_blockscaled_wgrad(op(qd), op(sd), op(qx), op(sx), dw.data_ptr(), fp32, acc, offs.data_ptr(), E,
+                                           cap, M, N, None, 0, status.data_ptr(), nat.stream_ptr())
+    nat.check(rc, "dm_gemm_blockscaled_wgrad")
+    torch.cuda.synchronize()
+    assert status[0].item() == 0, status.tolist()
+    for e in range(E):
+        lo, hi = off[e], off[e + 1]
+        ref = dd[lo:hi].T @ dx[lo:hi]
+        got = dw[e].float().cpu()
+        if acc:
+            ref = ref + base[e].float().cpu()
+            if not fp32:  # one bf16 rounding of the sum
+                ref = ref.bfloat16().float()
+                assert (got - ref).abs().max().item() <= ref.abs().max().item() * 2.0**-7
+                continue
+        elif hi == lo:
+            assert bool((got == 0).all())
+            continue
+        _close(got if fp32 else got.bfloat16(), ref, f"wgrad expert {e}")

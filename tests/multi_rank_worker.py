@@ -98,6 +98,44 @@ def run_block_scaled_case(dm, group, rank, world, dev, fmt, T, D, F, K, E):
         ctx.close()
 
 
+def run_mxfp8_training_case(dm, group, rank, world, dev, T, D, F, K, E):
+    """MXFP8 forward + backward across ranks (bf16 rows dispatched, quantised by the expert rank); the reference's
+    two-rank block-scaled shape and bounds (tests/test_dist_moe.py:317-322: relative L2 < 0.075, cosine > 0.9975)."""
+    xs, ids, scores, w13, w2 = inputs(world, T, D, F, K, E, False)
+    xs = [(x.float() * 0.1).bfloat16() for x in xs]
+    el = E // world
+    gen = torch.Generator().manual_seed(23)
+    gos = [torch.randn(T, D, generator=gen).bfloat16() for _ in range(world)]
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, device_scratch_capacity_factor=float(world),
+                    block_scaled=dm.BlockScaledConfig())
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    try:
+        xr = [x.clone().requires_grad_(True) for x in xs]
+        sr = [s.clone().requires_grad_(True) for s in scores]
+        a = w13.clone().requires_grad_(True)
+        b = w2.clone().requires_grad_(True)
+        refs = [oracle_moe.moe_forward(xr[r], ids[r], sr[r], a, b) for r in range(world)]
+        torch.autograd.backward(refs, gos)
+        for _ in range(2):
+            x = xs[rank].to(dev).requires_grad_(True)
+            s = scores[rank].to(dev).requires_grad_(True)
+            wa = w13[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
+            wb = w2[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
+            out = dm.routed_experts(x, ids[rank].to(dev), s, wa, wb, ctx)
+            out.backward(gos[rank].to(dev))
+            ctx.check_status()
+            pairs = ((out, refs[rank]), (x.grad, xr[rank].grad), (s.grad, sr[rank].grad),
+                     (wa.grad, a.grad[rank * el:(rank + 1) * el]), (wb.grad, b.grad[rank * el:(rank + 1) * el]))
+            for name, (got, ref) in zip(("output", "grad x", "grad scores", "grad w13", "grad w2"), pairs):
+                got, ref = got.detach().float().cpu(), ref.detach().float()
+                l2 = ((got - ref).norm() / ref.norm()).item()
+                cos = torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item()
+                assert l2 < 0.075 and cos > 0.9975, ("MXFP8 training", rank, name, l2, cos)
+    finally:
+        ctx.close()
+
+
 def main():
     import dist_moe_b200 as dm
 
@@ -111,6 +149,7 @@ def main():
     run_case(dm, group, rank, world, dev, 300, 512, 384, 4, 8 * world, False, 1.0)
     run_block_scaled_case(dm, group, rank, world, dev, "MXFP8_E4M3", 200, 512, 256, 4, 4 * world)
     run_block_scaled_case(dm, group, rank, world, dev, "NVFP4", 130, 512, 256, 2, 4 * world)
+    run_mxfp8_training_case(dm, group, rank, world, dev, 128, 1024, 1024, 2, 2 * world)
     dist.barrier()
     if rank == 0:
         print("MULTI_RANK_OK", world, flush=True)

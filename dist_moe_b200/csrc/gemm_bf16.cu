@@ -560,6 +560,16 @@ static int launch(const GemmParams& p, int num_sms, cudaStream_t st) {
 
 using namespace dm;
 
+// Forward and input-gradient GEMMs run on the paired kernel when the shape allows it (default); the
+// single-CTA kernel stays selectable for comparison and serves the remaining shapes.
+static int g_use_pairs = 1;
+
+extern "C" int dm_set_gemm_pairs(int enabled) {
+  const int previous = g_use_pairs;
+  g_use_pairs = enabled ? 1 : 0;
+  return previous;
+}
+
 static int setup_gather(GemmParams& p, const dm_operand& a, const int64_t* gather_ptrs, int32_t* gather_flags,
                         int64_t max_rows, cudaStream_t st) {
   if (gather_ptrs == nullptr) return kRcOk;
@@ -581,6 +591,11 @@ static int fprop_impl(dm_operand a, const void* w, dm_operand c, dm_operand h2, 
   if ((Kd % 64) != 0 || (N % 8) != 0) return kRcUnsupportedShape;
   if (fuse_swiglu && (((N / 2) % (kBN / 2)) != 0 || !h2.base || !c.base || scatter_ptrs)) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
+  if (gather_ptrs != nullptr && gather_flags == nullptr) return kRcBadArg;
+  if (g_use_pairs && dm_pair_supported(N, Kd, fuse_swiglu, 0))
+    return dm_pair_launch(a, w, c, h2, scatter_ptrs, gather_ptrs, gather_flags, expert_offsets, e_local, max_rows, N, Kd,
+                          fuse_swiglu, 0, clamped, alpha, limit, cond, num_sms, status,
+                          static_cast<cudaStream_t>(stream));
   GemmParams p{};
   int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
   if (rc != kRcOk) return rc;
@@ -633,6 +648,11 @@ static int dgrad_impl(dm_operand a, const void* w, dm_operand c, const int64_t* 
   if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
   if ((Kd % 64) != 0 || (N % 8) != 0) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
+  if (gather_ptrs != nullptr && gather_flags == nullptr) return kRcBadArg;
+  if (g_use_pairs && dm_pair_supported(N, Kd, 0, 1))
+    return dm_pair_launch(a, w, c, dm_operand{nullptr, 0, nullptr}, scatter_ptrs, gather_ptrs, gather_flags,
+                          expert_offsets, e_local, max_rows, N, Kd, 0, 1, 0, 1.0f, 0.0f, cond, num_sms, status,
+                          static_cast<cudaStream_t>(stream));
   GemmParams p{};
   int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
   if (rc != kRcOk) return rc;

@@ -378,9 +378,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--separate-gather", action="store_true",
                     help="gather routed rows with a separate kernel instead of inside the GEMM launches")
+    ap.add_argument("--single-cta", action="store_true",
+                    help="run forward / input-gradient GEMMs on the single-CTA kernel instead of CTA pairs")
     ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
     args = ap.parse_args()
+    if args.single_cta and args.impl == "ours":
+        from dist_moe_b200 import _native
+
+        _native.lib.dm_set_gemm_pairs(0)
     if args.micro:
         run_micro(args)
     elif args.impl == "reference":

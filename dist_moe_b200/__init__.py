@@ -20,6 +20,10 @@ from .api import (
     supports_fused_post_expert_rmsnorm,
 )
 from .formats import BlockScaledFormat
+from . import _ops as _ops
+
+# torch.ops.dist_moe.* (operator schemas and fake implementations for tracing); no device work happens here
+_ops.register()
 
 __all__ = [
     "Bf16GroupedGemmPreset",

@@ -184,8 +184,21 @@ def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save
     return out, c
 
 
-def _wgrad_destination(param: torch.Tensor, shape, options: ExecutionOptions, cfg, owner: torch.Tensor | None):
-    """Return (tensor, accumulate, returned_to_autograd)."""
+def _wgrad_destination(param: torch.Tensor, shape, options: ExecutionOptions, cfg, owner: torch.Tensor | None,
+                       explicit=None):
+    """Return (tensor, accumulate, returned_to_autograd).
+
+    ``explicit`` is used by the registered operators: a tensor to accumulate into, or a dtype for a fresh result.
+    """
+    if isinstance(explicit, torch.Tensor):
+        if not explicit.is_contiguous() or explicit.dtype not in (torch.bfloat16, torch.float32) \
+                or explicit.numel() != param.numel():
+            raise ValueError("WGRAD accumulators must be contiguous BF16 or FP32 tensors of the weight's size")
+        return explicit, 1, False
+    if isinstance(explicit, torch.dtype):
+        if explicit not in (torch.bfloat16, torch.float32):
+            raise ValueError("wgrad_output_dtype must be torch.bfloat16 or torch.float32")
+        return torch.empty(shape, dtype=explicit, device=param.device), 0, True
     if options.inplace_wgrad_accum:
         target = owner if owner is not None else param
         if target.grad is None:
@@ -204,7 +217,7 @@ def _wgrad_destination(param: torch.Tensor, shape, options: ExecutionOptions, cf
 
 
 def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_param, grad_out,
-                  options: ExecutionOptions, needs):
+                  options: ExecutionOptions, needs, wgrad_explicit=(None, None)):
     cfg = state.config
     T, D, K, F, el = c.T, cfg.hidden_dim, cfg.top_k, cfg.intermediate_dim, state.e_local
     dev, st, status = grad_out.device, nat.stream_ptr(), state.status.data_ptr()
@@ -264,7 +277,7 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     grad_w13 = grad_w2 = None
     owners = options.wgrad_parameter_owners or (None, None)
     if need_w2:
-        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1])
+        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1])
         _gemm_wgrad(_op(state, bo[4:5]), _op(state, bo[2:3]), dst.data_ptr(),
                                         int(dst.dtype == torch.float32), acc, c.offsets.data_ptr(), el, c.max_rows,
                                         D, F, state.num_sms, status, st, what="gemm_wgrad(w2)")
@@ -278,7 +291,7 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
                                         c.offsets.data_ptr(), el, c.max_rows, D, 2 * F, None, state.num_sms, status,
                                         st, what="gemm_dgrad(w13)")
     if need_w13:
-        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0])
+        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0])
         _gemm_wgrad(_op(state, bo[5:6]), _op(state, bo[0:1]), dst.data_ptr(),
                                         int(dst.dtype == torch.float32), acc, c.offsets.data_ptr(), el, c.max_rows,
                                         2 * F, D, state.num_sms, status, st, what="gemm_wgrad(w13)")

@@ -102,11 +102,36 @@ def prepare_weight(weight: torch.Tensor, config, *, fuse_swiglu: bool = False, i
         if F % 64 != 0:
             raise ValueError("fuse_swiglu needs intermediate_dim to be a multiple of 64")
         w = w.index_select(1, interleave_index(F, w.device)).contiguous()
-    vec = 16 if fmt is BlockScaledFormat.NVFP4 else 32
-    if K % (256 if fmt is BlockScaledFormat.NVFP4 else 128) or N % 128:
+    if out is not None:
+        qfmt = "nvfp4" if fmt is BlockScaledFormat.NVFP4 else "mxfp8"
+        _quantize_weight(w, qfmt, inference, out=out)
+        return out
+    if fmt is BlockScaledFormat.NVFP4:
+        q, sc, gs, gsi = _quantize_weight(w, "nvfp4", True)
+        return PreparedWeight._create(source=weight, format=fmt, fprop_data=q, fprop_scale=sc, dgrad_data=None,
+                                      dgrad_scale=None, global_scale=gs, global_scale_inv=gsi,
+                                      interleaved_fc13=bool(fuse_swiglu))
+    q, s0, s1 = _quantize_weight(w, "mxfp8", inference)
+    return PreparedWeight._create(source=weight, format=fmt, fprop_data=q, fprop_scale=s0,
+                                  dgrad_data=None if inference else q, dgrad_scale=s1, global_scale=None,
+                                  global_scale_inv=None, interleaved_fc13=bool(fuse_swiglu))
+
+
+def _quantize_weight(w: torch.Tensor, kind: str, inference: bool, out: PreparedWeight | None = None):
+    """Quantise a contiguous bf16 ``[E, N, K]`` weight (rows already interleaved if wanted).
+
+    mxfp8: ``(qdata [E,N,K] u8, forward scales, input-gradient scales or None)``; training uses 32x32 tiles with
+    one shared qdata and two scale orientations, inference 1x32 rows (dist_moe/_blockscaled.py:798-882).
+    nvfp4: ``(packed qdata [E,N,K/2], E4M3 scales, global scale fp32[E], its inverse)`` with
+    ``global scale = 2688 / amax`` per expert (dist_moe/_blockscaled.py:140-196).
+    ``out`` refills the tensors of an existing PreparedWeight in place.
+    """
+    E, N, K = w.shape
+    nvfp4 = kind == "nvfp4"
+    if K % (256 if nvfp4 else 128) or N % 128:
         raise ValueError("block-scaled weights need N % 128 == 0 and K % 128 == 0 (K % 256 for NVFP4)")
     dev, st = w.device, nat.stream_ptr()
-    qb, sc = _geometry(fmt, K)
+    qb, sc = (K // 2, K // 16) if nvfp4 else (K, K // 32)
     grp = _blocked_group_bytes(N, sc)
 
     def storage(name, shape, dtype):
@@ -119,8 +144,7 @@ def prepare_weight(weight: torch.Tensor, config, *, fuse_swiglu: bool = False, i
 
     fprop_data = storage("fprop_data", (E, N, qb), torch.uint8)
     fprop_scale = storage("fprop_scale", (E * grp,), torch.uint8)
-    dgrad_data = dgrad_scale = gs = gsi = None
-    if fmt is BlockScaledFormat.NVFP4:
+    if nvfp4:
         amax = torch.linalg.vector_norm(w, ord=float("inf"), dim=(-2, -1), dtype=torch.float32).clamp(min=1e-12)
         gs_new = 2688.0 * torch.reciprocal(amax)
         gs = storage("global_scale", (E,), torch.float32)
@@ -129,21 +153,43 @@ def prepare_weight(weight: torch.Tensor, config, *, fuse_swiglu: bool = False, i
         gsi.copy_(torch.reciprocal(gs_new))
         nat.check(nat.lib.dm_quant_nvfp4_weight(w.data_ptr(), gs.data_ptr(), E, N, K, fprop_data.data_ptr(),
                                                 fprop_scale.data_ptr(), 1, st), "dm_quant_nvfp4_weight")
-    elif inference:
+        return fprop_data, fprop_scale, gs, gsi
+    if inference:
         for e in range(E):
             nat.check(nat.lib.dm_quant_mxfp8_row(w[e].data_ptr(), None, N, K, fprop_data[e].data_ptr(), 0,
                                                  fprop_scale[e * grp:].data_ptr(), 0, 1, st), "dm_quant_mxfp8_row")
-    else:
-        grp_d = _blocked_group_bytes(K, N // 32)
-        dgrad_scale = storage("dgrad_scale", (E * grp_d,), torch.uint8)
-        nat.check(nat.lib.dm_quant_mxfp8_tile32(w.data_ptr(), E, N, K, fprop_data.data_ptr(), fprop_scale.data_ptr(),
-                                                dgrad_scale.data_ptr(), 1, st), "dm_quant_mxfp8_tile32")
-        dgrad_data = fprop_data
-    if out is not None:
-        return out
-    return PreparedWeight._create(source=weight, format=fmt, fprop_data=fprop_data, fprop_scale=fprop_scale,
-                                  dgrad_data=dgrad_data, dgrad_scale=dgrad_scale, global_scale=gs,
-                                  global_scale_inv=gsi, interleaved_fc13=bool(fuse_swiglu))
+        return fprop_data, fprop_scale, None
+    grp_d = _blocked_group_bytes(K, N // 32)
+    dgrad_scale = storage("dgrad_scale", (E * grp_d,), torch.uint8)
+    nat.check(nat.lib.dm_quant_mxfp8_tile32(w.data_ptr(), E, N, K, fprop_data.data_ptr(), fprop_scale.data_ptr(),
+                                            dgrad_scale.data_ptr(), 1, st), "dm_quant_mxfp8_tile32")
+    return fprop_data, fprop_scale, dgrad_scale
+
+
+def _as_enk(weight: torch.Tensor, fuse_swiglu: bool) -> torch.Tensor:
+    if weight.device.type != "cuda" or weight.dtype != torch.bfloat16:
+        raise TypeError("weight must be a CUDA bfloat16 tensor")
+    w = weight.detach()
+    if w.ndim == 4:
+        w = w.reshape(w.shape[0], w.shape[1] * w.shape[2], w.shape[3])
+    if w.ndim != 3:
+        raise ValueError("weight must be [E_local, N, K]")
+    if fuse_swiglu:
+        F = w.shape[1] // 2
+        if F % 64:
+            raise ValueError("fuse_swiglu needs intermediate_dim to be a multiple of 64")
+        w = w.index_select(1, interleave_index(F, w.device))
+    return w.contiguous()
+
+
+def quantize_mxfp8_weight(weight: torch.Tensor, *, inference: bool, fuse_swiglu: bool):
+    """Body of ``dist_moe::prepare_mxfp8_weight`` (dist_moe/_blockscaled.py:2870-2913): shape-only contract."""
+    return _quantize_weight(_as_enk(weight, fuse_swiglu), "mxfp8", inference)
+
+
+def quantize_nvfp4_weight(weight: torch.Tensor, *, fuse_swiglu: bool):
+    """Body of ``dist_moe::prepare_nvfp4_weight`` (dist_moe/_blockscaled.py:140-196)."""
+    return _quantize_weight(_as_enk(weight, fuse_swiglu), "nvfp4", True)
 
 
 class _Layout:
@@ -450,7 +496,8 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
     return out, c
 
 
-def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_param, grad_out, options, needs):
+def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_param, grad_out, options, needs,
+                    wgrad_explicit=(None, None)):
     from ._bf16 import _wgrad_destination
 
     cfg = state.config
@@ -489,7 +536,7 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
     owners = options.wgrad_parameter_owners or (None, None)
     if need_w2:
         nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dyg), recv, R, D, _ptr(dyc), _ptr(dycsf), 1, st), "dm_quant_mxfp8_col(dy)")
-        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1])
+        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1])
         nat.check(nat.lib.dm_gemm_blockscaled_wgrad(dyc, dycsf, full(c.h2_col), full(c.h2_col_sf), dst.data_ptr(),
                                                     int(dst.dtype == torch.float32), acc, offs, el, R, D, F, None,
                                                     state.num_sms, status, st), "dm_gemm_blockscaled_wgrad(w2)")
@@ -507,7 +554,7 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
     if need_w13:
         nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dh1), recv, R, 2 * F, _ptr(d1c), _ptr(d1csf), 1, st),
                   "dm_quant_mxfp8_col(dh1)")
-        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0])
+        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0])
         nat.check(nat.lib.dm_gemm_blockscaled_wgrad(d1c, d1csf, full(c.x_col), full(c.x_col_sf), dst.data_ptr(),
                                                     int(dst.dtype == torch.float32), acc, offs, el, R, 2 * F, D, None,
                                                     state.num_sms, status, st), "dm_gemm_blockscaled_wgrad(w13)")

@@ -298,7 +298,10 @@ def run_ours(args):
         "flops_per_launch": flops_step / 6.0,
         "avg_launch_ms": gemm_ms / n_gemm if n_gemm else None,
         "launches": n_gemm,
-        "traffic": None,
+        # dram__bytes_read + dram__bytes_write per working launch, from one ncu capture of this exact workload at
+        # N=1 (5.88 GB per step over 6 launches; summary under profiles/).  Not captured for N>1.
+        "traffic": 0.98e9 if world == 1 else None,
+        "traffic_unit": "bytes per launch (ncu dram read+write, N=1 capture)",
     }
 
     if rank == 0:
@@ -378,15 +381,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--separate-gather", action="store_true",
                     help="gather routed rows with a separate kernel instead of inside the GEMM launches")
-    ap.add_argument("--single-cta", action="store_true",
-                    help="run forward / input-gradient GEMMs on the single-CTA kernel instead of CTA pairs")
+    ap.add_argument("--cta-pairs", action="store_true",
+                    help="run forward / input-gradient GEMMs on the CTA-pair kernel (tcgen05 cta_group::2)")
     ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
     args = ap.parse_args()
-    if args.single_cta and args.impl == "ours":
+    if args.cta_pairs and args.impl == "ours":
         from dist_moe_b200 import _native
 
-        _native.lib.dm_set_gemm_pairs(0)
+        _native.lib.dm_set_gemm_pairs(1)
     if args.micro:
         run_micro(args)
     elif args.impl == "reference":

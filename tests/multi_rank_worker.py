@@ -100,7 +100,10 @@ def run_block_scaled_case(dm, group, rank, world, dev, fmt, T, D, F, K, E):
 
 def run_mxfp8_training_case(dm, group, rank, world, dev, T, D, F, K, E):
     """MXFP8 forward + backward across ranks (bf16 rows dispatched, quantised by the expert rank); the reference's
-    two-rank block-scaled shape and bounds (tests/test_dist_moe.py:317-322: relative L2 < 0.075, cosine > 0.9975)."""
+    two-rank block-scaled widths and bounds (tests/test_dist_moe.py:317-322: relative L2 < 0.075, cosine > 0.9975).
+    The algorithm's own error at these widths is about 0.065 (two E4M3 GEMMs in sequence), so the cosine floor
+    (equivalent to a relative L2 of 0.0707) leaves little room; 512 tokens per rank instead of the reference's 128
+    keep the sampling noise of the aggregate (about 0.065 / sqrt(2 * samples)) well inside that room."""
     xs, ids, scores, w13, w2 = inputs(world, T, D, F, K, E, False)
     xs = [(x.float() * 0.1).bfloat16() for x in xs]
     el = E // world
@@ -149,7 +152,7 @@ def main():
     run_case(dm, group, rank, world, dev, 300, 512, 384, 4, 8 * world, False, 1.0)
     run_block_scaled_case(dm, group, rank, world, dev, "MXFP8_E4M3", 200, 512, 256, 4, 4 * world)
     run_block_scaled_case(dm, group, rank, world, dev, "NVFP4", 130, 512, 256, 2, 4 * world)
-    run_mxfp8_training_case(dm, group, rank, world, dev, 128, 1024, 1024, 2, 2 * world)
+    run_mxfp8_training_case(dm, group, rank, world, dev, 512, 1024, 1024, 2, 2 * world)
     dist.barrier()
     if rank == 0:
         print("MULTI_RANK_OK", world, flush=True)

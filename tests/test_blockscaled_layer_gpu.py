@@ -133,7 +133,7 @@ def _oracle_grads(x, ids, scores, w13, w2, clamped):
 
 
 @pytest.mark.parametrize("T,D,F,K,E,clamped,elementwise", [
-    (128, 1024, 1024, 2, 4, False, True),
+    (384, 1024, 1024, 2, 4, False, True),
     (200, 512, 384, 4, 8, False, False),
     (64, 256, 256, 2, 4, True, False),
     (16, 256, 128, 2, 8, False, False),      # experts with no rows

@@ -123,12 +123,13 @@ def cpu_baseline(steps: int, warmup: int, threads: int | None = None):
     w13 = w13.requires_grad_(True)
     w2 = w2.requires_grad_(True)
     times = []
+    grad_out = torch.randn(CPU_SAMPLE_TOKENS, D, generator=torch.Generator().manual_seed(4000)).bfloat16()
     for i in range(warmup + steps):
         xs = x.clone().requires_grad_(True)
         ss = scores.clone().requires_grad_(True)
         t0 = time.perf_counter()
         out = oracle_moe.moe_forward(xs, ids, ss, w13, w2)
-        out.float().sum().backward()
+        out.backward(grad_out)
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
@@ -219,12 +220,14 @@ def run_ours(args):
     ids = ids_h.to(dev)
     scores = scores_h.to(dev)
     out_host = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
+    # upstream gradient of the layer output: an input of the backward pass, as in a model step (seeded, resident)
+    grad_out = torch.randn(T, D, generator=torch.Generator().manual_seed(4000 + rank)).bfloat16().to(dev)
 
     def step(xd, idd, sd):
         xs = xd.requires_grad_(True)
         ss = sd.requires_grad_(True)
         out = dm.routed_experts(xs, idd, ss, w13, w2, ctx, options=opts)
-        out.float().sum().backward()
+        out.backward(grad_out)
         return out
 
     def step_e2e():

@@ -29,7 +29,7 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kStages = 4;
-constexpr int kGemmThreads = 448;  // TMA warp, MMA warp, eight epilogue warps, four gather warps
+constexpr int kGemmThreads = 480;  // TMA warp, MMA warp, eight epilogue warps, four gather warps, one accumulator watcher
 constexpr int kGatherWarps = 4;
 constexpr int kMaxGroups = 256;
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
@@ -314,6 +314,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       }
       __syncwarp();
     }
+  } else if (warp == 14) {
+    // ======================= accumulator watcher =======================
+    // One warp polls the accumulator-ready barriers on behalf of the eight epilogue warps and releases them
+    // through a hardware named barrier: the epilogue warps then sleep without taking issue slots from the
+    // MMA-issuing and TMA-issuing threads that share their schedulers.  The watcher arrives for every tile,
+    // also after a timeout, so that no epilogue warp is left blocked.
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (ok && lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      asm volatile("bar.arrive %0, %1;" ::"r"(1 + buf), "r"(8 * 32 + 32) : "memory");
+    }
   } else if (warp >= 10) {
     // ======================= gather (fused dispatch) =======================
     // Row blocks of 128 rows are dealt round-robin to the CTAs in ascending order, the order in which
@@ -382,8 +397,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      if (lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + buf), "r"(8 * 32 + 32) : "memory");  // released by the watcher
+      (void)acc_phase;
+      ok = abort_flag == 0;
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;

@@ -43,6 +43,7 @@ enum GemmMode : int { kFprop = 0, kDgrad = 1, kWgrad = 2 };
 struct GemmParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
+  CUtensorMap tm_b256;  // forward without SwiGLU pairing: one 256-row box per stage
   const int64_t* a_off;  // device byte offsets (may be null = 0)
   const int64_t* b_off;
   const int64_t* c_off;
@@ -223,8 +224,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                   r0 = t.e * p.N + t.n_blk * kBN;
                   r1 = r0 + kBN / 2;
                 }
-                tma_load_2d(sb, &p.tm_b, kb * kBK, r0, &full_bar[stage]);
-                tma_load_2d(sb + kBBytes / 2, &p.tm_b, kb * kBK, r1, &full_bar[stage]);
+                if (p.fused) {
+                  tma_load_2d(sb, &p.tm_b, kb * kBK, r0, &full_bar[stage]);
+                  tma_load_2d(sb + kBBytes / 2, &p.tm_b, kb * kBK, r1, &full_bar[stage]);
+                } else {
+                  tma_load_2d(sb, &p.tm_b256, kb * kBK, r0, &full_bar[stage]);
+                }
               } else {
 #pragma unroll
                 for (int b = 0; b < kBN / 64; ++b)
@@ -617,6 +622,8 @@ static int fprop_impl(dm_operand a, const void* w, dm_operand c, dm_operand h2, 
   int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
   if (rc != kRcOk) return rc;
   rc = encode_2d(&p.tm_b, w, static_cast<int64_t>(e_local) * N, Kd, kBN / 2);
+  if (rc != kRcOk) return rc;
+  rc = encode_2d(&p.tm_b256, w, static_cast<int64_t>(e_local) * N, Kd, kBN);
   if (rc != kRcOk) return rc;
   p.a_off = a.offset;
   p.c_off = c.offset;

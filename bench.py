@@ -1,6 +1,6 @@
 """Benchmark of the routed-expert layer (BF16 training layer, forward + backward).
 
-Workload (``BASELINE.json`` configs[1]): T=4096 tokens per rank, D=2048, F=1408, E=64 experts
+Workload (the reference's EP8 BF16 training configuration): T=4096 tokens per rank, D=2048, F=1408, E=64 experts
 sharded over the ranks (E_local = 64 / N), top-6 softmax routing renormalised to 1, plain
 SwiGLU, weight gradients accumulated in place into ``parameter.grad``.  Inputs are seeded
 synthetic data: x ~ N(0,1), weights ~ N(0,0.02), router logits ~ N(0,1).

@@ -1,8 +1,8 @@
 """Generate golden vectors by executing the reference's own code on the CPU.
 
-Run in a container that has the reference checkout (default ``/root/reference``):
+Run where a checkout of the reference is available and pass its location:
 
-    python tests/golden/gen_golden.py [--reference /root/reference]
+    python tests/golden/gen_golden.py --reference <path to the dist_moe checkout>
 
 What runs, unmodified, from the reference:
 * ``dist_moe.plan_memory`` (pure Python) -> ``plan_memory.json``;
@@ -345,7 +345,7 @@ def gen_quant(ref):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("DIST_MOE_REFERENCE", "reference"))
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)

@@ -162,7 +162,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   const int64_t a_off = p.a_off ? *p.a_off : 0;
   const int64_t b_off = p.b_off ? *p.b_off : 0;
 
-  if (warp == 0) {
+  // Weight gradient: a stage is six 64 x 64 boxes, and one thread cannot issue six TMA loads in the time the
+  // tensor cores need for the stage, so the (otherwise idle) warps 10 and 11 issue the boxes of the second
+  // operand; warp 0 arms the stage's barrier and loads the first operand.
+  const int wgrad_part = (kMode == kWgrad) ? (warp == 0 ? 0 : (warp == 10 ? 1 : (warp == 11 ? 2 : -1))) : -1;
+  if (warp == 0 || wgrad_part > 0) {
     // ======================= TMA producer =======================
     int stage = 0;
     uint32_t phase = 0;
@@ -203,15 +207,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           if (ok) {
             uint8_t* sa = smem + stage * kStageBytes;
             uint8_t* sb = sa + kABytes;
-            mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+            if (kMode != kWgrad || wgrad_part == 0) mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
             if (kMode == kWgrad) {
               const int row = t.row0 + kb * kBK;
+              if (wgrad_part == 0) {
 #pragma unroll
-              for (int b = 0; b < kBM / 64; ++b)
-                tma_load_3d(sa + b * 8192, &p.tm_a, 0, a_line0 + t.m_blk * (kBM / 64) + b, row, &full_bar[stage]);
+                for (int b = 0; b < kBM / 64; ++b)
+                  tma_load_3d(sa + b * 8192, &p.tm_a, 0, a_line0 + t.m_blk * (kBM / 64) + b, row, &full_bar[stage]);
+              } else {
+                const int b0 = (wgrad_part - 1) * 2;
 #pragma unroll
-              for (int b = 0; b < kBN / 64; ++b)
-                tma_load_3d(sb + b * 8192, &p.tm_b, 0, b_line0 + t.n_blk * (kBN / 64) + b, row, &full_bar[stage]);
+                for (int b = b0; b < b0 + 2; ++b)
+                  tma_load_3d(sb + b * 8192, &p.tm_b, 0, b_line0 + t.n_blk * (kBN / 64) + b, row, &full_bar[stage]);
+              }
             } else {
               tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
               if (kMode == kFprop) {
@@ -271,24 +279,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         tcgen05_fence_after();
         uint8_t* sa = smem + stage * kStageBytes;
         uint8_t* sb = sa + kABytes;
+        int ksteps = kBK / 16;  // K = 16 steps to issue for this stage
         if (kMode == kWgrad) {
           const int valid = (t.row_end - t.row0) - kb * kBK;  // rows of this chunk that belong to the expert
           if (valid < kBK) {
-            // Rows [valid, 64) of every 64x64 box are one contiguous byte range.
-            const int vec_per_box = (kBK - valid) * 8;
-            const int boxes = (kBM + kBN) / 64;
-            for (int i = lane; i < boxes * vec_per_box; i += 32) {
-              const int box = i / vec_per_box, v = i - box * vec_per_box;
-              reinterpret_cast<uint4*>(sa + box * 8192 + valid * 128)[v] = make_uint4(0, 0, 0, 0);
+            // Ragged last chunk: only the K = 16 steps that hold rows of this expert are issued, and the rows
+            // between the expert's end and the end of its last step (at most 15) are zeroed in shared memory.
+            // Row r of every 64 x 64 box is one contiguous 128-byte line.
+            ksteps = (valid + 15) >> 4;
+            const int vec_per_box = (ksteps * 16 - valid) * 8;
+            if (vec_per_box > 0) {
+              const int boxes = (kBM + kBN) / 64;
+              for (int i = lane; i < boxes * vec_per_box; i += 32) {
+                const int box = i / vec_per_box, v = i - box * vec_per_box;
+                reinterpret_cast<uint4*>(sa + box * 8192 + valid * 128)[v] = make_uint4(0, 0, 0, 0);
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
             }
-            fence_proxy_async_smem();
-            __syncwarp();
           }
         }
         if (lane == 0) {
           const uint32_t a_addr = smem_u32(sa), b_addr = smem_u32(sb);
 #pragma unroll
           for (int j = 0; j < kBK / 16; ++j) {
+            if (kMode == kWgrad && j >= ksteps) break;
             uint64_t da, db;
             if (kMode == kWgrad) {
               da = umma_smem_desc(a_addr + j * 2048, 8192, 1024);

@@ -466,9 +466,8 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
     none = nat.Operand(None, 0, None)
     full = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
     nat.check(nat.lib.dm_gather_rows(c.fwd.data_ptr(), recv, _ptr(xg), None, D * 2, R, None, st), "dm_gather_rows")
-    nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(xg), recv, R, D, _ptr(xq), 0, _ptr(xsf), 0, 1, st), "dm_quant_mxfp8_row(x)")
-    nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(xg), recv, R, D, c.x_col.data_ptr(), c.x_col_sf.data_ptr(), 1, st),
-              "dm_quant_mxfp8_col(x)")
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(xg), recv, R, D, _ptr(xq), _ptr(xsf), c.x_col.data_ptr(),
+                                            c.x_col_sf.data_ptr(), st), "dm_quant_mxfp8_rowcol(x)")
     nat.check(nat.lib.dm_gemm_blockscaled(0, xq, xsf, p13.fprop_data.data_ptr(), p13.fprop_scale.data_ptr(), full(c.h1),
                                           none, None, none, None, c.offsets.data_ptr(), el, R, 2 * F, D, 0, 0, 1.0, 0.0,
                                           None, state.num_sms, status, st), "dm_gemm_blockscaled(w13)")
@@ -477,9 +476,8 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
         clip.zero_()
     nat.check(nat.lib.dm_swiglu_fwd(c.h1.data_ptr(), None, _ptr(h2), None, recv, R, F, clamped, alpha, limit,
                                     nat.ptr(clip), float(options.swiglu_clip_limit), None, st), "dm_swiglu_fwd")
-    nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(h2), recv, R, F, _ptr(hq), 0, _ptr(hsf), 0, 1, st), "dm_quant_mxfp8_row(h2)")
-    nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(h2), recv, R, F, c.h2_col.data_ptr(), c.h2_col_sf.data_ptr(), 1, st),
-              "dm_quant_mxfp8_col(h2)")
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(h2), recv, R, F, _ptr(hq), _ptr(hsf), c.h2_col.data_ptr(),
+                                            c.h2_col_sf.data_ptr(), st), "dm_quant_mxfp8_rowcol(h2)")
     nat.check(nat.lib.dm_gemm_blockscaled(0, hq, hsf, p2.fprop_data.data_ptr(), p2.fprop_scale.data_ptr(), none, none,
                                           c.sct.data_ptr(), none, None, c.offsets.data_ptr(), el, R, D, F, 0, 0, 1.0,
                                           0.0, None, state.num_sms, status, st), "dm_gemm_blockscaled(w2)")
@@ -528,14 +526,18 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
     # ---- W2 ----------------------------------------------------------------------------------
     nat.check(nat.lib.dm_gather_rows(c.sct.data_ptr(), recv, _ptr(dyg), None, D * 2, R, None, st),
               "dm_gather_rows(grad_h3)")
-    nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dyg), recv, R, D, _ptr(dyq), 0, _ptr(dysf), 0, 1, st), "dm_quant_mxfp8_row(dy)")
+    if need_w2:
+        nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(dyg), recv, R, D, _ptr(dyq), _ptr(dysf), _ptr(dyc), _ptr(dycsf), st),
+                  "dm_quant_mxfp8_rowcol(dy)")
+    else:
+        nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dyg), recv, R, D, _ptr(dyq), 0, _ptr(dysf), 0, 1, st),
+                  "dm_quant_mxfp8_row(dy)")
     nat.check(nat.lib.dm_gemm_blockscaled_dgrad(dyq, dysf, c.p2.fprop_data.data_ptr(), c.p2.dgrad_scale.data_ptr(), dh2,
                                                 None, offs, el, R, F, D, None, state.num_sms, status, st),
               "dm_gemm_blockscaled_dgrad(w2)")
     grad_w13 = grad_w2 = None
     owners = options.wgrad_parameter_owners or (None, None)
     if need_w2:
-        nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dyg), recv, R, D, _ptr(dyc), _ptr(dycsf), 1, st), "dm_quant_mxfp8_col(dy)")
         dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1])
         nat.check(nat.lib.dm_gemm_blockscaled_wgrad(dyc, dycsf, full(c.h2_col), full(c.h2_col_sf), dst.data_ptr(),
                                                     int(dst.dtype == torch.float32), acc, offs, el, R, D, F, None,
@@ -544,16 +546,21 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
     # ---- SwiGLU backward, W13 ---------------------------------------------------------------
     nat.check(nat.lib.dm_swiglu_bwd(c.h1.data_ptr(), None, _ptr(dh2), None, _ptr(dh1), None, recv, R, F, clamped, alpha,
                                     limit, st), "dm_swiglu_bwd")
-    if need_x:
+    if need_x and need_w13:
+        nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(dh1), recv, R, 2 * F, _ptr(d1q), _ptr(d1sf), _ptr(d1c), _ptr(d1csf),
+                                                st), "dm_quant_mxfp8_rowcol(dh1)")
+    elif need_x:
         nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dh1), recv, R, 2 * F, _ptr(d1q), 0, _ptr(d1sf), 0, 1, st),
                   "dm_quant_mxfp8_row(dh1)")
+    elif need_w13:
+        nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dh1), recv, R, 2 * F, _ptr(d1c), _ptr(d1csf), 1, st),
+                  "dm_quant_mxfp8_col(dh1)")
+    if need_x:
         nat.check(nat.lib.dm_gemm_blockscaled_dgrad(d1q, d1sf, c.p13.fprop_data.data_ptr(),
                                                     c.p13.dgrad_scale.data_ptr(), none, c.bwd.data_ptr(), offs, el, R, D,
                                                     2 * F, None, state.num_sms, status, st),
                   "dm_gemm_blockscaled_dgrad(w13)")
     if need_w13:
-        nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dh1), recv, R, 2 * F, _ptr(d1c), _ptr(d1csf), 1, st),
-                  "dm_quant_mxfp8_col(dh1)")
         dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0])
         nat.check(nat.lib.dm_gemm_blockscaled_wgrad(d1c, d1csf, full(c.x_col), full(c.x_col_sf), dst.data_ptr(),
                                                     int(dst.dtype == torch.float32), acc, offs, el, R, 2 * F, D, None,

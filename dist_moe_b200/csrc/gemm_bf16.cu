@@ -257,7 +257,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     }
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
+    // One thread runs the whole issue loop: a poll of the stage barrier, the K = 16 MMAs with descriptor words
+    // derived by integer adds, one commit.  The other lanes join only where a weight-gradient tile ends in a
+    // ragged chunk whose tail rows must be zeroed in shared memory.  (Per-stage warp synchronisation in this
+    // loop costs about a quarter of the tensor time of a stage; tiles of the weight gradient are only a few
+    // stages long, so it mattered most there.)
     constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, kMode == kWgrad ? 1 : 0, kMode == kFprop ? 0 : 1);
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+    constexpr uint32_t kLboK = (16u >> 4) << 16, kLboMN = (8192u >> 4) << 16;
+    constexpr uint32_t a_step = kMode == kWgrad ? (2048u >> 4) : (32u >> 4);
+    constexpr uint32_t b_step = kMode == kFprop ? (32u >> 4) : (2048u >> 4);
+    const uint32_t a_lo0 = ((smem_u32(smem) & 0x3ffffu) >> 4) | (kMode == kWgrad ? kLboMN : kLboK);
+    const uint32_t b_lo0 = (((smem_u32(smem) + kABytes) & 0x3ffffu) >> 4) | (kMode == kFprop ? kLboK : kLboMN);
+    const uint32_t empty0 = smem_u32(&empty_bar[0]), tfull0 = smem_u32(&tmem_full_bar[0]);
     int stage = 0;
     uint32_t phase = 0;
     int e = 0;
@@ -267,68 +279,118 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      if (lane == 0) ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      tcgen05_fence_after();
       const uint32_t d_tmem = tmem_base + buf * kBN;
-      for (int kb = 0; kb < t.k_iters; ++kb) {
-        if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+      // weight gradient: rows of the last chunk that belong to the expert, and whether its tail needs zeroing
+      const int valid_last = kMode == kWgrad ? (t.row_end - t.row0) - (t.k_iters - 1) * kBK : kBK;
+      const bool ragged = kMode == kWgrad && t.k_iters > 0 && (valid_last & 15) != 0;
+      if (ragged && t.k_iters <= 16) {
+        // Short ragged tile: the lanes that must zero the tail stay in step with the issuing lane for the
+        // whole tile (re-joining lanes that waited through a single-thread loop costs about a microsecond,
+        // which only long tiles can afford).
+        if (lane == 0) ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         tcgen05_fence_after();
-        uint8_t* sa = smem + stage * kStageBytes;
-        uint8_t* sb = sa + kABytes;
-        int ksteps = kBK / 16;  // K = 16 steps to issue for this stage
-        if (kMode == kWgrad) {
-          const int valid = (t.row_end - t.row0) - kb * kBK;  // rows of this chunk that belong to the expert
-          if (valid < kBK) {
-            // Ragged last chunk: only the K = 16 steps that hold rows of this expert are issued, and the rows
-            // between the expert's end and the end of its last step (at most 15) are zeroed in shared memory.
-            // Row r of every 64 x 64 box is one contiguous 128-byte line.
-            ksteps = (valid + 15) >> 4;
-            const int vec_per_box = (ksteps * 16 - valid) * 8;
-            if (vec_per_box > 0) {
-              const int boxes = (kBM + kBN) / 64;
-              for (int i = lane; i < boxes * vec_per_box; i += 32) {
-                const int box = i / vec_per_box, v = i - box * vec_per_box;
-                reinterpret_cast<uint4*>(sa + box * 8192 + valid * 128)[v] = make_uint4(0, 0, 0, 0);
-              }
-              fence_proxy_async_smem();
-              __syncwarp();
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          int ksteps = kBK / 16;
+          if (kb == t.k_iters - 1) {
+            uint8_t* sa = smem + stage * kStageBytes;
+            ksteps = (valid_last + 15) >> 4;
+            const int vec_per_box = (ksteps * 16 - valid_last) * 8;
+            const int boxes = (kBM + kBN) / 64;
+            for (int i = lane; i < boxes * vec_per_box; i += 32) {
+              const int box = i / vec_per_box, v = i - box * vec_per_box;
+              reinterpret_cast<uint4*>(sa + box * 8192 + valid_last * 128)[v] = make_uint4(0, 0, 0, 0);
             }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+          if (lane == 0) {
+            const uint32_t a_lo = a_lo0 + stage * (kStageBytes >> 4), b_lo = b_lo0 + stage * (kStageBytes >> 4);
+            umma_bf16_lo(d_tmem, a_lo, b_lo, kDescHi, idesc, kb > 0 ? 1u : 0u);
+            if (ksteps > 1) umma_bf16_lo(d_tmem, a_lo + a_step, b_lo + b_step, kDescHi, idesc, 1u);
+            if (ksteps > 2) umma_bf16_lo(d_tmem, a_lo + 2 * a_step, b_lo + 2 * b_step, kDescHi, idesc, 1u);
+            if (ksteps > 3) umma_bf16_lo(d_tmem, a_lo + 3 * a_step, b_lo + 3 * b_step, kDescHi, idesc, 1u);
+            tcgen05_commit_addr(empty0 + stage * 8);
+          }
+          __syncwarp();
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(sa), b_addr = smem_u32(sb);
-#pragma unroll
-          for (int j = 0; j < kBK / 16; ++j) {
-            if (kMode == kWgrad && j >= ksteps) break;
-            uint64_t da, db;
-            if (kMode == kWgrad) {
-              da = umma_smem_desc(a_addr + j * 2048, 8192, 1024);
-            } else {
-              da = umma_smem_desc(a_addr + j * 32, 16, 1024);
-            }
-            if (kMode == kFprop) {
-              db = umma_smem_desc(b_addr + j * 32, 16, 1024);
-            } else {
-              db = umma_smem_desc(b_addr + j * 2048, 8192, 1024);
-            }
-            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          }
-          tcgen05_commit(&empty_bar[stage]);
-        }
+        if (!ok) break;
+        if (lane == 0) tcgen05_commit_addr(tfull0 + buf * 8);
         __syncwarp();
+        continue;
+      }
+      const int solo = ragged ? t.k_iters - 1 : t.k_iters;  // stages lane 0 handles alone
+      if (lane == 0) {
+        ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
+        tcgen05_fence_after();
+        int st = stage;
+        uint32_t ph = phase;
+        for (int kb = 0; kb < solo && ok; ++kb) {
+          ok = mbar_wait(&full_bar[st], ph, &abort_flag);
+          if (!ok) break;
+          const uint32_t a_lo = a_lo0 + st * (kStageBytes >> 4), b_lo = b_lo0 + st * (kStageBytes >> 4);
+          const int ksteps = (kMode == kWgrad && kb == t.k_iters - 1) ? (valid_last + 15) >> 4 : kBK / 16;
+          umma_bf16_lo(d_tmem, a_lo, b_lo, kDescHi, idesc, kb > 0 ? 1u : 0u);
+          if (ksteps > 1) umma_bf16_lo(d_tmem, a_lo + a_step, b_lo + b_step, kDescHi, idesc, 1u);
+          if (ksteps > 2) umma_bf16_lo(d_tmem, a_lo + 2 * a_step, b_lo + 2 * b_step, kDescHi, idesc, 1u);
+          if (ksteps > 3) umma_bf16_lo(d_tmem, a_lo + 3 * a_step, b_lo + 3 * b_step, kDescHi, idesc, 1u);
+          tcgen05_commit_addr(empty0 + st * 8);
+          if (++st == kStages) {
+            st = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      {  // every lane tracks the ring position
+        const int adv = stage + solo;
+        phase ^= static_cast<uint32_t>(adv / kStages) & 1u;
+        stage = adv % kStages;
+      }
+      if (ragged) {
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (ok && lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (ok) {
+          // Ragged last chunk: only the K = 16 steps that hold rows of this expert are issued, and the rows
+          // between the expert's end and the end of its last step (at most 15) are zeroed in shared memory.
+          // Row r of every 64 x 64 box is one contiguous 128-byte line.
+          uint8_t* sa = smem + stage * kStageBytes;
+          const int ksteps = (valid_last + 15) >> 4;
+          const int vec_per_box = (ksteps * 16 - valid_last) * 8;
+          const int boxes = (kBM + kBN) / 64;
+          for (int i = lane; i < boxes * vec_per_box; i += 32) {
+            const int box = i / vec_per_box, v = i - box * vec_per_box;
+            reinterpret_cast<uint4*>(sa + box * 8192 + valid_last * 128)[v] = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t a_lo = a_lo0 + stage * (kStageBytes >> 4), b_lo = b_lo0 + stage * (kStageBytes >> 4);
+            umma_bf16_lo(d_tmem, a_lo, b_lo, kDescHi, idesc, t.k_iters > 1 ? 1u : 0u);
+            if (ksteps > 1) umma_bf16_lo(d_tmem, a_lo + a_step, b_lo + b_step, kDescHi, idesc, 1u);
+            if (ksteps > 2) umma_bf16_lo(d_tmem, a_lo + 2 * a_step, b_lo + 2 * b_step, kDescHi, idesc, 1u);
+            if (ksteps > 3) umma_bf16_lo(d_tmem, a_lo + 3 * a_step, b_lo + 3 * b_step, kDescHi, idesc, 1u);
+            tcgen05_commit_addr(empty0 + stage * 8);
+          }
+        }
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (lane == 0) {
         if (t.k_iters > 0)
-          tcgen05_commit(&tmem_full_bar[buf]);
+          tcgen05_commit_addr(tfull0 + buf * 8);
         else
           mbar_arrive(&tmem_full_bar[buf]);
       }

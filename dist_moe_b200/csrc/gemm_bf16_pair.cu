@@ -71,26 +71,6 @@ struct Unit {
   int e, fb, tok0, valid, n_mma;
 };
 
-// One poll of an mbarrier phase (barrier given by its shared-memory address).
-__device__ __forceinline__ uint32_t mbar_poll(uint32_t bar_addr, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
-  return ok;
-}
-// Wait of the single-thread producer / issuer loops: a bare polling loop (a million polls, tens of
-// milliseconds), then the timed wait that can give up.  The common case costs a handful of instructions,
-// which matters because these threads issue every load and MMA of the CTA one instruction after another.
-__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar_addr, uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 20); ++i)
-    if (mbar_poll(bar_addr, parity)) return true;
-  return mbar_wait(bar, parity, abort_flag);
-}
 // Loads / MMAs taking precomputed shared-memory addresses and descriptor words.
 __device__ __forceinline__ void tma_load_2d_pair_a(uint32_t smem_dst, const void* tmap, int x, int y, uint32_t bar) {
   asm volatile(

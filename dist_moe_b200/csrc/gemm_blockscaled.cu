@@ -206,28 +206,31 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
     }
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
-    int stage = 0;
-    uint32_t phase = 0;
-    int e = 0, it = 0;
-    uint32_t kstep = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      if (lane == 0) ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      tcgen05_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * kBsBN;
-      for (int kb = 0; kb < t.k_iters; ++kb, ++kstep) {
-        if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    // One thread runs the whole issue loop (no per-stage warp synchronisation: a stage is only four MMAs).
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int e = 0, it = 0;
+      uint32_t kstep = 0;
+      bool ok = true;
+      const int a_mn = p.mode == 2, b_mn = p.mode != 0;
+      const uint32_t a_step = a_mn ? 4096u : 32u, b_step = b_mn ? 4096u : 32u;
+      const uint32_t idesc4 = umma_idesc_blockscaled(kBsBN, 1, 0, 0);
+      uint32_t idesc8[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) idesc8[j] = umma_idesc_blockscaled(kBsBN, 0, j, j, a_mn, b_mn);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
         if (!ok) break;
         tcgen05_fence_after();
-        if (lane == 0) {
-          uint8_t* sa = smem + stage * kBsStageBytes;
-          const uint32_t a_addr = smem_u32(sa), b_addr = a_addr + kBsABytes;
+        const uint32_t d_tmem = tmem_base + buf * kBsBN;
+        for (int kb = 0; kb < t.k_iters; ++kb, ++kstep) {
+          ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+          if (!ok) break;
+          const uint32_t a_addr = smem_u32(smem + stage * kBsStageBytes), b_addr = a_addr + kBsABytes;
           const uint32_t ssa = b_addr + kBsBBytes, ssb = ssa + kBsSfBytes;
           const uint32_t sfa_t = tmem_base + kBsSfTmemBase + (kstep & 1u) * 32u;
           const uint32_t sfb_t = sfa_t + 16u;
@@ -238,32 +241,28 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             // K-major: 32 bytes of K per step inside the 128-byte row; MN-major: four 8-row groups of 1 KiB.
-            const int a_mn = p.mode == 2, b_mn = p.mode != 0;
-            const uint64_t da = a_mn ? umma_smem_desc(a_addr + j * 4096, 16, 1024) : umma_smem_desc(a_addr + j * 32, 16, 1024);
-            const uint64_t db = b_mn ? umma_smem_desc(b_addr + j * 4096, 16, 1024) : umma_smem_desc(b_addr + j * 32, 16, 1024);
+            const uint64_t da = umma_smem_desc(a_addr + j * a_step, 16, 1024);
+            const uint64_t db = umma_smem_desc(b_addr + j * b_step, 16, 1024);
             const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
             if (p.fp4)
-              umma_nvf4(d_tmem, da, db, umma_idesc_blockscaled(kBsBN, 1, 0, 0), sfa_t + 4 * j, sfb_t + 4 * j, acc);
+              umma_nvf4(d_tmem, da, db, idesc4, sfa_t + 4 * j, sfb_t + 4 * j, acc);
             else
-              umma_mxf8(d_tmem, da, db, umma_idesc_blockscaled(kBsBN, 0, j, j, a_mn, b_mn), sfa_t, sfb_t, acc);
+              umma_mxf8(d_tmem, da, db, idesc8[j], sfa_t, sfb_t, acc);
           }
           tcgen05_commit(&empty_bar[stage]);
+          if (++stage == kBsStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
-        __syncwarp();
-        if (++stage == kBsStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-      if (!ok) break;
-      if (lane == 0) {
+        if (!ok) break;
         if (t.k_iters > 0)
           tcgen05_commit(&tmem_full_bar[buf]);
         else
           mbar_arrive(&tmem_full_bar[buf]);
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ======================= epilogue =======================
     const int quad = warp & 3;

@@ -33,6 +33,43 @@ __device__ __forceinline__ uint4 pack8_bf16(const uint32_t* r) {
                     pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
 }
 
+// Lean forms for the single-thread issue loops: barrier given by its shared-memory address, shared-memory
+// descriptors given by their lower word (address >> 4 | LBO >> 4 << 16) and a constant upper word.
+__device__ __forceinline__ uint32_t mbar_poll(uint32_t bar_addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
+  return ok;
+}
+// A bare polling loop (a million polls, tens of milliseconds), then the timed wait that can give up.
+__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar_addr, uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 20); ++i)
+    if (mbar_poll(bar_addr, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag);
+}
+__device__ __forceinline__ void umma_bf16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_addr(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+
 // 16-byte fire-and-forget reductions performed by L2 (each output tile has one owner CTA).
 __device__ __forceinline__ void red_add_f32x4(uint64_t addr, uint4 v) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(v.x)),

@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(256) mxfp8_slab_kernel(const __nv_bfloat16* __
                                                          int64_t max_rows, int C, uint8_t* __restrict__ q,
                                                          uint8_t* __restrict__ s0, uint8_t* __restrict__ s1,
                                                          int blocked, int s0_col_atoms, int s1_col_atoms,
-                                                         int64_t batch_rows) {
+                                                         int64_t batch_rows, uint8_t* __restrict__ q_row = nullptr,
+                                                         uint8_t* __restrict__ s_row = nullptr, int row_col_atoms = 0) {
   __shared__ float tile[32][257];
   __shared__ float col_amax[256];
   int64_t rows = num_rows ? *num_rows : max_rows;
@@ -185,6 +186,28 @@ __global__ void __launch_bounds__(256) mxfp8_slab_kernel(const __nv_bfloat16* __
         s0[blocked_offset(c, static_cast<int>(rb), s0_col_atoms)] = byte;
       else
         s0[static_cast<int64_t>(c) * ((max_rows + 31) / 32) + rb] = byte;
+    }
+  }
+  if (!kTile && q_row != nullptr) {
+    // Row-quantised copy from the same staged slab (1 x 32 blocks along the columns): warp b takes the
+    // 32-column block b, lane r its row r, so the shared-memory reads of a warp hit 32 different banks.
+    const int b = t >> 5, r = t & 31;
+    const int colb = col0 + b * 32;
+    if (row0 + r < rows && colb < C) {
+      float ra = 0.f;
+#pragma unroll 8
+      for (int j = 0; j < 32; ++j) ra = amax_nonfinite(ra, tile[r][b * 32 + j]);
+      float rrecip;
+      const uint8_t rbyte = mxfp8_scale(ra, rrecip);
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        w[j] = e4m3x4(tile[r][b * 32 + 4 * j] * rrecip, tile[r][b * 32 + 4 * j + 1] * rrecip,
+                      tile[r][b * 32 + 4 * j + 2] * rrecip, tile[r][b * 32 + 4 * j + 3] * rrecip);
+      uint4* dst = reinterpret_cast<uint4*>(q_row + (row0 + r) * C + colb);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      s_row[blocked_offset(row0 + r, colb >> 5, row_col_atoms)] = rbyte;
     }
   }
   // every thread converts one column of the slab: 32 rows, written as bytes into shared memory first
@@ -402,6 +425,21 @@ extern "C" int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_
   mxfp8_slab_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q),
       static_cast<uint8_t*>(scales), nullptr, blocked, atoms, 0, max_rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_mxfp8_rowcol(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q_row,
+                                     void* scales_row_blocked, void* q_col, void* scales_col_blocked, void* stream) {
+  if (!x || !q_row || !scales_row_blocked || !q_col || !scales_col_blocked || max_rows < 0 || C <= 0 || (C % 32) != 0)
+    return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
+  const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  const int row_atoms = static_cast<int>((C / 32 + 3) / 4);
+  mxfp8_slab_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q_col),
+      static_cast<uint8_t*>(scales_col_blocked), nullptr, 1, col_atoms, 0, max_rows, static_cast<uint8_t*>(q_row),
+      static_cast<uint8_t*>(scales_row_blocked), row_atoms);
   return static_cast<int>(cudaGetLastError());
 }
 

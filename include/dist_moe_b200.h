@@ -341,6 +341,12 @@ int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_t max_rows,
                        int64_t q_row_stride, void* scales, int64_t scale_row_stride, int blocked, void* stream);
 int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q, void* scales,
                        int blocked, void* stream);
+/* Row- and column-quantised copies of one bf16 [rows, C] matrix in a single pass over the input (the pair the
+ * MXFP8 training path needs of every activation: rows for the next GEMM, columns for the weight gradient; the
+ * reference emits both from its in-GEMM quantising producers, dist_moe/kernels/dist_blockscaled_grouped_gemm_kernel.py:112-222).
+ * Outputs are bit-identical to dm_quant_mxfp8_row (blocked scales) and dm_quant_mxfp8_col (blocked scales). C % 32 == 0. */
+int dm_quant_mxfp8_rowcol(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q_row,
+                          void* scales_row_blocked, void* q_col, void* scales_col_blocked, void* stream);
 int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
                           void* col_scales, int blocked, void* stream);
 int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,

@@ -156,3 +156,31 @@ def test_nvfp4_weight_and_swizzle():
     nat.check(nat.lib.dm_sf_swizzle(s[:n].contiguous().data_ptr(), sw.data_ptr(), n, k // 16, nat.stream_ptr()), "swz")
     torch.cuda.synchronize()
     np.testing.assert_array_equal(sw.cpu().numpy(), Q.to_blocked(rs[0]))
+
+
+@pytest.mark.parametrize("rows,cols,cap", [(96, 64, 128), (333, 512, 384), (4096, 1536, 4096)])
+def test_mxfp8_rowcol_equals_the_separate_kernels(rows, cols, cap):
+    """One pass producing both copies is bit-identical to the row kernel (blocked scales) and the column kernel
+    (blocked scales), which are held to the oracle above."""
+    nat = _nat()
+    x = _data(rows, cols, rows + 3, specials=False).to(DEV)
+    cnt = torch.tensor([rows], dtype=torch.int32, device=DEV)
+    ra, ca = (cols // 32 + 3) // 4, ((cap + 31) // 32 + 3) // 4
+    n_rs, n_cs = (cap + 127) // 128 * 128 * ra * 4, (cols + 127) // 128 * 128 * ca * 4
+    st = nat.stream_ptr()
+    q_r = torch.zeros(cap, cols, dtype=torch.uint8, device=DEV)
+    s_r = torch.zeros(n_rs, dtype=torch.uint8, device=DEV)
+    q_c = torch.zeros(cap, cols, dtype=torch.uint8, device=DEV)
+    s_c = torch.zeros(n_cs, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_row(x.data_ptr(), cnt.data_ptr(), cap, cols, q_r.data_ptr(), 0, s_r.data_ptr(), 0, 1, st), "row")
+    nat.check(nat.lib.dm_quant_mxfp8_col(x.data_ptr(), cnt.data_ptr(), cap, cols, q_c.data_ptr(), s_c.data_ptr(), 1, st), "col")
+    f_r, fs_r, f_c, fs_c = (torch.zeros_like(t) for t in (q_r, s_r, q_c, s_c))
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol(x.data_ptr(), cnt.data_ptr(), cap, cols, f_r.data_ptr(), fs_r.data_ptr(),
+                                            f_c.data_ptr(), fs_c.data_ptr(), st), "rowcol")
+    torch.cuda.synchronize()
+    assert torch.equal(f_r, q_r) and torch.equal(f_c, q_c)
+    assert torch.equal(fs_c, s_c)
+    # row scales: compare the entries of real rows (the row kernel leaves other positions untouched as well)
+    r, c = np.meshgrid(np.arange(rows), np.arange(cols // 32), indexing="ij")
+    idx = Q.blocked_scale_offset(r, c, ra)
+    np.testing.assert_array_equal(fs_r.cpu().numpy()[idx], s_r.cpu().numpy()[idx])

@@ -23,7 +23,7 @@ namespace dm {
 constexpr int kBsBM = 128;
 constexpr int kBsBN = 128;
 constexpr int kBsStages = 5;
-constexpr int kBsThreads = 192;
+constexpr int kBsThreads = 224;  // TMA warp, MMA warp, four epilogue warps, one accumulator watcher
 constexpr uint32_t kBsABytes = kBsBM * 128;  // 16 KiB
 constexpr uint32_t kBsBBytes = kBsBN * 128;  // 16 KiB
 constexpr uint32_t kBsSfBytes = 2048;        // up to 4 atoms for A and for B each
@@ -263,6 +263,20 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
       }
     }
     __syncwarp();
+  } else if (warp == 6) {
+    // ======================= accumulator watcher =======================
+    // Polls the accumulator-ready barriers for the epilogue warps and releases them through a hardware named
+    // barrier, so that waiting epilogue warps take no issue slots from the threads that issue loads and MMAs.
+    // It arrives for every tile, also after a timeout, so that no epilogue warp is left blocked.
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (ok && lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      asm volatile("bar.arrive %0, %1;" ::"r"(1 + buf), "r"(4 * 32 + 32) : "memory");
+    }
   } else {
     // ======================= epilogue =======================
     const int quad = warp & 3;
@@ -278,8 +292,9 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
       const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      if (lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + buf), "r"(4 * 32 + 32) : "memory");  // released by the watcher
+      (void)acc_phase;
+      ok = abort_flag == 0;
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBsBN;

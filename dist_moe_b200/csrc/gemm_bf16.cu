@@ -44,6 +44,7 @@ struct GemmParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
   CUtensorMap tm_b256;  // forward without SwiGLU pairing: one 256-row box per stage
+  CUtensorMap tm_c;     // wgrad: dW as [e_local][N][Kd], boxes of 32 rows x 64 bytes
   const int64_t* a_off;  // device byte offsets (may be null = 0)
   const int64_t* b_off;
   const int64_t* c_off;
@@ -487,10 +488,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;
 
       if (kMode == kWgrad) {
-        const int out_row = t.m_blk * kBM + row_in_tile;  // row of dW[e]
-        const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kd;
-        const uint64_t my_row =
-            out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
         for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
           uint32_t r[32];
           if (t.k_iters > 0) {
@@ -501,51 +498,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
           const int col = t.n_blk * kBN + c0;
-          if (p.out_fp32) {
+          // The staging tile is laid out as a 32-row x 64-byte box in the 64-byte swizzle: one thread
+          // hands it to the copy engine, which stores it or adds it to dW in L2 (accumulation rounds
+          // the fp32 accumulator to the stored type first, then L2 adds: no read round trip through
+          // the SM) and clips rows and columns past the matrix.
+          const int box_row = t.m_blk * kBM + quad * 32;
+          const bool box_ok = box_row < p.N;
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {  // 16 fp32 columns = 64 bytes per row
+          for (int sub = 0; sub < 2; ++sub) {
+            if (!p.out_fp32 && sub == 1) break;
+            if (lane == 0) bulk_wait_read();  // the engine has read the previous box out of the staging tile
+            __syncwarp();
+            if (p.out_fp32) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
                 stage64_put(stg, lane, j,
                             make_uint4(r[16 * sub + 4 * j], r[16 * sub + 4 * j + 1], r[16 * sub + 4 * j + 2],
                                        r[16 * sub + 4 * j + 3]));
-              __syncwarp();
+            } else {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int rr = i * 8 + (lane >> 2), j = lane & 3;
-                const uint4 v = stage64_get(stg, rr, j);
-                const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-                const int cc = col + 16 * sub + 4 * j;
-                if (rp != 0 && cc + 4 <= p.Kd) {
-                  const uint64_t dst = rp + static_cast<uint64_t>(cc) * 4;
-                  if (p.accumulate)
-                    red_add_f32x4(dst, v);
-                  else
-                    *reinterpret_cast<uint4*>(dst) = v;
-                }
-              }
-              __syncwarp();
+              for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
             }
-          } else {
-            // Accumulation rounds the fp32 accumulator to bf16 and lets L2 add it to the stored
-            // gradient (a 16-byte reduction per lane): no read round trip through the SM.
-#pragma unroll
-            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
+            fence_proxy_async_smem();
             __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = i * 8 + (lane >> 2), j = lane & 3;
-              const uint4 v = stage64_get(stg, rr, j);
-              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-              if (rp != 0 && col + 8 * j + 8 <= p.Kd) {
-                const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
-                if (p.accumulate)
-                  red_add_bf16x8(dst, v);
-                else
-                  *reinterpret_cast<uint4*>(dst) = v;
-              }
+            const int cc = col + (p.out_fp32 ? 16 * sub : 0);
+            if (lane == 0 && box_ok && cc < p.Kd) {
+              if (p.accumulate)
+                tma_reduce_add_3d(&p.tm_c, stg, cc, box_row, t.e);
+              else
+                tma_store_3d(&p.tm_c, stg, cc, box_row, t.e);
+              bulk_commit();
             }
-            __syncwarp();
           }
         }
       } else {
@@ -628,6 +611,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
     }
+    if (kMode == kWgrad && lane == 0) bulk_wait_all();  // staged boxes are out of shared memory and written
   }
 
   // ---- teardown ---------------------------------------------------------------
@@ -798,6 +782,7 @@ extern "C" int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_f
     return kRcBadArg;
   if (e_local > kMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
   if ((N % 64) != 0 || (Kd % 64) != 0) return kRcUnsupportedShape;
+  if ((reinterpret_cast<uintptr_t>(dw) % 16) != 0) return kRcBadArg;
   GemmParams p{};
   int rc = encode_arena(&p.tm_a, dy, N * 2, max_rows + 256, kBK);
   if (rc != kRcOk) return rc;
@@ -814,5 +799,7 @@ extern "C" int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_f
   p.Kd = static_cast<int>(Kd);
   p.out_fp32 = out_is_fp32 ? 1 : 0;
   p.accumulate = accumulate ? 1 : 0;
+  rc = encode_out_3d(&p.tm_c, dw, e_local, N, Kd, out_is_fp32 != 0);
+  if (rc != kRcOk) return rc;
   return launch<kWgrad>(p, num_sms, static_cast<cudaStream_t>(stream));
 }

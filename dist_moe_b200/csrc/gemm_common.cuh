@@ -82,6 +82,25 @@ __device__ __forceinline__ void red_add_bf16x8(uint64_t addr, uint4 v) {
                : "memory");
 }
 
+// Bulk tensor store and reduce-add of one staged box (shared memory -> global), issued by one thread.  The
+// staged bytes must have been made visible to the async proxy (fence_proxy_async_smem by every writer, then
+// a barrier) and stay untouched until bulk_wait_read has returned.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const void* tmap, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------
 // Host side: tensor-map encoding through the driver entry point (no link-time
 // dependency on libcuda) and launch.
@@ -130,6 +149,22 @@ static inline int encode_arena(CUtensorMap* tm, const dm_operand& op, int64_t pi
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, op.base, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
+}
+
+// Weight-gradient destination [groups][rows][cols] (bf16 or fp32), boxes of 32 rows x 64 bytes in the
+// 64-byte swizzle: the layout of an epilogue warp's staging tile.
+static inline int encode_out_3d(CUtensorMap* tm, void* base, int64_t groups, int64_t rows, int64_t cols, bool fp32) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return kRcNoDriver;
+  const cuuint64_t esz = fp32 ? 4 : 2;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * esz, static_cast<cuuint64_t>(cols) * rows * esz};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(64 / esz), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
 }

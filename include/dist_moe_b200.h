@@ -211,7 +211,9 @@ int dm_broadcast_and_scale(const void* grad_out, const void* scores, int scores_
  *  dm_gemm_dgrad:   C[r, :] = A[r, :] * W[e]             W = [e_local, Kd, N] (N contiguous), A = [rows, Kd]
  *     scatter_ptrs as above.
  *  dm_gemm_wgrad:   dW[e] (+)= dY[e]^T * X[e]            dY = [rows, N], X = [rows, Kd], dW = [e_local, N, Kd]
- *     out_is_fp32 selects fp32 or bf16 dW; accumulate != 0 adds into dW.
+ *     out_is_fp32 selects fp32 or bf16 dW; accumulate != 0 adds into dW (the fp32 accumulator is rounded to
+ *     dW's type and added in L2 by bulk tensor reduce-adds, the reference's TMA reduce-add store).  dW must be
+ *     16-byte aligned.
  * ------------------------------------------------------------------------- */
 typedef struct {
   void* base;             /* arena (or any 256-byte aligned allocation) */

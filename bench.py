@@ -456,6 +456,144 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+INFERENCE_WORKLOADS = {
+    # name: (format, T, D, F, E, K, clamped SwiGLU, routing)
+    "nvfp4-decode": ("NVFP4", 128, 7168, 2048, 256, 8, False, "sigmoid"),
+    "nvfp4-prefill": ("NVFP4", 8192, 7168, 2048, 256, 8, False, "sigmoid"),
+    # the reference rejects D = F = 2880 for MXFP8 (dimensions must be multiples of 128); 2816 is the nearest legal shape
+    "mxfp8-infer": ("MXFP8_E4M3", 4096, 2816, 2816, 128, 4, True, "uniform"),
+}
+
+
+def run_inference(args):
+    """Forward-only inference workloads with prepared block-scaled weights, timed as CUDA-graph replays.
+
+    Every replay is bracketed by its own pair of CUDA events, so the line carries the median (p50) and the
+    90th percentile of the layer time next to the whole-job tokens/s.  Experts are sharded over the ranks
+    (E_local = E / N) and every rank contributes T tokens, as in the training workload.
+    """
+    import torch.distributed as dist
+
+    import dist_moe_b200 as dm
+
+    fmt, Tn, Dn, Fn, En, Kn, clamped, routing = INFERENCE_WORKLOADS[args.workload]
+    if args.tokens:
+        Tn = args.tokens
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    e_local = En // world
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    x = torch.randn(Tn, Dn, device=dev, generator=g).bfloat16()
+    logits = torch.randn(Tn, En, device=dev, generator=g)
+    if routing == "sigmoid":   # sigmoid scores of the top-k logits, not renormalised
+        top = torch.topk(logits, Kn)
+        scores, ids = torch.sigmoid(top.values).float(), top.indices
+    else:                      # uniform random distinct experts, softmax-renormalised scores
+        top = torch.topk(logits, Kn)
+        scores, ids = torch.softmax(top.values, -1).float(), top.indices
+    bs = dm.BlockScaledConfig(format=getattr(dm.BlockScaledFormat, fmt))
+    extra = {"activation": "swiglu_clamped", "swiglu_limit": 7.0} if clamped else {}
+    rows_max = int(torch.bincount((ids // e_local).flatten(), minlength=world).max().item())
+    if world > 1:
+        t = torch.tensor([rows_max], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rows_max = int(t.item())
+    # the busiest rank's received rows relative to T*K (the plan adds the per-expert padding to 128 rows itself)
+    factor = min(float(world), max(1.0, 1.05 * rows_max / float(Tn * Kn)))
+    cfg = dm.Config(max_num_local_input_tokens=Tn, hidden_dim=Dn, intermediate_dim=Fn, top_k=Kn, num_experts=En,
+                    max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0, block_scaled=bs,
+                    device_scratch_capacity_factor=factor, **extra)
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    gw = torch.Generator(device=dev).manual_seed(2027 + rank)
+    w13 = (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16()
+    p13 = dm.prepare_block_scaled_weight(w13, cfg, fuse_swiglu=True, inference=True)
+    del w13
+    w2 = (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16()
+    p2 = dm.prepare_block_scaled_weight(w2, cfg, inference=True)
+    del w2
+    torch.cuda.empty_cache()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(3):
+            dm.routed_experts(x, ids, scores, p13, p2, ctx)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.no_grad(), torch.cuda.graph(graph):
+        out = dm.routed_experts(x, ids, scores, p13, p2, ctx)
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    ctx.check_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sync_all()
+    sampler.mark()
+    pairs = []
+    for _ in range(args.steps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        pairs.append((s, e))
+    sync_all()
+    sampler.mark()
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.check_status()
+    times = sorted(s.elapsed_time(e) for s, e in pairs)
+    stats = torch.tensor([times[len(times) // 2], times[min(len(times) - 1, (len(times) * 9) // 10)],
+                          sum(times) / len(times)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    p50, p90, mean = (float(v) for v in stats.tolist())
+    rows = int((ids // e_local == rank).sum().item()) if world > 1 else Tn * Kn
+    bits = 4.5 if fmt == "NVFP4" else 8.25   # payload + block scales per weight element
+    hit = int(torch.unique(ids[(ids // e_local) == rank]).numel()) if world > 1 else int(torch.unique(ids).numel())
+    weight_bytes = hit * 3 * Dn * Fn * bits / 8
+    flops = 6.0 * rows * Dn * Fn
+    pk, src = peaks()
+    if rank == 0:
+        line = {
+            "metric": f"MoE layer tokens/s ({fmt} inference forward, prepared weights, CUDA-graph replay), whole job",
+            "value": world * Tn / (mean * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": mean, "p50_us": p50 * 1e3, "p90_us": p90 * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e2m1 x e4m3 block scales" if fmt == "NVFP4" else "e4m3 x e8m0 block scales",
+            "data": "synthetic (seeded N(0,1) tokens, N(0,0.02) weights quantised once, top-k router on N(0,1) logits)",
+            "config": {"workload": f"{args.workload}: T={Tn} tokens/rank, D={Dn}, F={Fn}, E={En} (E_local={e_local}), "
+                                   f"K={Kn}, {'clamped' if clamped else 'plain'} SwiGLU, forward only",
+                       "l2": "no flush: the prepared weights of the experts hit exceed the 126 MB L2"
+                       if weight_bytes > 126e6 else "weights of the experts hit fit in L2 between replays"},
+            "gpu_launches": None, "step_mode": "cuda-graph replay", "clocks": clocks,
+            "rows_rank0": rows, "experts_hit_rank0": hit,
+            "achieved": {"weight_stream_GBps": weight_bytes / (p50 * 1e-3) / 1e9, "hbm_peak_GBps": pk["hbm_gbs"],
+                         "tflops": flops / (p50 * 1e-3) / 1e12, "peak_source": src},
+        }
+        print(json.dumps(line), flush=True)
+    _ = out
+    ctx.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_micro(args):
     """A few launches of one grouped-GEMM arrangement on a reduced case (E_local=8, R=8192 rows):
     operands exceed L2 but stay small enough for a multi-pass profiler capture."""
@@ -514,6 +652,9 @@ def main():
                     help="run forward / input-gradient GEMMs on the CTA-pair kernel (tcgen05 cta_group::2)")
     ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
+    ap.add_argument("--workload", default="bf16-train", choices=["bf16-train"] + sorted(INFERENCE_WORKLOADS),
+                    help="bf16-train is the headline training layer; the others are forward-only inference layers")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per rank of an inference workload (sweeps)")
     args = ap.parse_args()
     if args.cta_pairs and args.impl == "ours":
         from dist_moe_b200 import _native
@@ -523,6 +664,8 @@ def main():
         run_micro(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload != "bf16-train":
+        run_inference(args)
     else:
         run_ours(args)
 

@@ -480,9 +480,357 @@ __global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const _
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Wide forward kernel: 128 x 256 output tiles for the K-major forward GEMMs (inference and training forward).
+//
+// Per 128 bytes of K a 128 x 128 tile moves 32 KiB of operands and spends, for NVFP4, more tensor-pipe time
+// on the eight scale-atom copies (about 47 cycles each, they serialise with the MMAs) than on its four MMAs
+// (69 cycles each).  A 256-column tile moves 48 KiB for twice the work and needs twelve copies per four
+// 132-cycle MMAs.  TMEM then holds one 256-column accumulator plus two buffers of scale columns, so the
+// epilogue (eight warps, a few thousand cycles) does not overlap the next tile's MMAs; tiles here are tens of
+// thousands of cycles long.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kWdBN = 256;
+constexpr int kWdThreads = 352;  // TMA warp, MMA warp, eight epilogue warps, accumulator watcher
+constexpr uint32_t kWdBBytes = kWdBN * 128;                                   // 32 KiB
+constexpr uint32_t kWdStageFp4 = kBsABytes + kWdBBytes + 2048 + 4096;         // 54 KiB: 4 + 8 scale atoms
+constexpr uint32_t kWdStageFp8 = kBsABytes + kWdBBytes + 2048;                // 50 KiB: 1 + 2 scale atoms, padded
+constexpr int kWdStagesFp4 = 3;
+constexpr int kWdStagesFp8 = 4;
+constexpr int kWdMaxStages = 4;
+constexpr uint32_t kWdSfTmemBase = kWdBN;  // scale columns: two buffers of 64 columns after the accumulator
+constexpr size_t kWdSmemFp4 = kWdStagesFp4 * kWdStageFp4 + 8 * kStaging64Bytes + 1024;
+constexpr size_t kWdSmemFp8 = kWdStagesFp8 * kWdStageFp8 + 8 * kStaging64Bytes + 1024;
+
+__global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const __grid_constant__ BsParams p) {
+  if (p.cond != nullptr && *p.cond == 0) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  __shared__ uint64_t full_bar[kWdMaxStages];
+  __shared__ uint64_t empty_bar[kWdMaxStages];
+  __shared__ uint64_t tmem_full_bar;
+  __shared__ uint64_t tmem_empty_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int s_off[kBsMaxGroups + 1];
+  __shared__ int s_tile_start[kBsMaxGroups + 1];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = (p.N + kWdBN - 1) / kWdBN;
+  const int atoms = p.fp4 ? 4 : 1;  // scale atoms per stage and 128 rows
+  const int stages = p.fp4 ? kWdStagesFp4 : kWdStagesFp8;
+  const uint32_t stage_bytes = p.fp4 ? kWdStageFp4 : kWdStageFp8;
+
+  for (int i = threadIdx.x; i <= p.e_local; i += blockDim.x) {
+    const int v = p.expert_offsets[i];
+    s_off[i] = v < p.max_rows ? v : p.max_rows;
+  }
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kWdMaxStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full_bar, 1);
+    mbar_init(&tmem_empty_bar, 8);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.e_local; ++e) {
+      s_tile_start[e] = acc;
+      const int rows = s_off[e + 1] - s_off[e];
+      if ((s_off[e] & 127) != 0) set_status(p.status, kCapacityExceeded, -1, e, s_off[e]);  // rows must be 128-padded
+      acc += ((rows + kBsBM - 1) / kBsBM) * n_tiles;
+    }
+    s_tile_start[p.e_local] = acc;
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, kBsTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&p.tm_a);
+    tma_prefetch_desc(&p.tm_b);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const int total_tiles = s_tile_start[p.e_local];
+
+  if (warp == 0) {
+    // ======================= producer =======================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int e = 0;
+      const int a_line0 = static_cast<int>((p.a_off ? *p.a_off : 0) >> 7);
+      const uint8_t* sfa = p.sfa_base + (p.sfa_off ? *p.sfa_off : 0);
+      const uint32_t sf_bytes = atoms * 512;
+      const int row_blocks = (p.N + 127) >> 7;  // 128-row scale blocks of one expert's weight
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, 0, n_tiles, p.k_iters);
+        const uint8_t* sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
+        const uint8_t* sfb_row0 = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk * 2) * p.b_col_atoms * 512;
+        const uint8_t* sfb_row1 = sfb_row0 + static_cast<int64_t>(p.b_col_atoms) * 512;
+        const bool second = t.n_blk * 2 + 1 < row_blocks;  // the tile's upper 128 columns exist
+        for (int kb = 0; kb < t.k_iters && ok; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * stage_bytes;
+          uint8_t* sb = sa + kBsABytes;
+          uint8_t* ssa = sb + kWdBBytes;
+          uint8_t* ssb = ssa + sf_bytes;
+          mbar_arrive_expect_tx(&full_bar[stage], kBsABytes + kWdBBytes + (second ? 3 : 2) * sf_bytes);
+          tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
+          tma_load_2d(sb, &p.tm_b, kb * 128, t.e * p.N + t.n_blk * kWdBN, &full_bar[stage]);
+          bulk_load(ssa, sfa_row + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
+          bulk_load(ssb, sfb_row0 + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
+          if (second) bulk_load(ssb + sf_bytes, sfb_row1 + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int e = 0, it = 0;
+      uint32_t kstep = 0;
+      bool ok = true;
+      const uint32_t sf_bytes = atoms * 512;
+      const uint32_t idesc4 = umma_idesc_blockscaled(kWdBN, 1, 0, 0);
+      uint32_t idesc8[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) idesc8[j] = umma_idesc_blockscaled(kWdBN, 0, j, j);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, 0, n_tiles, p.k_iters);
+        ok = mbar_wait(&tmem_empty_bar, (it & 1u) ^ 1u, &abort_flag);  // the epilogue has drained the accumulator
+        if (!ok) break;
+        tcgen05_fence_after();
+        for (int kb = 0; kb < t.k_iters; ++kb, ++kstep) {
+          ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+          if (!ok) break;
+          const uint32_t a_addr = smem_u32(smem + stage * stage_bytes), b_addr = a_addr + kBsABytes;
+          const uint32_t ssa = b_addr + kWdBBytes, ssb = ssa + sf_bytes;
+          const uint32_t sfa_t = tmem_base + kWdSfTmemBase + (kstep & 1u) * 64u;
+          const uint32_t sfb_t = sfa_t + 16u;
+          // Scale columns: A atom a (K step a) at +4a; B atoms of the tile's lower and upper 128 columns side
+          // by side, 8 columns per K step.
+          for (int a = 0; a < atoms; ++a) {
+            tmem_cp_sf_atom(sfa_t + 4 * a, sf_smem_desc(ssa + a * 512));
+            tmem_cp_sf_atom(sfb_t + 8 * a, sf_smem_desc(ssb + a * 512));
+            tmem_cp_sf_atom(sfb_t + 8 * a + 4, sf_smem_desc(ssb + sf_bytes + a * 512));
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t da = umma_smem_desc(a_addr + j * 32u, 16, 1024);
+            const uint64_t db = umma_smem_desc(b_addr + j * 32u, 16, 1024);
+            const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+            if (p.fp4)
+              umma_nvf4(tmem_base, da, db, idesc4, sfa_t + 4 * j, sfb_t + 8 * j, acc);
+            else
+              umma_mxf8(tmem_base, da, db, idesc8[j], sfa_t, sfb_t, acc);
+          }
+          tcgen05_commit(&empty_bar[stage]);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (t.k_iters > 0)
+          tcgen05_commit(&tmem_full_bar);
+        else
+          mbar_arrive(&tmem_full_bar);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ======================= accumulator watcher =======================
+    // Polls the accumulator-ready barrier for the epilogue warps and releases them through a hardware named
+    // barrier; it arrives for every tile, also after a timeout, so that no epilogue warp is left blocked.
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      if (ok && lane == 0) ok = mbar_wait(&tmem_full_bar, it & 1u, &abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      asm volatile("bar.arrive %0, %1;" ::"r"(1 + (it & 1)), "r"(8 * 32 + 32) : "memory");
+    }
+  } else {
+    // ======================= epilogue =======================
+    // Eight warps: two per TMEM lane quadrant, each owning 128 of the tile's 256 columns.  A lane reads its own
+    // accumulator row; the warp transposes 32 x 32 blocks through its staging tile and stores 64-byte row segments.
+    const int ew = warp - 2;
+    const int quad = warp & 3;
+    const int half = ew >> 2;
+    const int row_in_tile = quad * 32 + lane;
+    uint8_t* stg = smem + stages * stage_bytes + ew * kStaging64Bytes;
+    int e = 0, it = 0;
+    bool ok = true;
+    const int64_t c_off = p.c_off ? *p.c_off : 0;
+    const int64_t h2_off = p.h2_off ? *p.h2_off : 0;
+    const float* row_inv =
+        p.row_inv_base ? reinterpret_cast<const float*>(p.row_inv_base + (p.row_inv_off ? *p.row_inv_off : 0)) : nullptr;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, 0, n_tiles, p.k_iters);
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + (it & 1)), "r"(8 * 32 + 32) : "memory");  // released by the watcher
+      ok = abort_flag == 0;
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      const int row = t.row0 + row_in_tile;
+      const bool row_ok = row < t.row_end;
+      float scale = 1.0f;
+      bool scaled = false;
+      if (row_inv != nullptr && row_ok) {
+        scale = row_inv[row];
+        scaled = true;
+      }
+      const float escale = p.expert_inv ? p.expert_inv[t.e] : 1.0f;
+      scaled = scaled || p.expert_inv != nullptr;
+      if (p.swiglu) {
+        // Columns come in groups of 16: 8 gate features then the matching 8 up features.
+        const int F = p.N / 2;
+        const uint64_t my_h2 =
+            row_ok ? reinterpret_cast<uint64_t>(p.h2_base) + h2_off + static_cast<uint64_t>(row) * F * 2 : 0ull;
+        const uint64_t my_h1 = (row_ok && p.c_base)
+                                   ? reinterpret_cast<uint64_t>(p.c_base) + c_off + static_cast<uint64_t>(row) * p.N * 2
+                                   : 0ull;
+        // Drain this warp's 128 columns into registers and hand the accumulator back at once: the SwiGLU
+        // arithmetic and the stores below then run while the next tile's MMAs fill the accumulator again.
+        uint32_t ra[32], rb[32], rc[32], rd[32];
+        tmem_ld_32x32(taddr + half * (kWdBN / 2), ra);
+        tmem_ld_32x32(taddr + half * (kWdBN / 2) + 32, rb);
+        tmem_ld_32x32(taddr + half * (kWdBN / 2) + 64, rc);
+        tmem_ld_32x32(taddr + half * (kWdBN / 2) + 96, rd);
+        tmem_ld_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar);
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          const int c0 = half * (kWdBN / 2) + 64 * blk;
+          uint32_t (&r0)[32] = blk == 0 ? ra : rc;
+          uint32_t (&r1)[32] = blk == 0 ? rb : rd;
+          uint4 zv[4], gv[4], uv[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t gw[4], uw[4], zw[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int b = 16 * (g & 1) + 2 * q;
+              float g0 = __uint_as_float(g < 2 ? r0[b] : r1[b]), g1 = __uint_as_float(g < 2 ? r0[b + 1] : r1[b + 1]);
+              float u0 = __uint_as_float(g < 2 ? r0[b + 8] : r1[b + 8]), u1 = __uint_as_float(g < 2 ? r0[b + 9] : r1[b + 9]);
+              if (scaled) {
+                g0 = (g0 * scale) * escale; g1 = (g1 * scale) * escale;
+                u0 = (u0 * scale) * escale; u1 = (u1 * scale) * escale;
+              }
+              gw[q] = pack_bf16x2(g0, g1);
+              uw[q] = pack_bf16x2(u0, u1);
+              const float z0 = swiglu_f32(__uint_as_float(gw[q] << 16), __uint_as_float(uw[q] << 16), p.act);
+              const float z1 =
+                  swiglu_f32(__uint_as_float(gw[q] & 0xffff0000u), __uint_as_float(uw[q] & 0xffff0000u), p.act);
+              zw[q] = pack_bf16x2(z0, z1);
+            }
+            zv[g] = make_uint4(zw[0], zw[1], zw[2], zw[3]);
+            gv[g] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+            uv[g] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+          }
+          const int f0 = t.n_blk * (kWdBN / 2) + c0 / 2;  // first of the 32 features of this block
+#pragma unroll
+          for (int which = 0; which < 3; ++which) {
+            if (which > 0 && p.c_base == nullptr) break;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, which == 0 ? zv[j] : (which == 1 ? gv[j] : uv[j]));
+            __syncwarp();
+            const uint64_t base = which == 0 ? my_h2 : my_h1;
+            const int col_out = which == 2 ? F + f0 : f0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), j = lane & 3;
+              const uint4 v = stage64_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, base, rr);
+              if (rp != 0 && f0 + 8 * j + 8 <= F)
+                *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col_out + 8 * j) * 2) = v;
+            }
+            __syncwarp();
+          }
+        }
+      } else {
+        uint64_t my_row = 0;
+        if (row_ok) {
+          if (p.scatter_ptrs != nullptr)
+            my_row = static_cast<uint64_t>(p.scatter_ptrs[row]);
+          else
+            my_row = reinterpret_cast<uint64_t>(p.c_base) + c_off + static_cast<uint64_t>(row) * p.N * 2;
+        }
+        uint32_t ra[32], rb[32], rc[32], rd[32];
+        tmem_ld_32x32(taddr + half * (kWdBN / 2), ra);
+        tmem_ld_32x32(taddr + half * (kWdBN / 2) + 32, rb);
+        tmem_ld_32x32(taddr + half * (kWdBN / 2) + 64, rc);
+        tmem_ld_32x32(taddr + half * (kWdBN / 2) + 96, rd);
+        tmem_ld_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar);  // accumulator handed back, see above
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          const int c0 = half * (kWdBN / 2) + 32 * blk;
+          uint32_t (&r)[32] = blk == 0 ? ra : (blk == 1 ? rb : (blk == 2 ? rc : rd));
+          if (scaled) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint((__uint_as_float(r[j]) * scale) * escale);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
+          __syncwarp();
+          const int col = t.n_blk * kWdBN + c0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rr = i * 8 + (lane >> 2), j = lane & 3;
+            const uint4 v = stage64_get(stg, rr, j);
+            const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+            if (rp != 0 && col + 8 * j + 8 <= p.N)
+              *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
+          }
+          __syncwarp();
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) set_status(p.status, kPipelineTimeout, 4, blockIdx.x);
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kBsTmemCols);
+  }
+}
+
 }  // namespace dm
 
 using namespace dm;
+
+static int g_bs_wide = 1;
+
+extern "C" int dm_set_blockscaled_wide(int enabled) {
+  const int previous = g_bs_wide;
+  g_bs_wide = enabled ? 1 : 0;
+  return previous;
+}
 
 static int bs_prepare_launch() {
   static bool attr_set = false;
@@ -544,6 +892,19 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   p.swiglu = swiglu_interleaved ? 1 : 0;
   p.act = ActParams{clamped, alpha, limit};
   const int grid = num_sms > 0 ? num_sms : sm_count();
+  if (g_bs_wide) {
+    static bool wide_attr_set = false;
+    if (!wide_attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      wide_attr_set = true;
+    }
+    rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kWdBN);
+    if (rc != kRcOk) return rc;
+    blockscaled_wide_kernel<<<grid, kWdThreads, fp4 ? kWdSmemFp4 : kWdSmemFp8, static_cast<cudaStream_t>(stream)>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
   blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
   return static_cast<int>(cudaGetLastError());
 }

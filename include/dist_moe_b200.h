@@ -274,6 +274,12 @@ int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w,
                         int64_t N, int64_t Kd, int swiglu_interleaved, int clamped, float alpha, float limit,
                         const int* cond, int num_sms, int* status, void* stream);
 
+/* Kernel selection for dm_gemm_blockscaled: non-zero (default) runs 128 x 256 output tiles (one 256-column
+ * accumulator in TMEM, 3 or 4 stages of 48 KiB operands + scale atoms), zero runs the 128 x 128 tiles the
+ * backward GEMMs use.  Returns the previous setting.  Results agree to fp32 accumulation order.  No
+ * counterpart in the reference (tile geometry is chosen by BlockScaledKernelConfig, dist_moe/api.py:233-329). */
+int dm_set_blockscaled_wide(int enabled);
+
 /* MXFP8 training backward GEMMs (dist_moe/_blockscaled_ops.py: `dist_blockscaled_grouped_gemm_dgrad_dispatch`,
  * `..._dgrad_swiglu_bwd_combine`, `blockscaled_grouped_gemm_wgrad`; sequencing dist_moe/_blockscaled.py:2284-2512).
  *

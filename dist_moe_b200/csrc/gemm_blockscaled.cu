@@ -519,7 +519,8 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tiles = (p.N + kWdBN - 1) / kWdBN;
+  const int n_tiles = p.mode == 2 ? (p.Kw + kWdBN - 1) / kWdBN : (p.N + kWdBN - 1) / kWdBN;
+  const int wgrad_m_tiles = (p.N + kBsBM - 1) / kBsBM;
   const int atoms = p.fp4 ? 4 : 1;  // scale atoms per stage and 128 rows
   const int stages = p.fp4 ? kWdStagesFp4 : kWdStagesFp8;
   const uint32_t stage_bytes = p.fp4 ? kWdStageFp4 : kWdStageFp8;
@@ -545,7 +546,7 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
       s_tile_start[e] = acc;
       const int rows = s_off[e + 1] - s_off[e];
       if ((s_off[e] & 127) != 0) set_status(p.status, kCapacityExceeded, -1, e, s_off[e]);  // rows must be 128-padded
-      acc += ((rows + kBsBM - 1) / kBsBM) * n_tiles;
+      acc += p.mode == 2 ? wgrad_m_tiles * n_tiles : ((rows + kBsBM - 1) / kBsBM) * n_tiles;
     }
     s_tile_start[p.e_local] = acc;
   }
@@ -570,14 +571,24 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
       uint32_t phase = 0;
       int e = 0;
       const int a_line0 = static_cast<int>((p.a_off ? *p.a_off : 0) >> 7);
+      const int b_line0 = static_cast<int>((p.b_off ? *p.b_off : 0) >> 7);
       const uint8_t* sfa = p.sfa_base + (p.sfa_off ? *p.sfa_off : 0);
+      const uint8_t* sfb_dyn = p.sfb + (p.sfb_off ? *p.sfb_off : 0);
       const uint32_t sf_bytes = atoms * 512;
-      const int row_blocks = (p.N + 127) >> 7;  // 128-row scale blocks of one expert's weight
+      const int row_blocks = ((p.mode == 2 ? p.Kw : p.N) + 127) >> 7;  // 128-wide blocks of the B side
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, 0, n_tiles, p.k_iters);
-        const uint8_t* sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
-        const uint8_t* sfb_row0 = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk * 2) * p.b_col_atoms * 512;
+        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
+        const uint8_t* sfa_row;
+        const uint8_t* sfb_row0;
+        if (p.mode == 2) {
+          // scales of the column-quantised operands: rows = features, columns = 32-row blocks of the packed rows
+          sfa_row = sfa + (static_cast<int64_t>(t.m_blk) * p.a_col_atoms + (t.row0 >> 7)) * 512;
+          sfb_row0 = sfb_dyn + (static_cast<int64_t>(t.n_blk * 2) * p.b_col_atoms + (t.row0 >> 7)) * 512;
+        } else {
+          sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
+          sfb_row0 = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk * 2) * p.b_col_atoms * 512;
+        }
         const uint8_t* sfb_row1 = sfb_row0 + static_cast<int64_t>(p.b_col_atoms) * 512;
         const bool second = t.n_blk * 2 + 1 < row_blocks;  // the tile's upper 128 columns exist
         for (int kb = 0; kb < t.k_iters && ok; ++kb) {
@@ -587,9 +598,23 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
           uint8_t* sb = sa + kBsABytes;
           uint8_t* ssa = sb + kWdBBytes;
           uint8_t* ssb = ssa + sf_bytes;
-          mbar_arrive_expect_tx(&full_bar[stage], kBsABytes + kWdBBytes + (second ? 3 : 2) * sf_bytes);
-          tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
-          tma_load_2d(sb, &p.tm_b, kb * 128, t.e * p.N + t.n_blk * kWdBN, &full_bar[stage]);
+          if (p.mode == 0) {
+            mbar_arrive_expect_tx(&full_bar[stage], kBsABytes + kWdBBytes + (second ? 3 : 2) * sf_bytes);
+            tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
+            tma_load_2d(sb, &p.tm_b, kb * 128, t.e * p.N + t.n_blk * kWdBN, &full_bar[stage]);
+          } else {
+            // B arrives as two 128-byte-wide boxes of 128 K rows (MN-major); the upper one only where it exists
+            mbar_arrive_expect_tx(&full_bar[stage], kBsABytes + (second ? kWdBBytes + 3 * sf_bytes : kWdBBytes / 2 + 2 * sf_bytes));
+            if (p.mode == 1) {
+              tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
+              tma_load_2d(sb, &p.tm_b, t.n_blk * kWdBN, t.e * p.Kw + kb * 128, &full_bar[stage]);
+              if (second) tma_load_2d(sb + kWdBBytes / 2, &p.tm_b, t.n_blk * kWdBN + 128, t.e * p.Kw + kb * 128, &full_bar[stage]);
+            } else {
+              tma_load_3d(sa, &p.tm_a, 0, a_line0 + t.m_blk, t.row0 + kb * 128, &full_bar[stage]);
+              tma_load_3d(sb, &p.tm_b, 0, b_line0 + t.n_blk * 2, t.row0 + kb * 128, &full_bar[stage]);
+              if (second) tma_load_3d(sb + kWdBBytes / 2, &p.tm_b, 0, b_line0 + t.n_blk * 2 + 1, t.row0 + kb * 128, &full_bar[stage]);
+            }
+          }
           bulk_load(ssa, sfa_row + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
           bulk_load(ssb, sfb_row0 + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
           if (second) bulk_load(ssb + sf_bytes, sfb_row1 + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
@@ -610,12 +635,15 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
       uint32_t kstep = 0;
       bool ok = true;
       const uint32_t sf_bytes = atoms * 512;
+      const int a_mn = p.mode == 2, b_mn = p.mode != 0;
+      const uint32_t a_step = a_mn ? 4096u : 32u, b_step = b_mn ? 4096u : 32u;
+      const uint32_t b_lbo = b_mn ? kWdBBytes / 2 : 16u;  // MN-major: the two 128-byte-wide halves are 16 KiB apart
       const uint32_t idesc4 = umma_idesc_blockscaled(kWdBN, 1, 0, 0);
       uint32_t idesc8[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) idesc8[j] = umma_idesc_blockscaled(kWdBN, 0, j, j);
+      for (int j = 0; j < 4; ++j) idesc8[j] = umma_idesc_blockscaled(kWdBN, 0, j, j, a_mn, b_mn);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, 0, n_tiles, p.k_iters);
+        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
         ok = mbar_wait(&tmem_empty_bar, (it & 1u) ^ 1u, &abort_flag);  // the epilogue has drained the accumulator
         if (!ok) break;
         tcgen05_fence_after();
@@ -635,8 +663,8 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint64_t da = umma_smem_desc(a_addr + j * 32u, 16, 1024);
-            const uint64_t db = umma_smem_desc(b_addr + j * 32u, 16, 1024);
+            const uint64_t da = umma_smem_desc(a_addr + j * a_step, 16, 1024);
+            const uint64_t db = umma_smem_desc(b_addr + j * b_step, b_lbo, 1024);
             const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
             if (p.fp4)
               umma_nvf4(tmem_base, da, db, idesc4, sfa_t + 4 * j, sfb_t + 8 * j, acc);
@@ -684,12 +712,83 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
     const float* row_inv =
         p.row_inv_base ? reinterpret_cast<const float*>(p.row_inv_base + (p.row_inv_off ? *p.row_inv_off : 0)) : nullptr;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, 0, n_tiles, p.k_iters);
+      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
       asm volatile("bar.sync %0, %1;" ::"r"(1 + (it & 1)), "r"(8 * 32 + 32) : "memory");  // released by the watcher
       ok = abort_flag == 0;
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      if (p.mode == 2) {
+        // weight gradient: dW[e][m][n], overwrite or accumulate (fp32 or bf16 destination)
+        uint32_t ra[32], rb[32], rc[32], rd[32];
+        if (t.k_iters > 0) {
+          tmem_ld_32x32(taddr + half * (kWdBN / 2), ra);
+          tmem_ld_32x32(taddr + half * (kWdBN / 2) + 32, rb);
+          tmem_ld_32x32(taddr + half * (kWdBN / 2) + 64, rc);
+          tmem_ld_32x32(taddr + half * (kWdBN / 2) + 96, rd);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ra[j] = rb[j] = rc[j] = rd[j] = 0u;
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar);  // accumulator handed back before the stores
+        const int out_row = t.m_blk * kBsBM + row_in_tile;
+        const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kw;
+        const uint64_t my_row =
+            out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          uint32_t (&r)[32] = blk == 0 ? ra : (blk == 1 ? rb : (blk == 2 ? rc : rd));
+          const int col = t.n_blk * kWdBN + half * (kWdBN / 2) + 32 * blk;
+          if (p.out_fp32) {
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {  // 16 fp32 columns = 64 bytes per row
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                stage64_put(stg, lane, j,
+                            make_uint4(r[16 * sub + 4 * j], r[16 * sub + 4 * j + 1], r[16 * sub + 4 * j + 2],
+                                       r[16 * sub + 4 * j + 3]));
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = i * 8 + (lane >> 2), j = lane & 3;
+                const uint4 v = stage64_get(stg, rr, j);
+                const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+                const int cc = col + 16 * sub + 4 * j;
+                if (rp != 0 && cc + 4 <= p.Kw) {
+                  const uint64_t dst = rp + static_cast<uint64_t>(cc) * 4;
+                  if (p.accumulate)
+                    red_add_f32x4(dst, v);
+                  else
+                    *reinterpret_cast<uint4*>(dst) = v;
+                }
+              }
+              __syncwarp();
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), j = lane & 3;
+              const uint4 v = stage64_get(stg, rr, j);
+              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+              if (rp != 0 && col + 8 * j + 8 <= p.Kw) {
+                const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
+                if (p.accumulate)
+                  red_add_bf16x8(dst, v);
+                else
+                  *reinterpret_cast<uint4*>(dst) = v;
+              }
+            }
+            __syncwarp();
+          }
+        }
+        continue;
+      }
       const int row = t.row0 + row_in_tile;
       const bool row_ok = row < t.row_end;
       float scale = 1.0f;
@@ -832,6 +931,28 @@ extern "C" int dm_set_blockscaled_wide(int enabled) {
   return previous;
 }
 
+static int bs_prepare_launch();
+
+// Launches the 128 x 256 kernel, or the 128 x 128 one when the wide tiles are switched off.
+static int bs_launch(const BsParams& p, int num_sms, cudaStream_t st) {
+  const int grid = num_sms > 0 ? num_sms : sm_count();
+  if (g_bs_wide) {
+    static bool wide_attr_set = false;
+    if (!wide_attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      wide_attr_set = true;
+    }
+    blockscaled_wide_kernel<<<grid, kWdThreads, p.fp4 ? kWdSmemFp4 : kWdSmemFp8, st>>>(p);
+  } else {
+    int rc = bs_prepare_launch();
+    if (rc != kRcOk) return rc;
+    blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, st>>>(p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
 static int bs_prepare_launch() {
   static bool attr_set = false;
   if (!attr_set) {
@@ -891,22 +1012,11 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   p.fp4 = fp4;
   p.swiglu = swiglu_interleaved ? 1 : 0;
   p.act = ActParams{clamped, alpha, limit};
-  const int grid = num_sms > 0 ? num_sms : sm_count();
   if (g_bs_wide) {
-    static bool wide_attr_set = false;
-    if (!wide_attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4));
-      if (e != cudaSuccess) return static_cast<int>(e);
-      wide_attr_set = true;
-    }
     rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kWdBN);
     if (rc != kRcOk) return rc;
-    blockscaled_wide_kernel<<<grid, kWdThreads, fp4 ? kWdSmemFp4 : kWdSmemFp8, static_cast<cudaStream_t>(stream)>>>(p);
-    return static_cast<int>(cudaGetLastError());
   }
-  blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
 }
 
 // Input gradient: C[r, n] = sum_k dY[r, k] * W[e][k, n].  W is the same E4M3 qdata as in the forward
@@ -950,9 +1060,7 @@ extern "C" int dm_gemm_blockscaled_dgrad(dm_operand dy, dm_operand sf_dy, const 
   p.k_iters = static_cast<int>(Kd / 128);
   p.mode = 1;
   p.act = ActParams{0, 1.0f, 0.0f};
-  const int grid = num_sms > 0 ? num_sms : sm_count();
-  blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
 }
 
 // Weight gradient: dW[e][m, n] (+)= sum_{r in expert e} dY[r, m] * X[r, n].  Both operands are quantised
@@ -996,7 +1104,5 @@ extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col
   p.out_fp32 = dw_is_fp32 ? 1 : 0;
   p.accumulate = accumulate ? 1 : 0;
   p.act = ActParams{0, 1.0f, 0.0f};
-  const int grid = num_sms > 0 ? num_sms : sm_count();
-  blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
 }

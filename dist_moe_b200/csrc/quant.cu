@@ -224,6 +224,121 @@ __global__ void __launch_bounds__(256) mxfp8_slab_kernel(const __nv_bfloat16* __
 }
 
 // ---------------------------------------------------------------------------
+// MXFP8 column mode, optionally with the row-quantised copy, for activations: the bandwidth-bound form.
+//
+// A CTA stages a slab of 32 rows x 512 columns as raw bf16 (16-byte loads, rows 1040 bytes apart so that
+// 16-byte reads of eight consecutive rows fall into different bank groups).  Block maxima are taken on the
+// bit patterns: |x| of a bf16 is its low 15 bits, their unsigned order is the order of the magnitudes, and
+// any pattern above 0x7f80 is a NaN, which makes the block non-finite exactly as the fp32 rule does
+// (bf16 -> fp32 is exact).  Two 16-bit lanes are compared per instruction.
+//   column pass: thread t owns columns 2t and 2t+1 (one 32-bit word per row);
+//   row pass   : lane r of a warp owns row r of one 32-column block (four 16-byte reads).
+// The column-quantised bytes go back through shared memory so that global stores are 16 bytes wide.
+// ---------------------------------------------------------------------------
+constexpr int kSlabCols = 512;
+constexpr int kSlabRawStride = kSlabCols * 2 + 16;
+constexpr int kSlabOutStride = kSlabCols + 16;
+
+__device__ __forceinline__ float amax_from_bf16_bits(uint32_t bits15) {
+  return bits15 > 0x7f80u ? __int_as_float(0x7f800000) : __uint_as_float(bits15 << 16);
+}
+
+__global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
+                                                           int64_t max_rows, int C, uint8_t* __restrict__ q_col,
+                                                           uint8_t* __restrict__ s_col, int blocked, int col_atoms,
+                                                           uint8_t* __restrict__ q_row, uint8_t* __restrict__ s_row,
+                                                           int row_atoms) {
+  __shared__ __align__(16) uint8_t slab[32 * kSlabRawStride];
+  int64_t rows = num_rows ? *num_rows : max_rows;
+  if (rows > max_rows) rows = max_rows;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.y) * 32;
+  const int col0 = blockIdx.x * kSlabCols;
+  if (row0 >= rows) return;
+  const int t = threadIdx.x;
+  const int vec_per_row = C >> 3;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = t + 256 * k;
+    const int r = i >> 6, v = i & 63;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (row0 + r < rows && col0 + v * 8 < C) val = x[(row0 + r) * vec_per_row + (col0 >> 3) + v];
+    *reinterpret_cast<uint4*>(slab + r * kSlabRawStride + v * 16) = val;
+  }
+  __syncthreads();
+
+  if (q_row != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int r = t & 31, b = (t >> 5) + 8 * k;
+      const int colb = col0 + b * 32;
+      if (row0 + r < rows && colb < C) {
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 v = *reinterpret_cast<const uint4*>(slab + r * kSlabRawStride + b * 64 + j * 16);
+          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+        uint32_t m = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m = __vmaxu2(m, w[j] & 0x7fff7fffu);
+        const uint32_t top = (m >> 16) > (m & 0xffffu) ? (m >> 16) : (m & 0xffffu);
+        float recip;
+        const uint8_t byte = mxfp8_scale(amax_from_bf16_bits(top), recip);
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          o[j] = e4m3x4(__uint_as_float(w[2 * j] << 16) * recip, __uint_as_float(w[2 * j] & 0xffff0000u) * recip,
+                        __uint_as_float(w[2 * j + 1] << 16) * recip, __uint_as_float(w[2 * j + 1] & 0xffff0000u) * recip);
+        uint4* dst = reinterpret_cast<uint4*>(q_row + (row0 + r) * C + colb);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        s_row[blocked_offset(row0 + r, colb >> 5, row_atoms)] = byte;
+      }
+    }
+  }
+
+  // column pass: 32 rows of two adjacent columns per thread
+  uint32_t w[32];
+#pragma unroll
+  for (int r = 0; r < 32; ++r) w[r] = *reinterpret_cast<const uint32_t*>(slab + r * kSlabRawStride + t * 4);
+  uint32_t m = 0;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) m = __vmaxu2(m, w[r] & 0x7fff7fffu);
+  float recip0, recip1;
+  const uint8_t byte0 = mxfp8_scale(amax_from_bf16_bits(m & 0xffffu), recip0);
+  const uint8_t byte1 = mxfp8_scale(amax_from_bf16_bits(m >> 16), recip1);
+  const int c = col0 + 2 * t;
+  if (c < C) {
+    const int64_t rb = row0 >> 5;
+    if (blocked) {
+      s_col[blocked_offset(c, static_cast<int>(rb), col_atoms)] = byte0;
+      s_col[blocked_offset(c + 1, static_cast<int>(rb), col_atoms)] = byte1;
+    } else {
+      const int64_t per_col = (max_rows + 31) / 32;
+      s_col[static_cast<int64_t>(c) * per_col + rb] = byte0;
+      s_col[static_cast<int64_t>(c + 1) * per_col + rb] = byte1;
+    }
+  }
+  __syncthreads();  // every thread holds what it needs of the raw slab: its storage now takes the quantised bytes
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const uint32_t pk = __nv_cvt_float2_to_fp8x2(
+        make_float2(__uint_as_float(w[r] << 16) * recip0, __uint_as_float(w[r] & 0xffff0000u) * recip1), __NV_SATFINITE,
+        __NV_E4M3);
+    *reinterpret_cast<uint16_t*>(slab + r * kSlabOutStride + t * 2) = static_cast<uint16_t>(pk);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = t + 256 * k;
+    const int r = i >> 5, v = i & 31;
+    if (row0 + r < rows && col0 + v * 16 < C)
+      *reinterpret_cast<uint4*>(q_col + (row0 + r) * C + col0 + v * 16) =
+          *reinterpret_cast<const uint4*>(slab + r * kSlabOutStride + v * 16);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // NVFP4
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint8_t nvfp4_block_scale(float amax, float scale, float& mult) {
@@ -420,8 +535,15 @@ extern "C" int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_
                                   void* scales, int blocked, void* stream) {
   if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 4) != 0) return kRcBadArg;
   if (max_rows == 0) return kRcOk;
-  const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
   const int atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  if ((C % 16) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q)) % 16) == 0) {
+    const dim3 fast(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
+    mxfp8_colrow_kernel<<<fast, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q),
+        static_cast<uint8_t*>(scales), blocked, atoms, nullptr, nullptr, 0);
+    return static_cast<int>(cudaGetLastError());
+  }
+  const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
   mxfp8_slab_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q),
       static_cast<uint8_t*>(scales), nullptr, blocked, atoms, 0, max_rows);
@@ -433,12 +555,12 @@ extern "C" int dm_quant_mxfp8_rowcol(const void* x, const int32_t* num_rows, int
   if (!x || !q_row || !scales_row_blocked || !q_col || !scales_col_blocked || max_rows < 0 || C <= 0 || (C % 32) != 0)
     return kRcBadArg;
   if (max_rows == 0) return kRcOk;
-  const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
+  const dim3 grid(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
   const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
   const int row_atoms = static_cast<int>((C / 32 + 3) / 4);
-  mxfp8_slab_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q_col),
-      static_cast<uint8_t*>(scales_col_blocked), nullptr, 1, col_atoms, 0, max_rows, static_cast<uint8_t*>(q_row),
+  mxfp8_colrow_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q_col),
+      static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms, static_cast<uint8_t*>(q_row),
       static_cast<uint8_t*>(scales_row_blocked), row_atoms);
   return static_cast<int>(cudaGetLastError());
 }

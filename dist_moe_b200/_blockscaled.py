@@ -465,19 +465,24 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
     c.h2_col_sf = torch.empty(_sf_cols_bytes(R, F), dtype=torch.uint8, device=dev)
     none = nat.Operand(None, 0, None)
     full = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
-    nat.check(nat.lib.dm_gather_rows(c.fwd.data_ptr(), recv, _ptr(xg), None, D * 2, R, None, st), "dm_gather_rows")
-    nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(xg), recv, R, D, _ptr(xq), _ptr(xsf), c.x_col.data_ptr(),
-                                            c.x_col_sf.data_ptr(), st), "dm_quant_mxfp8_rowcol(x)")
+    # dispatch: the routed rows are pulled through the pointer table by the quantiser itself
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol_gather(c.fwd.data_ptr(), recv, R, D, _ptr(xq), _ptr(xsf), c.x_col.data_ptr(),
+                                                   c.x_col_sf.data_ptr(), st), "dm_quant_mxfp8_rowcol_gather(x)")
     nat.check(nat.lib.dm_gemm_blockscaled(0, xq, xsf, p13.fprop_data.data_ptr(), p13.fprop_scale.data_ptr(), full(c.h1),
                                           none, None, none, None, c.offsets.data_ptr(), el, R, 2 * F, D, 0, 0, 1.0, 0.0,
                                           None, state.num_sms, status, st), "dm_gemm_blockscaled(w13)")
     clip = options.swiglu_clip_stats_out_3
     if clip is not None:
         clip.zero_()
-    nat.check(nat.lib.dm_swiglu_fwd(c.h1.data_ptr(), None, _ptr(h2), None, recv, R, F, clamped, alpha, limit,
-                                    nat.ptr(clip), float(options.swiglu_clip_limit), None, st), "dm_swiglu_fwd")
-    nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(h2), recv, R, F, _ptr(hq), _ptr(hsf), c.h2_col.data_ptr(),
-                                            c.h2_col_sf.data_ptr(), st), "dm_quant_mxfp8_rowcol(h2)")
+    if clip is None:
+        nat.check(nat.lib.dm_swiglu_fwd_quant_mxfp8_rowcol(c.h1.data_ptr(), recv, R, F, clamped, alpha, limit, _ptr(hq),
+                                                           _ptr(hsf), c.h2_col.data_ptr(), c.h2_col_sf.data_ptr(), st),
+                  "dm_swiglu_fwd_quant_mxfp8_rowcol")
+    else:  # the clip counters live in the standalone activation kernel
+        nat.check(nat.lib.dm_swiglu_fwd(c.h1.data_ptr(), None, _ptr(h2), None, recv, R, F, clamped, alpha, limit,
+                                        nat.ptr(clip), float(options.swiglu_clip_limit), None, st), "dm_swiglu_fwd")
+        nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(h2), recv, R, F, _ptr(hq), _ptr(hsf), c.h2_col.data_ptr(),
+                                                c.h2_col_sf.data_ptr(), st), "dm_quant_mxfp8_rowcol(h2)")
     nat.check(nat.lib.dm_gemm_blockscaled(0, hq, hsf, p2.fprop_data.data_ptr(), p2.fprop_scale.data_ptr(), none, none,
                                           c.sct.data_ptr(), none, None, c.offsets.data_ptr(), el, R, D, F, 0, 0, 1.0,
                                           0.0, None, state.num_sms, status, st), "dm_gemm_blockscaled(w2)")
@@ -524,12 +529,12 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
                                              nat.ptr(grad_scores), T, K, D, st), "dm_broadcast_and_scale")
     state.barrier(state.combine)
     # ---- W2 ----------------------------------------------------------------------------------
-    nat.check(nat.lib.dm_gather_rows(c.sct.data_ptr(), recv, _ptr(dyg), None, D * 2, R, None, st),
-              "dm_gather_rows(grad_h3)")
     if need_w2:
-        nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(dyg), recv, R, D, _ptr(dyq), _ptr(dysf), _ptr(dyc), _ptr(dycsf), st),
-                  "dm_quant_mxfp8_rowcol(dy)")
+        nat.check(nat.lib.dm_quant_mxfp8_rowcol_gather(c.sct.data_ptr(), recv, R, D, _ptr(dyq), _ptr(dysf), _ptr(dyc),
+                                                       _ptr(dycsf), st), "dm_quant_mxfp8_rowcol_gather(dy)")
     else:
+        nat.check(nat.lib.dm_gather_rows(c.sct.data_ptr(), recv, _ptr(dyg), None, D * 2, R, None, st),
+                  "dm_gather_rows(grad_h3)")
         nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dyg), recv, R, D, _ptr(dyq), 0, _ptr(dysf), 0, 1, st),
                   "dm_quant_mxfp8_row(dy)")
     nat.check(nat.lib.dm_gemm_blockscaled_dgrad(dyq, dysf, c.p2.fprop_data.data_ptr(), c.p2.dgrad_scale.data_ptr(), dh2,

@@ -243,7 +243,14 @@ __device__ __forceinline__ float amax_from_bf16_bits(uint32_t bits15) {
   return bits15 > 0x7f80u ? __int_as_float(0x7f800000) : __uint_as_float(bits15 << 16);
 }
 
-__global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
+// Where a slab comes from: a dense [rows, C] matrix; rows named by a pointer table (a null pointer is a row of
+// zeros; pointers may address peer memory); or SwiGLU of a dense [rows, 2C] matrix [gate | up], rounded to
+// bf16 exactly as the standalone activation kernel rounds it.
+enum SlabSource : int { kSlabDense = 0, kSlabGather = 1, kSlabSwiglu = 2 };
+
+template <int kSource>
+__global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restrict__ x, const int64_t* __restrict__ row_ptrs,
+                                                           ActParams act, const int32_t* num_rows,
                                                            int64_t max_rows, int C, uint8_t* __restrict__ q_col,
                                                            uint8_t* __restrict__ s_col, int blocked, int col_atoms,
                                                            uint8_t* __restrict__ q_row, uint8_t* __restrict__ s_row,
@@ -261,7 +268,25 @@ __global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restri
     const int i = t + 256 * k;
     const int r = i >> 6, v = i & 63;
     uint4 val = make_uint4(0, 0, 0, 0);
-    if (row0 + r < rows && col0 + v * 8 < C) val = x[(row0 + r) * vec_per_row + (col0 >> 3) + v];
+    if (row0 + r < rows && col0 + v * 8 < C) {
+      if (kSource == kSlabDense) {
+        val = x[(row0 + r) * vec_per_row + (col0 >> 3) + v];
+      } else if (kSource == kSlabGather) {
+        const uint4* src = reinterpret_cast<const uint4*>(row_ptrs[row0 + r]);
+        if (src != nullptr) val = __ldcg(src + (col0 >> 3) + v);
+      } else {
+        const uint4 g4 = x[(row0 + r) * 2 * vec_per_row + (col0 >> 3) + v];
+        const uint4 u4 = x[(row0 + r) * 2 * vec_per_row + vec_per_row + (col0 >> 3) + v];
+        float g[8], u[8];
+        unpack8f(g4, g);
+        unpack8f(u4, u);
+        uint32_t z[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          z[j] = pack_bf16x2(swiglu_f32(g[2 * j], u[2 * j], act), swiglu_f32(g[2 * j + 1], u[2 * j + 1], act));
+        val = make_uint4(z[0], z[1], z[2], z[3]);
+      }
+    }
     *reinterpret_cast<uint4*>(slab + r * kSlabRawStride + v * 16) = val;
   }
   __syncthreads();
@@ -538,9 +563,9 @@ extern "C" int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_
   const int atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
   if ((C % 16) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q)) % 16) == 0) {
     const dim3 fast(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
-    mxfp8_colrow_kernel<<<fast, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q),
-        static_cast<uint8_t*>(scales), blocked, atoms, nullptr, nullptr, 0);
+    mxfp8_colrow_kernel<kSlabDense><<<fast, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x), nullptr, ActParams{0, 1.0f, 0.0f}, num_rows, max_rows, static_cast<int>(C),
+        static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales), blocked, atoms, nullptr, nullptr, 0);
     return static_cast<int>(cudaGetLastError());
   }
   const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
@@ -558,10 +583,44 @@ extern "C" int dm_quant_mxfp8_rowcol(const void* x, const int32_t* num_rows, int
   const dim3 grid(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
   const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
   const int row_atoms = static_cast<int>((C / 32 + 3) / 4);
-  mxfp8_colrow_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q_col),
+  mxfp8_colrow_kernel<kSlabDense><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), nullptr, ActParams{0, 1.0f, 0.0f}, num_rows, max_rows, static_cast<int>(C),
+      static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms,
+      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_mxfp8_rowcol_gather(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows, int64_t C,
+                                            void* q_row, void* scales_row_blocked, void* q_col,
+                                            void* scales_col_blocked, void* stream) {
+  if (!row_ptrs || !q_row || !scales_row_blocked || !q_col || !scales_col_blocked || max_rows < 0 || C <= 0 ||
+      (C % 32) != 0)
+    return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  const dim3 grid(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
+  const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  const int row_atoms = static_cast<int>((C / 32 + 3) / 4);
+  mxfp8_colrow_kernel<kSlabGather><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      nullptr, row_ptrs, ActParams{0, 1.0f, 0.0f}, num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q_col),
       static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms, static_cast<uint8_t*>(q_row),
       static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* num_rows, int64_t max_rows, int64_t F,
+                                                int clamped, float alpha, float limit, void* q_row,
+                                                void* scales_row_blocked, void* q_col, void* scales_col_blocked,
+                                                void* stream) {
+  if (!h1 || !q_row || !scales_row_blocked || !q_col || !scales_col_blocked || max_rows < 0 || F <= 0 || (F % 32) != 0)
+    return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  const dim3 grid(static_cast<unsigned>((F + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
+  const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  const int row_atoms = static_cast<int>((F / 32 + 3) / 4);
+  mxfp8_colrow_kernel<kSlabSwiglu><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(h1), nullptr, ActParams{clamped, alpha, limit}, num_rows, max_rows, static_cast<int>(F),
+      static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms,
+      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -355,6 +355,17 @@ int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_t max_rows,
  * Outputs are bit-identical to dm_quant_mxfp8_row (blocked scales) and dm_quant_mxfp8_col (blocked scales). C % 32 == 0. */
 int dm_quant_mxfp8_rowcol(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q_row,
                           void* scales_row_blocked, void* q_col, void* scales_col_blocked, void* stream);
+/* The same pair with the dispatch gather folded in: row r is read through row_ptrs[r] (peer memory allowed, a
+ * null pointer is a row of zeros), so the gathered bf16 rows are never written (the reference's gather+quantise
+ * dispatch, dist_moe/_blockscaled.py:461-507 `_stage_blockscaled_dispatch`). */
+int dm_quant_mxfp8_rowcol_gather(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows, int64_t C,
+                                 void* q_row, void* scales_row_blocked, void* q_col, void* scales_col_blocked,
+                                 void* stream);
+/* SwiGLU of h1 = [rows, 2F] ([gate | up]) rounded to bf16 as dm_swiglu_fwd rounds it, then quantised both ways:
+ * h2 itself is never written (dist_moe/_quantization.py:151-183 `swiglu_fwd_quantize`). F % 32 == 0. */
+int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* num_rows, int64_t max_rows, int64_t F, int clamped,
+                                     float alpha, float limit, void* q_row, void* scales_row_blocked, void* q_col,
+                                     void* scales_col_blocked, void* stream);
 int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
                           void* col_scales, int blocked, void* stream);
 int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,

@@ -184,3 +184,52 @@ def test_mxfp8_rowcol_equals_the_separate_kernels(rows, cols, cap):
     r, c = np.meshgrid(np.arange(rows), np.arange(cols // 32), indexing="ij")
     idx = Q.blocked_scale_offset(r, c, ra)
     np.testing.assert_array_equal(fs_r.cpu().numpy()[idx], s_r.cpu().numpy()[idx])
+
+
+@pytest.mark.parametrize("rows,cols,cap", [(96, 512, 128), (200, 1536, 256)])
+def test_mxfp8_rowcol_with_gather_and_with_swiglu_equal_the_staged_forms(rows, cols, cap):
+    """The quantiser that pulls rows through a pointer table, and the one that applies SwiGLU to h1 first, give the
+    bytes of gather -> quantise and SwiGLU -> quantise run as separate kernels."""
+    nat = _nat()
+    st = nat.stream_ptr()
+    cnt = torch.tensor([rows], dtype=torch.int32, device=DEV)
+    ra, ca = (cols // 32 + 3) // 4, ((cap + 31) // 32 + 3) // 4
+    n_rs, n_cs = (cap + 127) // 128 * 128 * ra * 4, (cols + 127) // 128 * 128 * ca * 4
+
+    def outputs():
+        return (torch.zeros(cap, cols, dtype=torch.uint8, device=DEV), torch.zeros(n_rs, dtype=torch.uint8, device=DEV),
+                torch.zeros(cap, cols, dtype=torch.uint8, device=DEV), torch.zeros(n_cs, dtype=torch.uint8, device=DEV))
+
+    # --- gather: a permutation of source rows with every seventh pointer null
+    src = _data(rows, cols, rows + 11, specials=False).to(DEV)
+    perm = torch.randperm(rows, generator=torch.Generator().manual_seed(rows))
+    ptrs = torch.tensor([0 if i % 7 == 3 else src.data_ptr() + int(perm[i]) * cols * 2 for i in range(rows)],
+                        dtype=torch.int64, device=DEV)
+    dense = src[perm.to(DEV)].clone()
+    dense[torch.arange(rows, device=DEV) % 7 == 3] = 0
+    want = outputs()
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol(dense.data_ptr(), cnt.data_ptr(), cap, cols, want[0].data_ptr(),
+                                            want[1].data_ptr(), want[2].data_ptr(), want[3].data_ptr(), st), "rowcol")
+    got = outputs()
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol_gather(ptrs.data_ptr(), cnt.data_ptr(), cap, cols, got[0].data_ptr(),
+                                                   got[1].data_ptr(), got[2].data_ptr(), got[3].data_ptr(), st), "gather")
+    torch.cuda.synchronize()
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+
+    # --- SwiGLU (plain and clamped) of h1 = [gate | up]
+    for clamped in (0, 1):
+        h1 = (torch.randn(rows, 2 * cols, generator=torch.Generator().manual_seed(5 + clamped)) * 3).bfloat16().to(DEV)
+        h2 = torch.zeros(rows, cols, dtype=torch.bfloat16, device=DEV)
+        nat.check(nat.lib.dm_swiglu_fwd(h1.data_ptr(), None, h2.data_ptr(), None, cnt.data_ptr(), rows, cols, clamped, 1.702,
+                                        7.0, None, 0.0, None, st), "swiglu")
+        want = outputs()
+        nat.check(nat.lib.dm_quant_mxfp8_rowcol(h2.data_ptr(), cnt.data_ptr(), cap, cols, want[0].data_ptr(),
+                                                want[1].data_ptr(), want[2].data_ptr(), want[3].data_ptr(), st), "rowcol")
+        got = outputs()
+        nat.check(nat.lib.dm_swiglu_fwd_quant_mxfp8_rowcol(h1.data_ptr(), cnt.data_ptr(), cap, cols, clamped, 1.702, 7.0,
+                                                           got[0].data_ptr(), got[1].data_ptr(), got[2].data_ptr(),
+                                                           got[3].data_ptr(), st), "swiglu+quant")
+        torch.cuda.synchronize()
+        for g, w in zip(got, want):
+            assert torch.equal(g, w)

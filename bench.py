@@ -620,8 +620,28 @@ def run_micro(args):
         "wgrad": lambda: nat.lib.dm_gemm_wgrad(op(h1), op(x), dw13.data_ptr(), 0, 1, off.data_ptr(), e, rows, 2 * F, D,
                                                0, status.data_ptr(), st),
     }
+    if args.micro.startswith("bs-"):
+        # block-scaled forward GEMM (W13 with the SwiGLU epilogue) on synthetic quantised bytes: timing does not
+        # depend on the values, scale bytes are 1.0 in their format
+        fp4 = args.micro == "bs-nvfp4"
+        n, k = (4096, 7168) if fp4 else (3072, 4096)
+        rows = 8192
+        off = torch.arange(0, e + 1, dtype=torch.int32, device=dev) * (rows // e)
+        kb, per_scale = (k // 2, 16) if fp4 else (k, 32)
+        atoms = (k // per_scale + 3) // 4
+        qa = torch.randint(0, 120, (rows + 256, kb), dtype=torch.uint8, device=dev, generator=g)
+        qw = torch.randint(0, 120, (e * n, kb), dtype=torch.uint8, device=dev, generator=g)
+        sa = torch.full((rows * atoms * 4,), 0x38 if fp4 else 127, dtype=torch.uint8, device=dev)
+        sw = torch.full((e * n * atoms * 4,), 0x38 if fp4 else 127, dtype=torch.uint8, device=dev)
+        inv = torch.ones(rows, dtype=torch.float32, device=dev)
+        einv = torch.ones(e, dtype=torch.float32, device=dev)
+        hq = torch.zeros(rows + 8, n // 2, dtype=torch.bfloat16, device=dev)
+        calls[args.micro] = lambda: nat.lib.dm_gemm_blockscaled(
+            1 if fp4 else 0, op(qa), op(sa), qw.data_ptr(), sw.data_ptr(), none, op(hq), None, op(inv) if fp4 else none,
+            einv.data_ptr() if fp4 else None, off.data_ptr(), e, rows, n, k, 1, 0, 1.0, 0.0, None, 0, status.data_ptr(), st)
+        flops_bs = 2.0 * rows * n * k
     fn = calls[args.micro]
-    flops = 2.0 * rows * D * 2 * F
+    flops = flops_bs if args.micro.startswith("bs-") else 2.0 * rows * D * 2 * F
     for _ in range(2):
         nat.check(fn(), args.micro)
     torch.cuda.synchronize()
@@ -650,7 +670,7 @@ def main():
                     help="time eager routed_experts calls instead of CUDA-graph replays of the same step")
     ap.add_argument("--cta-pairs", action="store_true",
                     help="run forward / input-gradient GEMMs on the CTA-pair kernel (tcgen05 cta_group::2)")
-    ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad"],
+    ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
     ap.add_argument("--workload", default="bf16-train", choices=["bf16-train"] + sorted(INFERENCE_WORKLOADS),
                     help="bf16-train is the headline training layer; the others are forward-only inference layers")

@@ -479,6 +479,8 @@ def run_inference(args):
     fmt, Tn, Dn, Fn, En, Kn, clamped, routing = INFERENCE_WORKLOADS[args.workload]
     if args.tokens:
         Tn = args.tokens
+    if args.experts:
+        En = args.experts  # e.g. E / 8: one rank's share of the experts of the EP=8 configuration on one GPU
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -529,11 +531,15 @@ def run_inference(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    from dist_moe_b200 import _native
+
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side), torch.no_grad():
         for _ in range(3):
+            l0 = _native.LAUNCHES[0]
             dm.routed_experts(x, ids, scores, p13, p2, ctx)
+            launches_per_step = _native.LAUNCHES[0] - l0
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
     with torch.no_grad(), torch.cuda.graph(graph):
@@ -581,7 +587,7 @@ def run_inference(args):
                                    f"K={Kn}, {'clamped' if clamped else 'plain'} SwiGLU, forward only",
                        "l2": "no flush: the prepared weights of the experts hit exceed the 126 MB L2"
                        if weight_bytes > 126e6 else "weights of the experts hit fit in L2 between replays"},
-            "gpu_launches": None, "step_mode": "cuda-graph replay", "clocks": clocks,
+            "gpu_launches": launches_per_step * args.steps, "step_mode": "cuda-graph replay", "clocks": clocks,
             "rows_rank0": rows, "experts_hit_rank0": hit,
             "achieved": {"weight_stream_GBps": weight_bytes / (p50 * 1e-3) / 1e9, "hbm_peak_GBps": pk["hbm_gbs"],
                          "tflops": flops / (p50 * 1e-3) / 1e12, "peak_source": src},
@@ -675,6 +681,7 @@ def main():
     ap.add_argument("--workload", default="bf16-train", choices=["bf16-train"] + sorted(INFERENCE_WORKLOADS),
                     help="bf16-train is the headline training layer; the others are forward-only inference layers")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank of an inference workload (sweeps)")
+    ap.add_argument("--experts", type=int, default=0, help="total experts of an inference workload (default: the config's)")
     args = ap.parse_args()
     if args.cta_pairs and args.impl == "ours":
         from dist_moe_b200 import _native

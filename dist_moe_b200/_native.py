@@ -82,6 +82,7 @@ _SIGNATURES = {
     ),
     "dm_set_gemm_pairs": (c_int, [c_int]),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
+    "dm_set_route_decode_kernel": (c_int, [c_int]),
     "dm_gemm_blockscaled_dgrad": (
         c_int,
         [Operand, Operand, _P, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P],

@@ -241,6 +241,106 @@ __global__ void __launch_bounds__(kChunkTokens) route_fill_kernel(RouteParams p)
 }
 
 // ---------------------------------------------------------------------------
+// Decode regime: the whole routing step in one CTA and one launch (the reference's single-launch path,
+// dist_moe/_routing_metadata.py:265-300 and kernels/triton/dist_dispatch_routing_kernel.py:120-260, which
+// orders rows inside an expert by an atomic counter; this kernel keeps the general path's deterministic order).
+//
+// Thread i = source_rank * T + token (ep * T <= 1024), so ascending thread index is the (source rank, token)
+// order of the output rows inside an expert: a row's position is its expert's base + the routes of lower warps
+// + the routes of lower lanes of its own warp, all from per-warp lane masks in shared memory.  No workspace,
+// no histogram in global memory, no memset.
+// ---------------------------------------------------------------------------
+constexpr int kDecodeThreads = 1024;
+constexpr int kDecodeWarps = kDecodeThreads / 32;
+
+__global__ void __launch_bounds__(kDecodeThreads) route_decode_kernel(RouteParams p) {
+  extern __shared__ uint32_t smem_u[];
+  uint32_t* mask = smem_u;                                                // [32][e_local] lane masks
+  uint32_t* wprefix = mask + kDecodeWarps * p.e_local;                    // [32][e_local] routes of lower warps
+  int32_t* hist_s = reinterpret_cast<int32_t*>(wprefix + kDecodeWarps * p.e_local);  // [E]
+  int32_t* total = hist_s + p.E;                                          // [e_local] real rows
+  int32_t* base = total + p.e_local;                                      // [e_local + 1] padded exclusive prefix
+  __shared__ int overflow;
+  const int i = threadIdx.x, warp = i >> 5, lane = i & 31;
+  for (int j = i; j < kDecodeWarps * p.e_local; j += kDecodeThreads) mask[j] = 0u;
+  for (int j = i; j < p.E; j += kDecodeThreads) hist_s[j] = 0;
+  __syncthreads();
+  const int s = i / p.T, tok = i - s * p.T;
+  const bool live = s < p.ep;
+  const int first = p.rank * p.e_local;
+  const int16_t* ids = nullptr;
+  if (live) {
+    if (tok == 0) {
+      const int peer_t = *reinterpret_cast<const int32_t*>(p.routing_ptrs[s]);
+      if (peer_t != p.T) set_status(p.status, kTokenCountMismatch, s, peer_t, p.T);
+    }
+    ids = reinterpret_cast<const int16_t*>(p.routing_ptrs[s] + DM_ROUTING_HEADER_BYTES) + static_cast<int64_t>(tok) * p.K;
+    for (int k = 0; k < p.K; ++k) {
+      const int e = ids[k];
+      if (e < 0 || e >= p.E) continue;
+      atomicAdd(&hist_s[e], 1);
+      const int el = e - first;
+      if (el >= 0 && el < p.e_local) atomicOr(&mask[warp * p.e_local + el], 1u << lane);
+    }
+  }
+  __syncthreads();
+  for (int el = i; el < p.e_local; el += kDecodeThreads) {
+    int running = 0;
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      wprefix[w * p.e_local + el] = running;
+      running += __popc(mask[w * p.e_local + el]);
+    }
+    total[el] = running;
+  }
+  __syncthreads();
+  if (i == 0) {
+    int64_t acc = 0;
+    for (int el = 0; el < p.e_local; ++el) {
+      base[el] = static_cast<int32_t>(acc);
+      acc += pad_rows(total[el], p.m_mult);
+    }
+    base[p.e_local] = static_cast<int32_t>(acc);
+    overflow = (acc > p.capacity_rows || acc > p.ptrs_size) ? 1 : 0;
+    if (overflow) set_status(p.status, kCapacityExceeded, static_cast<int>(acc), static_cast<int>(p.capacity_rows));
+  }
+  __syncthreads();
+  const bool bad = overflow != 0;
+  for (int el = i; el <= p.e_local; el += kDecodeThreads) {
+    p.expert_offsets[el] = bad ? 0 : base[el];
+    if (el < p.e_local) p.counts[el] = bad ? 0 : pad_rows(total[el], p.m_mult);
+  }
+  for (int q = i; q < p.ep; q += kDecodeThreads) {
+    int acc = 0;
+    for (int el = 0; el < p.e_local; ++el) acc += pad_rows(hist_s[q * p.e_local + el], p.m_mult);
+    p.per_rank[q] = acc;
+  }
+  if (bad) return;
+  if (p.m_mult > 0) {
+    // Padding rows of every expert segment hold a null pointer.
+    for (int el = warp; el < p.e_local; el += kDecodeWarps) {
+      const int lo = base[el] + total[el], hi = base[el + 1];
+      for (int r = lo + lane; r < hi; r += 32) {
+        p.fwd[r] = 0;
+        p.sct[r] = 0;
+        if (p.bwd != nullptr) p.bwd[r] = 0;
+      }
+    }
+  }
+  if (!live) return;
+  const uint64_t dbase = p.dispatch_ptrs[s], cbase = p.combine_ptrs[s];
+  for (int k = 0; k < p.K; ++k) {
+    const int el = static_cast<int>(ids[k]) - first;
+    if (ids[k] < 0 || ids[k] >= p.E || el < 0 || el >= p.e_local) continue;
+    const int pos = base[el] + static_cast<int>(wprefix[warp * p.e_local + el]) +
+                    __popc(mask[warp * p.e_local + el] & ((1u << lane) - 1u));
+    const int64_t route = static_cast<int64_t>(tok) * p.K + k;
+    p.fwd[pos] = static_cast<int64_t>(dbase + static_cast<uint64_t>(tok) * p.gather_stride);
+    p.sct[pos] = static_cast<int64_t>(cbase + static_cast<uint64_t>(route) * p.scatter_stride);
+    if (p.bwd != nullptr) p.bwd[pos] = static_cast<int64_t>(dbase + static_cast<uint64_t>(route) * p.bwd_stride);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Row gather through a pointer table (sources may be peer memory)
 // ---------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const int64_t* __restrict__ ptrs, const int32_t* __restrict__ num_rows,
@@ -324,6 +424,14 @@ extern "C" int64_t dm_route_workspace_words(int64_t T, int ep, int E) {
   return 2 * ep * chunks * e_local + E;
 }
 
+static int g_route_decode = 1;
+
+extern "C" int dm_set_route_decode_kernel(int enabled) {
+  const int previous = g_route_decode;
+  g_route_decode = enabled ? 1 : 0;
+  return previous;
+}
+
 static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
                         int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
                         int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,
@@ -368,6 +476,18 @@ static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
   p.hist = workspace + 2 * n;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (g_route_decode && static_cast<int64_t>(ep) * T <= kDecodeThreads && p.e_local <= 512) {
+    const size_t smem = sizeof(uint32_t) * (2 * kDecodeWarps * p.e_local + E + 2 * p.e_local + 1);
+    static bool attr_set = false;
+    if (!attr_set) {
+      const cudaError_t ea = cudaFuncSetAttribute(route_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(sizeof(uint32_t) * (2 * kDecodeWarps * 512 + kMaxExpertsSmem + 1025)));
+      if (ea != cudaSuccess) return static_cast<int>(ea);
+      attr_set = true;
+    }
+    route_decode_kernel<<<1, kDecodeThreads, smem, st>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
   cudaError_t err = cudaMemsetAsync(p.hist, 0, sizeof(int32_t) * E, st);
   if (err != cudaSuccess) return static_cast<int>(err);
   const dim3 grid(p.chunks, ep);

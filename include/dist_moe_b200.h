@@ -122,6 +122,12 @@ int dm_route_static(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs,
                     int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
                     int64_t* scatter_ptrs, int* status, void* stream);
 
+/* Kernel selection for dm_route / dm_route_static: non-zero (default) lets calls with ep * T <= 1024 run the whole
+ * routing step in one single-CTA launch (the decode regime; the reference's single-launch path,
+ * dist_moe/_routing_metadata.py:265-300); zero keeps every call on the three general kernels.  Both produce the
+ * same tables bit for bit (rows ordered by local expert, source rank, token).  Returns the previous setting. */
+int dm_set_route_decode_kernel(int enabled);
+
 /* ---------------------------------------------------------------------------
  * Activation-arena planner, BF16
  * (dist_moe/_activation_buffer.py:2318-2591 `get_forward_plan`/`get_backward_plan`;

@@ -115,3 +115,36 @@ def test_route_reports_capacity_and_invalid_ids_without_trapping():
     bad[0, 0, 0] = 99
     out = run_route(bad, 0, 8, disp, comb, 512, 512, 512, 0)
     assert out["status"][0] == 3, out["status"]  # invalid expert id, reported by the publication check
+
+
+@pytest.mark.parametrize("ep,T,K,E,m_mult", [(8, 128, 8, 256, 128), (1, 128, 8, 256, 128), (2, 512, 4, 64, 0),
+                                             (4, 256, 8, 32, 128), (1, 1, 1, 4, 0), (8, 100, 6, 64, 0)])
+def test_single_launch_decode_routing_equals_the_general_path_and_the_oracle(ep, T, K, E, m_mult):
+    """ep * T <= 1024 takes the one-CTA kernel; its tables are those of the three general kernels and of the oracle."""
+    nat = _native()
+    rng = np.random.default_rng(77 + ep + T)
+    ids = np.argsort(-rng.standard_normal((ep, T, E)), axis=-1)[..., :K].astype(np.int64)
+    if T > 4:
+        ids[rng.random(ids.shape) < 0.03] = -1
+    disp = [(s + 1) << 40 for s in range(ep)]
+    comb = [((s + 1) << 40) | (1 << 39) for s in range(ep)]
+    stride = 7168
+    for rank in sorted({0, ep - 1}):
+        outs = {}
+        for decode in (0, 1):
+            previous = nat.lib.dm_set_route_decode_kernel(decode)
+            try:
+                outs[decode] = run_route(ids, rank, E, disp, comb, stride, stride, stride, m_mult)
+            finally:
+                nat.lib.dm_set_route_decode_kernel(previous)
+            assert outs[decode]["status"][0] == 0, outs[decode]["status"]
+        t = oracle_routing.route(ids, rank, E, disp, comb, stride, stride, stride, m_mult)
+        rows = int(t.expert_offsets[-1])
+        for key in ("counts", "per_rank", "offsets"):
+            np.testing.assert_array_equal(outs[1][key], outs[0][key])
+        for key in ("fwd", "bwd", "sct"):
+            np.testing.assert_array_equal(outs[1][key][:rows], outs[0][key][:rows])
+        np.testing.assert_array_equal(outs[1]["counts"], t.counts)
+        np.testing.assert_array_equal(outs[1]["per_rank"], t.per_rank)
+        np.testing.assert_array_equal(outs[1]["fwd"][:rows], t.fwd)
+        np.testing.assert_array_equal(outs[1]["sct"][:rows], t.sct)

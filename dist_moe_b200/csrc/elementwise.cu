@@ -141,19 +141,37 @@ __global__ void __launch_bounds__(256) scale_and_sum_kernel(const uint4* __restr
     const int64_t t = i / vec_per_row;
     const int v = static_cast<int>(i - t * vec_per_row);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < K; ++k) {
-      const int64_t route = t * K + k;
-      const uint4 raw = h3[route * vec_per_row + v];
-      if (save) save_dst[route * vec_per_row + v] = raw;
-      if (ids[route] < 0) continue;
-      float w = 1.0f;
-      if (scores != nullptr)
-        w = scores_are_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(scores)[route])
-                            : static_cast<const float*>(scores)[route];
-      float h[8];
-      unpack8(raw, h);
+    // Four routes are fetched before any is used (independent 16-byte loads in flight); they are then added in
+    // ascending k, the order of the one-at-a-time loop, so the fp32 sums are unchanged.
+    for (int k0 = 0; k0 < K; k0 += 4) {
+      uint4 raw[4];
+      float w[4];
+      bool ok[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += h[j] * w;
+      for (int q = 0; q < 4; ++q) {
+        ok[q] = false;
+        w[q] = 1.0f;
+        if (k0 + q < K) {
+          const int64_t route = t * K + k0 + q;
+          raw[q] = h3[route * vec_per_row + v];
+          ok[q] = ids[route] >= 0;
+          if (scores != nullptr)
+            w[q] = scores_are_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(scores)[route])
+                                   : static_cast<const float*>(scores)[route];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (k0 + q < K) {
+          if (save) save_dst[(t * K + k0 + q) * vec_per_row + v] = raw[q];
+          if (ok[q]) {
+            float h[8];
+            unpack8(raw[q], h);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += h[j] * w[q];
+          }
+        }
+      }
     }
     out[i] = pack8(acc);
   }

@@ -549,17 +549,12 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
                                                     state.num_sms, status, st), "dm_gemm_blockscaled_wgrad(w2)")
         grad_w2 = dst.view(w2_param.shape) if ret else None
     # ---- SwiGLU backward, W13 ---------------------------------------------------------------
-    nat.check(nat.lib.dm_swiglu_bwd(c.h1.data_ptr(), None, _ptr(dh2), None, _ptr(dh1), None, recv, R, F, clamped, alpha,
-                                    limit, st), "dm_swiglu_bwd")
-    if need_x and need_w13:
-        nat.check(nat.lib.dm_quant_mxfp8_rowcol(_ptr(dh1), recv, R, 2 * F, _ptr(d1q), _ptr(d1sf), _ptr(d1c), _ptr(d1csf),
-                                                st), "dm_quant_mxfp8_rowcol(dh1)")
-    elif need_x:
-        nat.check(nat.lib.dm_quant_mxfp8_row(_ptr(dh1), recv, R, 2 * F, _ptr(d1q), 0, _ptr(d1sf), 0, 1, st),
-                  "dm_quant_mxfp8_row(dh1)")
-    elif need_w13:
-        nat.check(nat.lib.dm_quant_mxfp8_col(_ptr(dh1), recv, R, 2 * F, _ptr(d1c), _ptr(d1csf), 1, st),
-                  "dm_quant_mxfp8_col(dh1)")
+    if need_x or need_w13:
+        # grad_h1 goes straight from the SwiGLU backward arithmetic into its quantised copies
+        nat.check(nat.lib.dm_swiglu_bwd_quant_mxfp8(c.h1.data_ptr(), _ptr(dh2), recv, R, F, clamped, alpha, limit,
+                                                    _ptr(d1q) if need_x else None, _ptr(d1sf) if need_x else None,
+                                                    _ptr(d1c) if need_w13 else None, _ptr(d1csf) if need_w13 else None,
+                                                    st), "dm_swiglu_bwd_quant_mxfp8")
     if need_x:
         nat.check(nat.lib.dm_gemm_blockscaled_dgrad(d1q, d1sf, c.p13.fprop_data.data_ptr(),
                                                     c.p13.dgrad_scale.data_ptr(), none, c.bwd.data_ptr(), offs, el, R, D,

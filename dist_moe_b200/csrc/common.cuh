@@ -406,6 +406,26 @@ __device__ __forceinline__ float swiglu_f32(float gate, float up, const ActParam
   return gate * sigmoid_rn(gate) * up;
 }
 
+// Gradients of h2 = SwiGLU(x, y) with respect to the gate x and the up value y, given dz = dL/dh2
+// (dist_moe/kernels/triton/swiglu.py:639-668: where a clamp saturates, that input's gradient is zero).
+__device__ __forceinline__ void swiglu_bwd_f32(float x, float y, float dz, const ActParams& act, float& dx, float& dy) {
+  if (act.clamped) {
+    const float g = fminf(x, act.limit);
+    const float u = fminf(fmaxf(y, -act.limit), act.limit);
+    const float s = sigmoid_rn(act.alpha * g);
+    const float silu = g * s;
+    const float d_silu = s + act.alpha * g * s * (1.0f - s);
+    float a = dz * (u + 1.0f) * d_silu;
+    float b = dz * silu;
+    dx = x > act.limit ? 0.0f : a;
+    dy = (y > act.limit || y < -act.limit) ? 0.0f : b;
+  } else {
+    const float s = sigmoid_rn(x);
+    dx = dz * y * s * (1.0f + x - x * s);
+    dy = dz * x * s;
+  }
+}
+
 __host__ __device__ constexpr int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ constexpr int64_t align_up64(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 

@@ -101,23 +101,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint8_t* h1_base,
     unpack8(h1[r * 2 * vec_per_row + vec_per_row + v], y);
     unpack8(gh2[r * vec_per_row + v], dz);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (act.clamped) {
-        const float g = fminf(x[j], act.limit);
-        const float u = fminf(fmaxf(y[j], -act.limit), act.limit);
-        const float s = sigmoid_rn(act.alpha * g);
-        const float silu = g * s;
-        const float d_silu = s + act.alpha * g * s * (1.0f - s);
-        float a = dz[j] * (u + 1.0f) * d_silu;
-        float b = dz[j] * silu;
-        dx[j] = x[j] > act.limit ? 0.0f : a;
-        dy[j] = (y[j] > act.limit || y[j] < -act.limit) ? 0.0f : b;
-      } else {
-        const float s = sigmoid_rn(x[j]);
-        dx[j] = dz[j] * y[j] * s * (1.0f + x[j] - x[j] * s);
-        dy[j] = dz[j] * x[j] * s;
-      }
-    }
+    for (int j = 0; j < 8; ++j) swiglu_bwd_f32(x[j], y[j], dz[j], act, dx[j], dy[j]);
     gh1[r * 2 * vec_per_row + v] = pack8(dx);
     gh1[r * 2 * vec_per_row + vec_per_row + v] = pack8(dy);
   }

@@ -248,6 +248,87 @@ __device__ __forceinline__ float amax_from_bf16_bits(uint32_t bits15) {
 // bf16 exactly as the standalone activation kernel rounds it.
 enum SlabSource : int { kSlabDense = 0, kSlabGather = 1, kSlabSwiglu = 2 };
 
+// Row pass, column pass and stores for one staged slab (see above).  `limit` bounds the columns this slab may
+// touch (the matrix width, or the end of the gate half when a CTA stages two slabs), `C` is the row pitch of the
+// outputs.  Called by every thread of the CTA after the slab has been written and a barrier has passed.
+__device__ __forceinline__ void slab_quantise(uint8_t* slab, int64_t rows, int64_t row0, int col0, int limit, int C,
+                                              int64_t max_rows, uint8_t* __restrict__ q_col, uint8_t* __restrict__ s_col,
+                                              int blocked, int col_atoms, uint8_t* __restrict__ q_row,
+                                              uint8_t* __restrict__ s_row, int row_atoms) {
+  const int t = threadIdx.x;
+  if (q_row != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int r = t & 31, b = (t >> 5) + 8 * k;
+      const int colb = col0 + b * 32;
+      if (row0 + r < rows && colb < limit) {
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 v = *reinterpret_cast<const uint4*>(slab + r * kSlabRawStride + b * 64 + j * 16);
+          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+        uint32_t m = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m = __vmaxu2(m, w[j] & 0x7fff7fffu);
+        const uint32_t top = (m >> 16) > (m & 0xffffu) ? (m >> 16) : (m & 0xffffu);
+        float recip;
+        const uint8_t byte = mxfp8_scale(amax_from_bf16_bits(top), recip);
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          o[j] = e4m3x4(__uint_as_float(w[2 * j] << 16) * recip, __uint_as_float(w[2 * j] & 0xffff0000u) * recip,
+                        __uint_as_float(w[2 * j + 1] << 16) * recip, __uint_as_float(w[2 * j + 1] & 0xffff0000u) * recip);
+        uint4* dst = reinterpret_cast<uint4*>(q_row + (row0 + r) * C + colb);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        s_row[blocked_offset(row0 + r, colb >> 5, row_atoms)] = byte;
+      }
+    }
+  }
+  if (q_col == nullptr) return;  // uniform over the CTA
+
+  // column pass: 32 rows of two adjacent columns per thread
+  uint32_t w[32];
+#pragma unroll
+  for (int r = 0; r < 32; ++r) w[r] = *reinterpret_cast<const uint32_t*>(slab + r * kSlabRawStride + t * 4);
+  uint32_t m = 0;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) m = __vmaxu2(m, w[r] & 0x7fff7fffu);
+  float recip0, recip1;
+  const uint8_t byte0 = mxfp8_scale(amax_from_bf16_bits(m & 0xffffu), recip0);
+  const uint8_t byte1 = mxfp8_scale(amax_from_bf16_bits(m >> 16), recip1);
+  const int c = col0 + 2 * t;
+  if (c < limit) {
+    const int64_t rb = row0 >> 5;
+    if (blocked) {
+      s_col[blocked_offset(c, static_cast<int>(rb), col_atoms)] = byte0;
+      s_col[blocked_offset(c + 1, static_cast<int>(rb), col_atoms)] = byte1;
+    } else {
+      const int64_t per_col = (max_rows + 31) / 32;
+      s_col[static_cast<int64_t>(c) * per_col + rb] = byte0;
+      s_col[static_cast<int64_t>(c + 1) * per_col + rb] = byte1;
+    }
+  }
+  __syncthreads();  // every thread holds what it needs of the raw slab: its storage now takes the quantised bytes
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const uint32_t pk = __nv_cvt_float2_to_fp8x2(
+        make_float2(__uint_as_float(w[r] << 16) * recip0, __uint_as_float(w[r] & 0xffff0000u) * recip1), __NV_SATFINITE,
+        __NV_E4M3);
+    *reinterpret_cast<uint16_t*>(slab + r * kSlabOutStride + t * 2) = static_cast<uint16_t>(pk);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = t + 256 * k;
+    const int r = i >> 5, v = i & 31;
+    if (row0 + r < rows && col0 + v * 16 < limit)
+      *reinterpret_cast<uint4*>(q_col + (row0 + r) * C + col0 + v * 16) =
+          *reinterpret_cast<const uint4*>(slab + r * kSlabOutStride + v * 16);
+  }
+}
+
 template <int kSource>
 __global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restrict__ x, const int64_t* __restrict__ row_ptrs,
                                                            ActParams act, const int32_t* num_rows,
@@ -290,77 +371,50 @@ __global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restri
     *reinterpret_cast<uint4*>(slab + r * kSlabRawStride + v * 16) = val;
   }
   __syncthreads();
+  slab_quantise(slab, rows, row0, col0, C, C, max_rows, q_col, s_col, blocked, col_atoms, q_row, s_row, row_atoms);
+}
 
-  if (q_row != nullptr) {
+// SwiGLU backward fused in: from h1 = [gate | up] ([rows, 2F]) and dz = dL/dh2 ([rows, F]) a CTA computes the
+// gate-gradient slab and the matching up-gradient slab of grad_h1 = [dgate | dup] (rounded to bf16 as the standalone
+// backward kernel rounds them) and quantises both; grad_h1 itself is never written.  Either copy may be left out.
+__global__ void __launch_bounds__(256) mxfp8_swiglu_bwd_colrow_kernel(const uint4* __restrict__ h1,
+                                                                      const uint4* __restrict__ dz, ActParams act,
+                                                                      const int32_t* num_rows, int64_t max_rows, int F,
+                                                                      uint8_t* __restrict__ q_col,
+                                                                      uint8_t* __restrict__ s_col, int col_atoms,
+                                                                      uint8_t* __restrict__ q_row,
+                                                                      uint8_t* __restrict__ s_row, int row_atoms) {
+  extern __shared__ __align__(16) uint8_t slabs[];  // two slabs
+  uint8_t* slab_g = slabs;
+  uint8_t* slab_u = slabs + 32 * kSlabRawStride;
+  int64_t rows = num_rows ? *num_rows : max_rows;
+  if (rows > max_rows) rows = max_rows;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.y) * 32;
+  const int col0 = blockIdx.x * kSlabCols;
+  if (row0 >= rows) return;
+  const int t = threadIdx.x;
+  const int vec_per_row = F >> 3;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int r = t & 31, b = (t >> 5) + 8 * k;
-      const int colb = col0 + b * 32;
-      if (row0 + r < rows && colb < C) {
-        uint32_t w[16];
+  for (int k = 0; k < 8; ++k) {
+    const int i = t + 256 * k;
+    const int r = i >> 6, v = i & 63;
+    uint4 dg4 = make_uint4(0, 0, 0, 0), du4 = make_uint4(0, 0, 0, 0);
+    if (row0 + r < rows && col0 + v * 8 < F) {
+      float x[8], y[8], d[8], dx[8], dy[8];
+      unpack8f(h1[(row0 + r) * 2 * vec_per_row + (col0 >> 3) + v], x);
+      unpack8f(h1[(row0 + r) * 2 * vec_per_row + vec_per_row + (col0 >> 3) + v], y);
+      unpack8f(dz[(row0 + r) * vec_per_row + (col0 >> 3) + v], d);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 v = *reinterpret_cast<const uint4*>(slab + r * kSlabRawStride + b * 64 + j * 16);
-          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-        }
-        uint32_t m = 0;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) m = __vmaxu2(m, w[j] & 0x7fff7fffu);
-        const uint32_t top = (m >> 16) > (m & 0xffffu) ? (m >> 16) : (m & 0xffffu);
-        float recip;
-        const uint8_t byte = mxfp8_scale(amax_from_bf16_bits(top), recip);
-        uint32_t o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          o[j] = e4m3x4(__uint_as_float(w[2 * j] << 16) * recip, __uint_as_float(w[2 * j] & 0xffff0000u) * recip,
-                        __uint_as_float(w[2 * j + 1] << 16) * recip, __uint_as_float(w[2 * j + 1] & 0xffff0000u) * recip);
-        uint4* dst = reinterpret_cast<uint4*>(q_row + (row0 + r) * C + colb);
-        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-        s_row[blocked_offset(row0 + r, colb >> 5, row_atoms)] = byte;
-      }
+      for (int j = 0; j < 8; ++j) swiglu_bwd_f32(x[j], y[j], d[j], act, dx[j], dy[j]);
+      dg4 = make_uint4(pack_bf16x2(dx[0], dx[1]), pack_bf16x2(dx[2], dx[3]), pack_bf16x2(dx[4], dx[5]), pack_bf16x2(dx[6], dx[7]));
+      du4 = make_uint4(pack_bf16x2(dy[0], dy[1]), pack_bf16x2(dy[2], dy[3]), pack_bf16x2(dy[4], dy[5]), pack_bf16x2(dy[6], dy[7]));
     }
-  }
-
-  // column pass: 32 rows of two adjacent columns per thread
-  uint32_t w[32];
-#pragma unroll
-  for (int r = 0; r < 32; ++r) w[r] = *reinterpret_cast<const uint32_t*>(slab + r * kSlabRawStride + t * 4);
-  uint32_t m = 0;
-#pragma unroll
-  for (int r = 0; r < 32; ++r) m = __vmaxu2(m, w[r] & 0x7fff7fffu);
-  float recip0, recip1;
-  const uint8_t byte0 = mxfp8_scale(amax_from_bf16_bits(m & 0xffffu), recip0);
-  const uint8_t byte1 = mxfp8_scale(amax_from_bf16_bits(m >> 16), recip1);
-  const int c = col0 + 2 * t;
-  if (c < C) {
-    const int64_t rb = row0 >> 5;
-    if (blocked) {
-      s_col[blocked_offset(c, static_cast<int>(rb), col_atoms)] = byte0;
-      s_col[blocked_offset(c + 1, static_cast<int>(rb), col_atoms)] = byte1;
-    } else {
-      const int64_t per_col = (max_rows + 31) / 32;
-      s_col[static_cast<int64_t>(c) * per_col + rb] = byte0;
-      s_col[static_cast<int64_t>(c + 1) * per_col + rb] = byte1;
-    }
-  }
-  __syncthreads();  // every thread holds what it needs of the raw slab: its storage now takes the quantised bytes
-#pragma unroll
-  for (int r = 0; r < 32; ++r) {
-    const uint32_t pk = __nv_cvt_float2_to_fp8x2(
-        make_float2(__uint_as_float(w[r] << 16) * recip0, __uint_as_float(w[r] & 0xffff0000u) * recip1), __NV_SATFINITE,
-        __NV_E4M3);
-    *reinterpret_cast<uint16_t*>(slab + r * kSlabOutStride + t * 2) = static_cast<uint16_t>(pk);
+    *reinterpret_cast<uint4*>(slab_g + r * kSlabRawStride + v * 16) = dg4;
+    *reinterpret_cast<uint4*>(slab_u + r * kSlabRawStride + v * 16) = du4;
   }
   __syncthreads();
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int i = t + 256 * k;
-    const int r = i >> 5, v = i & 31;
-    if (row0 + r < rows && col0 + v * 16 < C)
-      *reinterpret_cast<uint4*>(q_col + (row0 + r) * C + col0 + v * 16) =
-          *reinterpret_cast<const uint4*>(slab + r * kSlabOutStride + v * 16);
-  }
+  slab_quantise(slab_g, rows, row0, col0, F, 2 * F, max_rows, q_col, s_col, 1, col_atoms, q_row, s_row, row_atoms);
+  slab_quantise(slab_u, rows, row0, F + col0, 2 * F, 2 * F, max_rows, q_col, s_col, 1, col_atoms, q_row, s_row, row_atoms);
 }
 
 // ---------------------------------------------------------------------------
@@ -620,6 +674,32 @@ extern "C" int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* n
   mxfp8_colrow_kernel<kSlabSwiglu><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(h1), nullptr, ActParams{clamped, alpha, limit}, num_rows, max_rows, static_cast<int>(F),
       static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms,
+      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, const int32_t* num_rows, int64_t max_rows,
+                                        int64_t F, int clamped, float alpha, float limit, void* q_row,
+                                        void* scales_row_blocked, void* q_col, void* scales_col_blocked, void* stream) {
+  if (!h1 || !grad_h2 || max_rows < 0 || F <= 0 || (F % 32) != 0) return kRcBadArg;
+  if ((q_row == nullptr) != (scales_row_blocked == nullptr) || (q_col == nullptr) != (scales_col_blocked == nullptr) ||
+      (q_row == nullptr && q_col == nullptr))
+    return kRcBadArg;
+  if (max_rows == 0) return kRcOk;
+  constexpr int kSmem = 2 * 32 * kSlabRawStride;
+  static bool attr_set = false;
+  if (!attr_set) {
+    const cudaError_t e =
+        cudaFuncSetAttribute(mxfp8_swiglu_bwd_colrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const dim3 grid(static_cast<unsigned>((F + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
+  const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
+  const int row_atoms = static_cast<int>((2 * F / 32 + 3) / 4);
+  mxfp8_swiglu_bwd_colrow_kernel<<<grid, 256, kSmem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(h1), static_cast<const uint4*>(grad_h2), ActParams{clamped, alpha, limit}, num_rows,
+      max_rows, static_cast<int>(F), static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), col_atoms,
       static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
   return static_cast<int>(cudaGetLastError());
 }

@@ -372,6 +372,12 @@ int dm_quant_mxfp8_rowcol_gather(const int64_t* row_ptrs, const int32_t* num_row
 int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* num_rows, int64_t max_rows, int64_t F, int clamped,
                                      float alpha, float limit, void* q_row, void* scales_row_blocked, void* q_col,
                                      void* scales_col_blocked, void* stream);
+/* SwiGLU backward and quantisation in one pass: from h1 = [rows, 2F] and grad_h2 = [rows, F] the row- and/or
+ * column-quantised grad_h1 = [dgate | dup] ([rows, 2F]; pass NULL for the pair that is not wanted), grad_h1 rounded
+ * to bf16 as dm_swiglu_bwd rounds it and never written (dist_moe/_quantization.py:186-215 `swiglu_bwd_quantize`). */
+int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, const int32_t* num_rows, int64_t max_rows, int64_t F,
+                              int clamped, float alpha, float limit, void* q_row, void* scales_row_blocked, void* q_col,
+                              void* scales_col_blocked, void* stream);
 int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
                           void* col_scales, int blocked, void* stream);
 int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,

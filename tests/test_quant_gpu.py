@@ -233,3 +233,43 @@ def test_mxfp8_rowcol_with_gather_and_with_swiglu_equal_the_staged_forms(rows, c
         torch.cuda.synchronize()
         for g, w in zip(got, want):
             assert torch.equal(g, w)
+
+
+@pytest.mark.parametrize("rows,F,cap,clamped", [(96, 512, 128, 0), (200, 1536, 256, 1), (70, 96, 128, 0)])
+def test_swiglu_backward_fused_into_the_quantiser_equals_the_staged_form(rows, F, cap, clamped):
+    """dm_swiglu_bwd_quant_mxfp8 gives the bytes of dm_swiglu_bwd followed by the row+column quantiser, and leaves
+    out the copy that is not asked for."""
+    nat = _nat()
+    st = nat.stream_ptr()
+    cnt = torch.tensor([rows], dtype=torch.int32, device=DEV)
+    C = 2 * F
+    ra, ca = (C // 32 + 3) // 4, ((cap + 31) // 32 + 3) // 4
+    n_rs, n_cs = (cap + 127) // 128 * 128 * ra * 4, (C + 127) // 128 * 128 * ca * 4
+
+    def outputs():
+        return (torch.zeros(cap, C, dtype=torch.uint8, device=DEV), torch.zeros(n_rs, dtype=torch.uint8, device=DEV),
+                torch.zeros(cap, C, dtype=torch.uint8, device=DEV), torch.zeros(n_cs, dtype=torch.uint8, device=DEV))
+
+    g = torch.Generator().manual_seed(31 + rows)
+    h1 = (torch.randn(rows, C, generator=g) * 4).bfloat16().to(DEV)
+    dz = (torch.randn(rows, F, generator=g) * torch.logspace(-3, 2, rows)[:, None]).bfloat16().to(DEV)
+    dh1 = torch.zeros(rows, C, dtype=torch.bfloat16, device=DEV)
+    nat.check(nat.lib.dm_swiglu_bwd(h1.data_ptr(), None, dz.data_ptr(), None, dh1.data_ptr(), None, cnt.data_ptr(), rows, F,
+                                    clamped, 1.702, 7.0, st), "swiglu_bwd")
+    want = outputs()
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol(dh1.data_ptr(), cnt.data_ptr(), cap, C, want[0].data_ptr(), want[1].data_ptr(),
+                                            want[2].data_ptr(), want[3].data_ptr(), st), "rowcol")
+    got = outputs()
+    nat.check(nat.lib.dm_swiglu_bwd_quant_mxfp8(h1.data_ptr(), dz.data_ptr(), cnt.data_ptr(), cap, F, clamped, 1.702, 7.0,
+                                                got[0].data_ptr(), got[1].data_ptr(), got[2].data_ptr(), got[3].data_ptr(),
+                                                st), "fused")
+    only_row, only_col = outputs(), outputs()
+    nat.check(nat.lib.dm_swiglu_bwd_quant_mxfp8(h1.data_ptr(), dz.data_ptr(), cnt.data_ptr(), cap, F, clamped, 1.702, 7.0,
+                                                only_row[0].data_ptr(), only_row[1].data_ptr(), None, None, st), "row only")
+    nat.check(nat.lib.dm_swiglu_bwd_quant_mxfp8(h1.data_ptr(), dz.data_ptr(), cnt.data_ptr(), cap, F, clamped, 1.702, 7.0,
+                                                None, None, only_col[2].data_ptr(), only_col[3].data_ptr(), st), "col only")
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert torch.equal(only_row[0], want[0]) and torch.equal(only_row[1], want[1]) and not only_row[2].any()
+    assert torch.equal(only_col[2], want[2]) and torch.equal(only_col[3], want[3]) and not only_col[0].any()

@@ -626,6 +626,30 @@ def run_micro(args):
         "wgrad": lambda: nat.lib.dm_gemm_wgrad(op(h1), op(x), dw13.data_ptr(), 0, 1, off.data_ptr(), e, rows, 2 * F, D,
                                                0, status.data_ptr(), st),
     }
+    if args.micro == "quant-mxfp8":
+        # row + column MXFP8 quantiser on a [16384, 4096] bf16 matrix (134 MB in, 134 MB + scales out)
+        qr, qc_cols = 16384, 4096
+        xq = torch.randn(qr, qc_cols, device=dev, generator=g).bfloat16()
+        q_row = torch.empty(qr, qc_cols, dtype=torch.uint8, device=dev)
+        q_col = torch.empty(qr, qc_cols, dtype=torch.uint8, device=dev)
+        s_row = torch.empty(qr * (qc_cols // 32), dtype=torch.uint8, device=dev)
+        s_col = torch.empty(qc_cols * (qr // 32), dtype=torch.uint8, device=dev)
+        fnq = lambda: nat.lib.dm_quant_mxfp8_rowcol(xq.data_ptr(), None, qr, qc_cols, q_row.data_ptr(), s_row.data_ptr(),  # noqa: E731
+                                                    q_col.data_ptr(), s_col.data_ptr(), st)
+        for _ in range(2):
+            nat.check(fnq(), args.micro)
+        torch.cuda.synchronize()
+        s0, t0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            nat.check(fnq(), args.micro)
+        t0.record()
+        torch.cuda.synchronize()
+        ms = s0.elapsed_time(t0) / args.steps
+        nbytes = qr * qc_cols * (2 + 2 * (1 + 1 / 32))
+        print(json.dumps({"micro": args.micro, "rows": qr, "cols": qc_cols, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6}),
+              flush=True)
+        return
     if args.micro.startswith("bs-"):
         # block-scaled forward GEMM (W13 with the SwiGLU epilogue) on synthetic quantised bytes: timing does not
         # depend on the values, scale bytes are 1.0 in their format
@@ -676,7 +700,7 @@ def main():
                     help="time eager routed_experts calls instead of CUDA-graph replays of the same step")
     ap.add_argument("--cta-pairs", action="store_true",
                     help="run forward / input-gradient GEMMs on the CTA-pair kernel (tcgen05 cta_group::2)")
-    ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8"],
+    ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8", "quant-mxfp8"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
     ap.add_argument("--workload", default="bf16-train", choices=["bf16-train"] + sorted(INFERENCE_WORKLOADS),
                     help="bf16-train is the headline training layer; the others are forward-only inference layers")

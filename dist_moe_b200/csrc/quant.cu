@@ -233,11 +233,11 @@ __global__ void __launch_bounds__(256) mxfp8_slab_kernel(const __nv_bfloat16* __
 // (bf16 -> fp32 is exact).  Two 16-bit lanes are compared per instruction.
 //   column pass: thread t owns columns 2t and 2t+1 (one 32-bit word per row);
 //   row pass   : lane r of a warp owns row r of one 32-column block (four 16-byte reads).
-// The column-quantised bytes go back through shared memory so that global stores are 16 bytes wide.
+// The column pass sweeps the slab twice (maxima, then conversion) instead of holding 32 rows in registers, which
+// lets six CTAs share an SM; it stores two bytes per lane, 64 contiguous bytes per warp and row.
 // ---------------------------------------------------------------------------
 constexpr int kSlabCols = 512;
 constexpr int kSlabRawStride = kSlabCols * 2 + 16;
-constexpr int kSlabOutStride = kSlabCols + 16;
 
 __device__ __forceinline__ float amax_from_bf16_bits(uint32_t bits15) {
   return bits15 > 0x7f80u ? __int_as_float(0x7f800000) : __uint_as_float(bits15 << 16);
@@ -288,44 +288,35 @@ __device__ __forceinline__ void slab_quantise(uint8_t* slab, int64_t rows, int64
   }
   if (q_col == nullptr) return;  // uniform over the CTA
 
-  // column pass: 32 rows of two adjacent columns per thread
-  uint32_t w[32];
-#pragma unroll
-  for (int r = 0; r < 32; ++r) w[r] = *reinterpret_cast<const uint32_t*>(slab + r * kSlabRawStride + t * 4);
+  // column pass: 32 rows of two adjacent columns per thread, in two sweeps over the staged slab (maxima, then
+  // conversion) so that no row values are held in registers; a warp's 2-byte stores cover 64 contiguous bytes.
   uint32_t m = 0;
 #pragma unroll
-  for (int r = 0; r < 32; ++r) m = __vmaxu2(m, w[r] & 0x7fff7fffu);
+  for (int r = 0; r < 32; ++r)
+    m = __vmaxu2(m, *reinterpret_cast<const uint32_t*>(slab + r * kSlabRawStride + t * 4) & 0x7fff7fffu);
   float recip0, recip1;
   const uint8_t byte0 = mxfp8_scale(amax_from_bf16_bits(m & 0xffffu), recip0);
   const uint8_t byte1 = mxfp8_scale(amax_from_bf16_bits(m >> 16), recip1);
   const int c = col0 + 2 * t;
-  if (c < limit) {
-    const int64_t rb = row0 >> 5;
-    if (blocked) {
-      s_col[blocked_offset(c, static_cast<int>(rb), col_atoms)] = byte0;
-      s_col[blocked_offset(c + 1, static_cast<int>(rb), col_atoms)] = byte1;
-    } else {
-      const int64_t per_col = (max_rows + 31) / 32;
-      s_col[static_cast<int64_t>(c) * per_col + rb] = byte0;
-      s_col[static_cast<int64_t>(c + 1) * per_col + rb] = byte1;
-    }
+  if (c >= limit) return;
+  const int64_t rb = row0 >> 5;
+  if (blocked) {
+    s_col[blocked_offset(c, static_cast<int>(rb), col_atoms)] = byte0;
+    s_col[blocked_offset(c + 1, static_cast<int>(rb), col_atoms)] = byte1;
+  } else {
+    const int64_t per_col = (max_rows + 31) / 32;
+    s_col[static_cast<int64_t>(c) * per_col + rb] = byte0;
+    s_col[static_cast<int64_t>(c + 1) * per_col + rb] = byte1;
   }
-  __syncthreads();  // every thread holds what it needs of the raw slab: its storage now takes the quantised bytes
-#pragma unroll
-  for (int r = 0; r < 32; ++r) {
+  const int live = rows - row0 < 32 ? static_cast<int>(rows - row0) : 32;
+  uint8_t* dst = q_col + row0 * C + c;
+#pragma unroll 8
+  for (int r = 0; r < live; ++r) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(slab + r * kSlabRawStride + t * 4);
     const uint32_t pk = __nv_cvt_float2_to_fp8x2(
-        make_float2(__uint_as_float(w[r] << 16) * recip0, __uint_as_float(w[r] & 0xffff0000u) * recip1), __NV_SATFINITE,
+        make_float2(__uint_as_float(w << 16) * recip0, __uint_as_float(w & 0xffff0000u) * recip1), __NV_SATFINITE,
         __NV_E4M3);
-    *reinterpret_cast<uint16_t*>(slab + r * kSlabOutStride + t * 2) = static_cast<uint16_t>(pk);
-  }
-  __syncthreads();
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int i = t + 256 * k;
-    const int r = i >> 5, v = i & 31;
-    if (row0 + r < rows && col0 + v * 16 < limit)
-      *reinterpret_cast<uint4*>(q_col + (row0 + r) * C + col0 + v * 16) =
-          *reinterpret_cast<const uint4*>(slab + r * kSlabOutStride + v * 16);
+    *reinterpret_cast<uint16_t*>(dst + static_cast<int64_t>(r) * C) = static_cast<uint16_t>(pk);
   }
 }
 

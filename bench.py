@@ -465,6 +465,132 @@ INFERENCE_WORKLOADS = {
 }
 
 
+def run_mxfp8_train(args):
+    """MXFP8 E4M3 training layer (forward + backward, prepared weights, in-place weight-gradient accumulation) at
+    the reference's EP=8 MXFP8 configuration: T=8192 tokens/rank, D=4096, F=1536, E=128, K=8, router logits N(0,1)
+    plus a per-expert bias drawn from Zipf(1.1).  Steps are eager calls timed with CUDA events; a second pass
+    brackets every C-ABI call with events for the per-call breakdown."""
+    import torch.distributed as dist
+
+    import dist_moe_b200 as dm
+    from dist_moe_b200 import _native
+
+    Tn, Dn, Fn, En, Kn = args.tokens or 8192, 4096, 1536, args.experts or 128, 8
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    e_local = En // world
+    g = torch.Generator().manual_seed(1000 + rank)
+    x = torch.randn(Tn, Dn, generator=g).bfloat16().to(dev)
+    bias = torch.from_numpy(__import__("numpy").random.default_rng(2027).zipf(1.1, En).clip(max=64).astype("float32")).log()
+    logits = torch.randn(Tn, En, generator=g) + bias
+    top = torch.topk(torch.softmax(logits, -1), Kn)
+    scores = (top.values / top.values.sum(-1, keepdim=True)).float().to(dev)
+    ids = top.indices.to(dev)
+    # rows the busiest rank receives (every expert's rows padded to 128), relative to T*K: the plan's capacity factor
+    per_expert = torch.bincount(top.indices.flatten(), minlength=En).float()
+    if world > 1:
+        t = per_expert.to(dev)
+        dist.all_reduce(t)
+        per_expert = t.cpu()
+    padded = ((per_expert + 127) // 128 * 128).view(world, e_local).sum(1).max().item()
+    factor = min(float(world), max(1.0, 1.02 * padded / float(Tn * Kn)))
+    gw = torch.Generator(device=dev).manual_seed(2027 + rank)
+    w13 = (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16().requires_grad_(True)
+    w13.grad, w2.grad = torch.zeros_like(w13), torch.zeros_like(w2)
+    grad_out = torch.randn(Tn, Dn, generator=g).bfloat16().to(dev)
+    cfg = dm.Config(max_num_local_input_tokens=Tn, hidden_dim=Dn, intermediate_dim=Fn, top_k=Kn, num_experts=En,
+                    max_moe_layers_per_activation_slot=1, block_scaled=dm.BlockScaledConfig(),
+                    device_scratch_capacity_factor=factor)
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    opts = dm.ExecutionOptions(inplace_wgrad_accum=True)
+    p13, p2 = dm.prepare_block_scaled_weight(w13, cfg), dm.prepare_block_scaled_weight(w2, cfg)
+
+    def step():
+        xs, ss = x.detach().requires_grad_(True), scores.detach().requires_grad_(True)
+        dm.routed_experts(xs, ids, ss, p13, p2, ctx, options=opts).backward(grad_out)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    ctx.check_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sync_all()
+    sampler.mark()
+    l0 = _native.LAUNCHES[0]
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        step()
+    s1.record()
+    sync_all()
+    sampler.mark()
+    launches = _native.LAUNCHES[0] - l0
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.check_status()
+    ms = torch.tensor([s0.elapsed_time(s1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    # per-call breakdown of one more step (rank 0)
+    events = []
+    names = [n for n in _native.EXPORTS if n.startswith("dm_") and n not in ("dm_version", "dm_route_workspace_words")]
+    saved = {n: getattr(_native.lib, n) for n in names}
+
+    def bracket(fn, n):
+        def call(*a):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            r = fn(*a)
+            a1.record()
+            events.append((n, a0, a1))
+            return r
+        return call
+
+    for n in names:
+        setattr(_native.lib, n, bracket(saved[n], n))
+    step()
+    torch.cuda.synchronize()
+    for n in names:
+        setattr(_native.lib, n, saved[n])
+    breakdown = [[n[3:], round(a0.elapsed_time(a1) * 1e3, 1)] for n, a0, a1 in events]
+    rows = int(padded) if world == 1 else None
+    if rank == 0:
+        print(json.dumps({
+            "metric": "MoE layer tokens/s (MXFP8 E4M3 training layer, fwd+bwd), whole job", "value": world * Tn / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e8m0 block scales",
+            "data": "synthetic (seeded N(0,1) tokens, N(0,0.02) weights, softmax top-8 on N(0,1) logits + log Zipf(1.1) bias)",
+            "config": {"workload": f"mxfp8-train: T={Tn} tokens/rank, D={Dn}, F={Fn}, E={En} (E_local={e_local}), K={Kn}, "
+                                   f"plain SwiGLU, fwd+bwd, prepared weights, in-place wgrad accumulation",
+                       "l2": "no flush: weights and routed activations exceed the 126 MB L2",
+                       "capacity_factor": factor},
+            "gpu_launches": launches, "step_mode": "eager", "clocks": clocks, "padded_rows_busiest_rank": rows,
+            "flops_per_step_rank0_balanced": 18.0 * Tn * Kn * Dn * Fn,
+            "tflops_balanced": 18.0 * Tn * Kn * Dn * Fn / (ms * 1e-3) / 1e12, "us_per_call": breakdown}), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_inference(args):
     """Forward-only inference workloads with prepared block-scaled weights, timed as CUDA-graph replays.
 
@@ -702,7 +828,7 @@ def main():
                     help="run forward / input-gradient GEMMs on the CTA-pair kernel (tcgen05 cta_group::2)")
     ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8", "quant-mxfp8"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
-    ap.add_argument("--workload", default="bf16-train", choices=["bf16-train"] + sorted(INFERENCE_WORKLOADS),
+    ap.add_argument("--workload", default="bf16-train", choices=["bf16-train", "mxfp8-train"] + sorted(INFERENCE_WORKLOADS),
                     help="bf16-train is the headline training layer; the others are forward-only inference layers")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank of an inference workload (sweeps)")
     ap.add_argument("--experts", type=int, default=0, help="total experts of an inference workload (default: the config's)")
@@ -715,6 +841,8 @@ def main():
         run_micro(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload == "mxfp8-train":
+        run_mxfp8_train(args)
     elif args.workload != "bf16-train":
         run_inference(args)
     else:

@@ -20,6 +20,15 @@ def _nat():
     return _native
 
 
+@pytest.fixture(autouse=True, params=[1, 0], ids=["tiles128x256", "tiles128x128"])
+def tile_choice(request):
+    """Every test runs on the 128x256 kernel (the default) and on the 128x128 comparison kernel."""
+    nat = _nat()
+    previous = nat.lib.dm_set_blockscaled_wide(request.param)
+    yield request.param
+    nat.lib.dm_set_blockscaled_wide(previous)
+
+
 def _close(got, ref, what):
     got, ref = got.float(), ref.float()
     scale = ref.pow(2).mean().sqrt().item() + 1e-9

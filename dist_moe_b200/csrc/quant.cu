@@ -485,6 +485,59 @@ __global__ void __launch_bounds__(128) nvfp4_token_kernel(const uint4* __restric
   }
 }
 
+// Rows of up to 2048 elements: one warp per row, the row stays in registers between the row-maximum pass and
+// the quantising pass (no second read, no block-wide barriers).  Same arithmetic as the kernel above.
+template <int kVpl>
+__global__ void __launch_bounds__(256) nvfp4_token_warp_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
+                                                               int64_t max_rows, int vec_per_row, uint8_t* q,
+                                                               int64_t q_stride, uint8_t* s, int64_t s_stride,
+                                                               uint8_t* inv, int64_t inv_stride, int blocked_atoms) {
+  int64_t rows = num_rows ? *num_rows : max_rows;
+  if (rows > max_rows) rows = max_rows;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const uint4* xr = x + r * vec_per_row;
+    uint4 raw[kVpl];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVpl; ++j) {
+      const int v = j * 32 + lane;
+      raw[j] = v < vec_per_row ? xr[v] : make_uint4(0, 0, 0, 0);
+      float f[8];
+      unpack8f(raw[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const float row_scale = 2688.0f * __frcp_rn(fmaxf(amax, 1e-8f));
+    if (lane == 0 && inv != nullptr) *reinterpret_cast<float*>(inv + r * inv_stride) = __frcp_rn(row_scale);
+#pragma unroll
+    for (int j = 0; j < kVpl; ++j) {
+      const int v = j * 32 + lane;
+      float f[8];
+      unpack8f(raw[j], f);
+      float bmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bmax = amax_nonfinite(bmax, f[i]);
+      const float other = __shfl_xor_sync(0xffffffffu, bmax, 1);
+      bmax = (other != other) ? other : fmaxf(bmax, other);
+      float mult;
+      const uint8_t byte = nvfp4_block_scale(bmax, row_scale, mult);
+      if (v < vec_per_row) {
+        *reinterpret_cast<uint32_t*>(q + r * q_stride + v * 4) = e2m1x8(f, mult);
+        if ((v & 1) == 0) {
+          if (blocked_atoms > 0)
+            s[blocked_offset(r, v >> 1, blocked_atoms)] = byte;
+          else
+            s[r * s_stride + (v >> 1)] = byte;
+        }
+      }
+    }
+  }
+}
+
 // Weights: per-expert global scale given; rows of K elements; scales natural or blocked per expert.
 __global__ void __launch_bounds__(256) nvfp4_weight_kernel(const uint4* __restrict__ w, const float* __restrict__ gs,
                                                            int64_t rows_per_expert, int64_t total_rows,
@@ -713,6 +766,26 @@ extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int6
   if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 16) != 0 || (q_row_stride % 4) != 0) return kRcBadArg;
   if (scale_inv && (inv_row_stride % 4) != 0) return kRcBadArg;
   if (max_rows == 0) return kRcOk;
+  const int vec = static_cast<int>(C / 8);
+  if (vec <= 256) {
+    const int atoms = scales_blocked ? static_cast<int>((C / 16 + 3) / 4) : 0;
+    const int blocks = blocks_for(max_rows, 8, 148 * 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define DM_TOKEN_WARP(VPL)                                                                                            \
+    nvfp4_token_warp_kernel<VPL><<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), num_rows, max_rows, vec,         \
+                                                         static_cast<uint8_t*>(q), q_row_stride,                        \
+                                                         static_cast<uint8_t*>(scales), scale_row_stride,               \
+                                                         static_cast<uint8_t*>(scale_inv), inv_row_stride, atoms)
+    if (vec <= 64) {
+      DM_TOKEN_WARP(2);
+    } else if (vec <= 128) {
+      DM_TOKEN_WARP(4);
+    } else {
+      DM_TOKEN_WARP(8);
+    }
+#undef DM_TOKEN_WARP
+    return static_cast<int>(cudaGetLastError());
+  }
   nvfp4_token_kernel<<<blocks_for(max_rows, 1, 148 * 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C / 8), static_cast<uint8_t*>(q),
       q_row_stride, static_cast<uint8_t*>(scales), scale_row_stride, static_cast<uint8_t*>(scale_inv),

@@ -227,6 +227,14 @@ def _workspace(state):
     return ws
 
 
+def _wide_tiles_selected() -> bool:
+    """Whether the block-scaled GEMMs run on 128x256 tiles (the library's switch has no read-only form)."""
+    previous = nat.lib.dm_set_blockscaled_wide(1)
+    if not previous:
+        nat.lib.dm_set_blockscaled_wide(0)
+    return bool(previous)
+
+
 def _view(buf: torch.Tensor, offset: int) -> nat.Operand:
     return nat.Operand(buf.data_ptr() + offset, buf.numel() - offset, None)
 
@@ -309,7 +317,18 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     # ---- W13 (+SwiGLU) ---------------------------------------------------------------------------
     fused = bool(p13._interleaved_fc13)
     row_inv = _view(buf, lay.x_inv) if lay.fp4 else none
-    if fused:
+    h2_quantised = False
+    if fused and not lay.fp4 and _wide_tiles_selected():
+        # MXFP8: the SwiGLU epilogue writes h2 already row-quantised, the operand of the W2 GEMM
+        h2_dense = lay.dense
+        h2_quantised = True
+        nat.check(nat.lib.dm_gemm_blockscaled_swiglu_mxfp8(_view(buf, lay.x_q), _view(buf, lay.x_sf),
+                                                           p13.fprop_data.data_ptr(), p13.fprop_scale.data_ptr(),
+                                                           _view(buf, lay.h_q), _view(buf, lay.h_sf),
+                                                           offsets.data_ptr(), el, max_rows, 2 * F, D, clamped, alpha,
+                                                           limit, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled_swiglu_mxfp8")
+    elif fused:
         h2_dense = lay.dense
         nat.check(nat.lib.dm_gemm_blockscaled(f, _view(buf, lay.x_q), _view(buf, lay.x_sf), p13.fprop_data.data_ptr(),
                                               p13.fprop_scale.data_ptr(), none, _view(buf, h2_dense), None, row_inv,
@@ -328,7 +347,9 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
                   "dm_swiglu_fwd")
     # ---- quantise h2 rows --------------------------------------------------------------------------
     h2_ptr = buf.data_ptr() + h2_dense
-    if lay.fp4:
+    if h2_quantised:
+        pass
+    elif lay.fp4:
         nat.check(nat.lib.dm_quant_nvfp4_token(h2_ptr, recv.data_ptr(), max_rows, F, buf.data_ptr() + lay.h_q, hq,
                                                buf.data_ptr() + lay.h_sf, 0, 1, buf.data_ptr() + lay.h_inv, 4, st),
                   "dm_quant_nvfp4_token(h2)")

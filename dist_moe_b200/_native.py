@@ -83,6 +83,11 @@ _SIGNATURES = {
     "dm_set_gemm_pairs": (c_int, [c_int]),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
     "dm_set_route_decode_kernel": (c_int, [c_int]),
+    "dm_gemm_blockscaled_swiglu_mxfp8": (
+        c_int,
+        [Operand, Operand, _P, _P, Operand, Operand, _P, c_int, c_int64, c_int64, c_int64, c_int, c_float, c_float, _P,
+         c_int, _P, _P],
+    ),
     "dm_gemm_blockscaled_dgrad": (
         c_int,
         [Operand, Operand, _P, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P],

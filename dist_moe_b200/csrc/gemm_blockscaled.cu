@@ -17,6 +17,7 @@
 // scales, optionally scattered to per-row destinations), or SwiGLU over a W13 whose rows were
 // interleaved in groups of 8 gate / 8 up rows at preparation time, producing bf16 h2 (and h1).
 #include "gemm_common.cuh"
+#include "quant_common.cuh"
 
 namespace dm {
 
@@ -56,6 +57,12 @@ struct BsParams {
   int mode;       // 0 fprop (A, W K-major), 1 dgrad (W N-major), 2 wgrad (both operands MN-major, K = expert rows)
   int Kw;         // dgrad: rows of one expert's W (the contraction extent); wgrad: dW columns
   int out_fp32, accumulate;
+  // SwiGLU epilogue of the 128 x 256 kernel writing h2 as MXFP8 rows (E4M3 bytes + blocked E8M0 scales) instead of bf16
+  uint8_t* hq_base;
+  const int64_t* hq_off;
+  uint8_t* hsf_base;
+  const int64_t* hsf_off;
+  int h_atoms;
   const int64_t* b_off;
   const int64_t* sfb_off;
   ActParams act;
@@ -848,6 +855,32 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
             uv[g] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
           }
           const int f0 = t.n_blk * (kWdBN / 2) + c0 / 2;  // first of the 32 features of this block
+          if (p.hq_base != nullptr) {
+            // The lane holds one whole 1 x 32 block of its h2 row (already rounded to bf16): quantise it here, as
+            // the row quantiser would from the stored bf16 values, and store 32 E4M3 bytes and the block's scale.
+            if (row_ok && f0 + 32 <= F) {
+              const uint32_t zw[16] = {zv[0].x, zv[0].y, zv[0].z, zv[0].w, zv[1].x, zv[1].y, zv[1].z, zv[1].w,
+                                       zv[2].x, zv[2].y, zv[2].z, zv[2].w, zv[3].x, zv[3].y, zv[3].z, zv[3].w};
+              uint32_t m = 0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) m = __vmaxu2(m, zw[j] & 0x7fff7fffu);
+              const uint32_t top = (m >> 16) > (m & 0xffffu) ? (m >> 16) : (m & 0xffffu);
+              float recip;
+              const uint8_t byte = mxfp8_scale(amax_from_bf16_bits(top), recip);
+              uint32_t o[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                o[j] = e4m3x4(__uint_as_float(zw[2 * j] << 16) * recip, __uint_as_float(zw[2 * j] & 0xffff0000u) * recip,
+                              __uint_as_float(zw[2 * j + 1] << 16) * recip,
+                              __uint_as_float(zw[2 * j + 1] & 0xffff0000u) * recip);
+              uint4* dst = reinterpret_cast<uint4*>(p.hq_base + (p.hq_off ? *p.hq_off : 0) +
+                                                    static_cast<int64_t>(row) * F + f0);
+              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+              (p.hsf_base + (p.hsf_off ? *p.hsf_off : 0))[blocked_offset(row, f0 >> 5, p.h_atoms)] = byte;
+            }
+            continue;
+          }
 #pragma unroll
           for (int which = 0; which < 3; ++which) {
             if (which > 0 && p.c_base == nullptr) break;
@@ -1016,6 +1049,49 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
     rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kWdBN);
     if (rc != kRcOk) return rc;
   }
+  return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
+}
+
+// MXFP8 forward W13 GEMM whose SwiGLU epilogue writes h2 already row-quantised (the operand of the W2 GEMM).
+extern "C" int dm_gemm_blockscaled_swiglu_mxfp8(dm_operand a, dm_operand sfa, const void* w, const void* sfb,
+                                                dm_operand h2_q, dm_operand h2_sf, const int32_t* expert_offsets,
+                                                int e_local, int64_t max_rows, int64_t N, int64_t Kd, int clamped,
+                                                float alpha, float limit, const int* cond, int num_sms, int* status,
+                                                void* stream) {
+  if (!a.base || !sfa.base || !w || !sfb || !h2_q.base || !h2_sf.base || !expert_offsets || e_local <= 0 ||
+      max_rows < 0 || N <= 0 || Kd <= 0)
+    return kRcBadArg;
+  if (e_local > kBsMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
+  if ((Kd % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0 || ((N / 2) % 32) != 0) return kRcUnsupportedShape;
+  if (!g_bs_wide) return kRcUnsupportedShape;  // only the 128 x 256 kernel has this epilogue
+  if (max_rows == 0) return kRcOk;
+  BsParams p{};
+  int rc = encode_arena_u8(&p.tm_a, a, Kd, max_rows + 256, kBsBM);
+  if (rc != kRcOk) return rc;
+  rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, Kd, kWdBN);
+  if (rc != kRcOk) return rc;
+  p.a_col_atoms = static_cast<int>((Kd / 32 + 3) / 4);
+  p.b_col_atoms = p.a_col_atoms;
+  p.sfb_group_bytes = (N + 127) / 128 * 128 * static_cast<int64_t>(p.b_col_atoms) * 4;
+  p.a_off = a.offset;
+  p.sfa_off = sfa.offset;
+  p.sfa_base = static_cast<const uint8_t*>(sfa.base);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.hq_base = static_cast<uint8_t*>(h2_q.base);
+  p.hq_off = h2_q.offset;
+  p.hsf_base = static_cast<uint8_t*>(h2_sf.base);
+  p.hsf_off = h2_sf.offset;
+  p.h_atoms = static_cast<int>((N / 2 / 32 + 3) / 4);
+  p.h2_base = p.hq_base;  // the SwiGLU branch keys on a non-null h2
+  p.expert_offsets = expert_offsets;
+  p.cond = cond;
+  p.status = status;
+  p.e_local = e_local;
+  p.max_rows = static_cast<int>(max_rows);
+  p.N = static_cast<int>(N);
+  p.k_iters = static_cast<int>(Kd / 128);
+  p.swiglu = 1;
+  p.act = ActParams{clamped, alpha, limit};
   return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
 }
 

@@ -280,6 +280,16 @@ int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w,
                         int64_t N, int64_t Kd, int swiglu_interleaved, int clamped, float alpha, float limit,
                         const int* cond, int num_sms, int* status, void* stream);
 
+/* dm_gemm_blockscaled(MXFP8, swiglu_interleaved) whose epilogue quantises h2 on the way out: h2_q receives the
+ * E4M3 bytes ([rows, N/2]) and h2_sf the blocked E8M0 scales of 1 x 32 blocks, bit-identical to dm_quant_mxfp8_row
+ * applied to the bf16 h2 the plain call writes; h2 itself is not written (the reference's
+ * `..._fprop_swiglu_fwd_combine` producers quantise h2 in the same place, dist_moe/_blockscaled_ops.py:172-420).
+ * 128 x 256 tiles only (dm_set_blockscaled_wide(1), the default). */
+int dm_gemm_blockscaled_swiglu_mxfp8(dm_operand a, dm_operand sfa, const void* w, const void* sfb, dm_operand h2_q,
+                                     dm_operand h2_sf, const int32_t* expert_offsets, int e_local, int64_t max_rows,
+                                     int64_t N, int64_t Kd, int clamped, float alpha, float limit, const int* cond,
+                                     int num_sms, int* status, void* stream);
+
 /* Kernel selection for dm_gemm_blockscaled: non-zero (default) runs 128 x 256 output tiles (one 256-column
  * accumulator in TMEM, 3 or 4 stages of 48 KiB operands + scale atoms), zero runs the 128 x 128 tiles the
  * backward GEMMs use.  Returns the previous setting.  Results agree to fp32 accumulation order.  No

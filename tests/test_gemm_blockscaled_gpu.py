@@ -283,3 +283,43 @@ def test_blockscaled_wgrad(counts, M, N, fp32, acc):
             assert bool((got == 0).all())
             continue
         _close(got if fp32 else got.bfloat16(), ref, f"wgrad expert {e}")
+
+
+def test_swiglu_epilogue_that_quantises_h2_equals_gemm_then_row_quantiser(tile_choice):
+    """dm_gemm_blockscaled_swiglu_mxfp8 writes the E4M3 bytes and scales that dm_quant_mxfp8_row produces from the
+    bf16 h2 of the plain SwiGLU call (128x256 tiles only)."""
+    if not tile_choice:
+        pytest.skip("the quantising epilogue exists on the 128x256 kernel only")
+    nat = _nat()
+    torch.manual_seed(11)
+    counts, K, F = [128, 384, 0, 256], 512, 320
+    E, N = len(counts), 2 * F
+    off = [0]
+    for c in counts:
+        off.append(off[-1] + c)
+    R = off[-1]
+    offs = torch.tensor(off, dtype=torch.int32, device=DEV)
+    x = torch.randn(R, K, device=DEV).bfloat16()
+    w = (torch.randn(E, N, K, device=DEV) * 0.05).bfloat16()
+    qa, sa, _, _ = _quant_act(nat, x, 0)
+    qw, sw, _, _ = _quant_w(nat, w, 0)
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    op = lambda t: nat.Operand(t.data_ptr(), t.numel() * t.element_size(), None)  # noqa: E731
+    none = nat.Operand(None, 0, None)
+    st = nat.stream_ptr()
+    h2 = torch.zeros(R, F, device=DEV, dtype=torch.bfloat16)
+    nat.check(nat.lib.dm_gemm_blockscaled(0, op(qa), op(sa), qw.data_ptr(), sw.data_ptr(), none, op(h2), None, none, None,
+                                          offs.data_ptr(), E, R, N, K, 1, 1, 1.702, 7.0, None, 0, status.data_ptr(), st),
+              "gemm+swiglu")
+    atoms = (F // 32 + 3) // 4
+    want_q = torch.zeros(R, F, dtype=torch.uint8, device=DEV)
+    want_s = torch.zeros(R * atoms * 4, dtype=torch.uint8, device=DEV)
+    nat.check(nat.lib.dm_quant_mxfp8_row(h2.data_ptr(), None, R, F, want_q.data_ptr(), 0, want_s.data_ptr(), 0, 1, st), "row")
+    got_q, got_s = torch.zeros_like(want_q), torch.zeros_like(want_s)
+    nat.check(nat.lib.dm_gemm_blockscaled_swiglu_mxfp8(op(qa), op(sa), qw.data_ptr(), sw.data_ptr(), op(got_q), op(got_s),
+                                                       offs.data_ptr(), E, R, N, K, 1, 1.702, 7.0, None, 0,
+                                                       status.data_ptr(), st), "gemm+swiglu+quant")
+    torch.cuda.synchronize()
+    assert status[0].item() == 0, status.tolist()
+    assert torch.equal(got_q, want_q)
+    assert torch.equal(got_s, want_s)

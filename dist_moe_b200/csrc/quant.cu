@@ -564,8 +564,19 @@ __global__ void __launch_bounds__(256) gather_packed_kernel(const int64_t* __res
   for (int64_t r = blockIdx.x * static_cast<int64_t>(wpb) + (threadIdx.x >> 5); r < rows;
        r += static_cast<int64_t>(gridDim.x) * wpb) {
     const uint8_t* src = reinterpret_cast<const uint8_t*>(ptrs[r]);
-    for (int v = lane; v < q_vecs; v += 32)
-      q[r * q_vecs + v] = src ? __ldcg(reinterpret_cast<const uint4*>(src) + v) : make_uint4(0, 0, 0, 0);
+    for (int v0 = lane; v0 < q_vecs; v0 += 128) {  // four 16-byte loads in flight per lane
+      uint4 t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int v = v0 + 32 * j;
+        t[j] = (src && v < q_vecs) ? __ldcg(reinterpret_cast<const uint4*>(src) + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int v = v0 + 32 * j;
+        if (v < q_vecs) q[r * q_vecs + v] = t[j];
+      }
+    }
     const uint8_t* ssrc = src ? src + static_cast<int64_t>(q_vecs) * 16 : nullptr;
     for (int c4 = lane; c4 < atoms; c4 += 32) {
       uint32_t w = 0;

@@ -350,9 +350,10 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     if h2_quantised:
         pass
     elif lay.fp4:
-        nat.check(nat.lib.dm_quant_nvfp4_token(h2_ptr, recv.data_ptr(), max_rows, F, buf.data_ptr() + lay.h_q, hq,
-                                               buf.data_ptr() + lay.h_sf, 0, 1, buf.data_ptr() + lay.h_inv, 4, st),
-                  "dm_quant_nvfp4_token(h2)")
+        # padding rows of the 128-row-padded expert groups (null scatter pointer) are skipped
+        nat.check(nat.lib.dm_quant_nvfp4_token_live(sct.data_ptr(), h2_ptr, recv.data_ptr(), max_rows, F,
+                                                    buf.data_ptr() + lay.h_q, hq, buf.data_ptr() + lay.h_sf, 0, 1,
+                                                    buf.data_ptr() + lay.h_inv, 4, st), "dm_quant_nvfp4_token_live(h2)")
     else:
         nat.check(nat.lib.dm_quant_mxfp8_row(h2_ptr, recv.data_ptr(), max_rows, F, buf.data_ptr() + lay.h_q, 0,
                                              buf.data_ptr() + lay.h_sf, 0, 1, st), "dm_quant_mxfp8_row(h2)")

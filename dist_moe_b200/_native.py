@@ -112,6 +112,7 @@ _SIGNATURES = {
     "dm_swiglu_bwd_quant_mxfp8": (c_int, [_P, _P, _P, c_int64, c_int64, c_int, c_float, c_float, _P, _P, _P, _P, _P]),
     "dm_quant_mxfp8_tile32": (c_int, [_P, c_int64, c_int64, c_int64, _P, _P, _P, c_int, _P]),
     "dm_quant_nvfp4_token": (c_int, [_P, _P, c_int64, c_int64, _P, c_int64, _P, c_int64, c_int, _P, c_int64, _P]),
+    "dm_quant_nvfp4_token_live": (c_int, [_P, _P, _P, c_int64, c_int64, _P, c_int64, _P, c_int64, c_int, _P, c_int64, _P]),
     "dm_gather_packed_rows": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int, Operand, Operand, Operand, _P, _P]),
     "dm_quant_nvfp4_weight": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, c_int, _P]),
     "dm_sf_swizzle": (c_int, [_P, _P, c_int64, c_int64, _P]),

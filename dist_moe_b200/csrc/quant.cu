@@ -393,11 +393,13 @@ __device__ __forceinline__ uint32_t e2m1x8(const float (&f)[8], float m) {
 __global__ void __launch_bounds__(128) nvfp4_token_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
                                                           int64_t max_rows, int vec_per_row, uint8_t* q,
                                                           int64_t q_stride, uint8_t* s, int64_t s_stride,
-                                                          uint8_t* inv, int64_t inv_stride, int blocked_atoms) {
+                                                          uint8_t* inv, int64_t inv_stride, int blocked_atoms,
+                                                          const int64_t* __restrict__ live) {
   __shared__ float red[4];
   int64_t rows = num_rows ? *num_rows : max_rows;
   if (rows > max_rows) rows = max_rows;
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (live != nullptr && live[r] == 0) continue;  // a padding row: nothing reads its quantised form
     const uint4* xr = x + r * vec_per_row;
     float amax = 0.f;
     for (int v = threadIdx.x; v < vec_per_row; v += 128) {
@@ -446,12 +448,14 @@ template <int kVpl>
 __global__ void __launch_bounds__(256) nvfp4_token_warp_kernel(const uint4* __restrict__ x, const int32_t* num_rows,
                                                                int64_t max_rows, int vec_per_row, uint8_t* q,
                                                                int64_t q_stride, uint8_t* s, int64_t s_stride,
-                                                               uint8_t* inv, int64_t inv_stride, int blocked_atoms) {
+                                                               uint8_t* inv, int64_t inv_stride, int blocked_atoms,
+                                                               const int64_t* __restrict__ live) {
   int64_t rows = num_rows ? *num_rows : max_rows;
   if (rows > max_rows) rows = max_rows;
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    if (live != nullptr && live[r] == 0) continue;  // a padding row: nothing reads its quantised form
     const uint4* xr = x + r * vec_per_row;
     uint4 raw[kVpl];
     float amax = 0.f;
@@ -726,7 +730,7 @@ extern "C" int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, 
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+static int nvfp4_token_impl(const int64_t* live, const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
                                     int64_t q_row_stride, void* scales, int64_t scale_row_stride, int scales_blocked,
                                     void* scale_inv, int64_t inv_row_stride, void* stream) {
   if (!x || !q || !scales || max_rows < 0 || C <= 0 || (C % 16) != 0 || (q_row_stride % 4) != 0) return kRcBadArg;
@@ -741,7 +745,7 @@ extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int6
     nvfp4_token_warp_kernel<VPL><<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), num_rows, max_rows, vec,         \
                                                          static_cast<uint8_t*>(q), q_row_stride,                        \
                                                          static_cast<uint8_t*>(scales), scale_row_stride,               \
-                                                         static_cast<uint8_t*>(scale_inv), inv_row_stride, atoms)
+                                                         static_cast<uint8_t*>(scale_inv), inv_row_stride, atoms, live)
     if (vec <= 64) {
       DM_TOKEN_WARP(2);
     } else if (vec <= 128) {
@@ -755,8 +759,24 @@ extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int6
   nvfp4_token_kernel<<<blocks_for(max_rows, 1, 148 * 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C / 8), static_cast<uint8_t*>(q),
       q_row_stride, static_cast<uint8_t*>(scales), scale_row_stride, static_cast<uint8_t*>(scale_inv),
-      inv_row_stride, scales_blocked ? static_cast<int>((C / 16 + 3) / 4) : 0);
+      inv_row_stride, scales_blocked ? static_cast<int>((C / 16 + 3) / 4) : 0, live);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
+                                    int64_t q_row_stride, void* scales, int64_t scale_row_stride, int scales_blocked,
+                                    void* scale_inv, int64_t inv_row_stride, void* stream) {
+  return nvfp4_token_impl(nullptr, x, num_rows, max_rows, C, q, q_row_stride, scales, scale_row_stride, scales_blocked,
+                          scale_inv, inv_row_stride, stream);
+}
+
+extern "C" int dm_quant_nvfp4_token_live(const int64_t* row_live, const void* x, const int32_t* num_rows,
+                                         int64_t max_rows, int64_t C, void* q, int64_t q_row_stride, void* scales,
+                                         int64_t scale_row_stride, int scales_blocked, void* scale_inv,
+                                         int64_t inv_row_stride, void* stream) {
+  if (!row_live) return kRcBadArg;
+  return nvfp4_token_impl(row_live, x, num_rows, max_rows, C, q, q_row_stride, scales, scale_row_stride, scales_blocked,
+                          scale_inv, inv_row_stride, stream);
 }
 
 extern "C" int dm_quant_nvfp4_weight(const void* w, const float* global_scale, int64_t experts, int64_t N, int64_t K,

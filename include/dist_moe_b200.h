@@ -393,6 +393,12 @@ int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, 
 int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,
                          int64_t q_row_stride, void* scales, int64_t scale_row_stride, int scales_blocked,
                          void* scale_inv, int64_t inv_row_stride, void* stream);
+/* dm_quant_nvfp4_token restricted to the rows r with row_live[r] != 0 (any per-row table whose padding rows hold 0,
+ * e.g. the scatter pointers of the routing step): padding rows of a 128-row-padded expert group are left as they
+ * are, since nothing consumes their quantised form. */
+int dm_quant_nvfp4_token_live(const int64_t* row_live, const void* x, const int32_t* num_rows, int64_t max_rows,
+                              int64_t C, void* q, int64_t q_row_stride, void* scales, int64_t scale_row_stride,
+                              int scales_blocked, void* scale_inv, int64_t inv_row_stride, void* stream);
 int dm_quant_nvfp4_weight(const void* w, const float* global_scale, int64_t experts, int64_t N, int64_t K, void* q,
                           void* scales, int blocked, void* stream);
 int dm_sf_swizzle(const void* natural, void* blocked_out, int64_t rows, int64_t cols, void* stream);

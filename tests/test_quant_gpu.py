@@ -273,3 +273,30 @@ def test_swiglu_backward_fused_into_the_quantiser_equals_the_staged_form(rows, F
         assert torch.equal(a, b)
     assert torch.equal(only_row[0], want[0]) and torch.equal(only_row[1], want[1]) and not only_row[2].any()
     assert torch.equal(only_col[2], want[2]) and torch.equal(only_col[3], want[3]) and not only_col[0].any()
+
+
+@pytest.mark.parametrize("rows,cols", [(96, 2048), (40, 7168)])
+def test_nvfp4_token_live_rows_only(rows, cols):
+    """dm_quant_nvfp4_token_live quantises the rows whose table entry is non-zero exactly as the plain call does
+    and leaves the others untouched."""
+    nat = _nat()
+    st = nat.stream_ptr()
+    x = _data(rows, cols, rows + 5, specials=False).to(DEV)
+    live = torch.tensor([0 if r % 3 == 1 else 1000 + r for r in range(rows)], dtype=torch.int64, device=DEV)
+
+    def outputs(fill):
+        return (torch.full((rows, cols // 2), fill, dtype=torch.uint8, device=DEV),
+                torch.full((rows, cols // 16), fill, dtype=torch.uint8, device=DEV),
+                torch.full((rows,), float(fill), dtype=torch.float32, device=DEV))
+
+    want, got = outputs(0), outputs(0xAB)
+    nat.check(nat.lib.dm_quant_nvfp4_token(x.data_ptr(), None, rows, cols, want[0].data_ptr(), cols // 2, want[1].data_ptr(),
+                                           cols // 16, 0, want[2].data_ptr(), 4, st), "plain")
+    nat.check(nat.lib.dm_quant_nvfp4_token_live(live.data_ptr(), x.data_ptr(), None, rows, cols, got[0].data_ptr(), cols // 2,
+                                                got[1].data_ptr(), cols // 16, 0, got[2].data_ptr(), 4, st), "live")
+    torch.cuda.synchronize()
+    keep = live != 0
+    for g, w in zip(got, want):
+        assert torch.equal(g[keep], w[keep])
+    assert bool((got[0][~keep] == 0xAB).all()) and bool((got[1][~keep] == 0xAB).all())
+    assert bool((got[2][~keep] == float(0xAB)).all())

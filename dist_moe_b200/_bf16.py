@@ -113,7 +113,7 @@ def _route_and_plan(state, x, ids, scratch_only: bool, validate: bool) -> _Call:
                                state.capacity_rows, size, c.counts.data_ptr(), c.per_rank.data_ptr(),
                                c.offsets.data_ptr(), c.fwd.data_ptr(), nat.ptr(c.bwd), c.sct.data_ptr(),
                                state.route_workspace.data_ptr(), state.route_workspace_words,
-                               state.status.data_ptr(), st), "dm_route")
+                               state.status.data_ptr(), st), nat.route_call_name(ep, T, el))
     c.recv_rows = c.offsets[el:]
     c.need = torch.empty(1, dtype=torch.uint8, device=dev)
     c.cond = torch.empty(1, dtype=torch.int32, device=dev)

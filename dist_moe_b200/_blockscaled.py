@@ -228,11 +228,8 @@ def _workspace(state):
 
 
 def _wide_tiles_selected() -> bool:
-    """Whether the block-scaled GEMMs run on 128x256 tiles (the library's switch has no read-only form)."""
-    previous = nat.lib.dm_set_blockscaled_wide(1)
-    if not previous:
-        nat.lib.dm_set_blockscaled_wide(0)
-    return bool(previous)
+    """Whether the block-scaled GEMMs run on 128x256 tiles (the only ones with the quantising SwiGLU epilogue)."""
+    return bool(nat.lib.dm_blockscaled_wide_enabled())
 
 
 def _view(buf: torch.Tensor, offset: int) -> nat.Operand:
@@ -306,7 +303,7 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
                                state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride, D * 2, 128,
                                state.capacity_rows, size, counts.data_ptr(), per_rank.data_ptr(), offsets.data_ptr(),
                                fwd.data_ptr(), None, sct.data_ptr(), state.route_workspace.data_ptr(),
-                               state.route_workspace_words, status, st), "dm_route")
+                               state.route_workspace_words, status, st), nat.route_call_name(ep, T, el))
     recv = offsets[el:]
     # ---- gather + unpack -----------------------------------------------------------------------
     none = nat.Operand(None, 0, None)
@@ -471,7 +468,7 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
                                state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride, stride, 128,
                                state.capacity_rows, size, counts.data_ptr(), per_rank.data_ptr(), c.offsets.data_ptr(),
                                c.fwd.data_ptr(), c.bwd.data_ptr(), c.sct.data_ptr(), state.route_workspace.data_ptr(),
-                               state.route_workspace_words, status, st), "dm_route")
+                               state.route_workspace_words, status, st), nat.route_call_name(ep, T, el))
     c.recv = c.offsets[el:]
     recv = c.recv.data_ptr()
     ws = _Bump(_train_workspace(state, R))

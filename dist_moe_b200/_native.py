@@ -82,7 +82,9 @@ _SIGNATURES = {
     ),
     "dm_set_gemm_pairs": (c_int, [c_int]),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
+    "dm_blockscaled_wide_enabled": (c_int, []),
     "dm_set_route_decode_kernel": (c_int, [c_int]),
+    "dm_route_decode_kernel_enabled": (c_int, []),
     "dm_gemm_blockscaled_swiglu_mxfp8": (
         c_int,
         [Operand, Operand, _P, _P, Operand, Operand, _P, c_int, c_int64, c_int64, c_int64, c_int, c_float, c_float, _P,
@@ -141,6 +143,12 @@ for _name, (_res, _args) in _SIGNATURES.items():
 # Kernel launches issued through this binding (benchmarks report the count).
 LAUNCHES = [0]
 _LAUNCHES_PER_CALL = {"dm_route": 3, "dm_route_static": 3}
+
+
+def route_call_name(ep: int, tokens: int, e_local: int) -> str:
+    """Name under which a ``dm_route`` call is counted: the decode regime runs one launch instead of three."""
+    single = ep * tokens <= 1024 and e_local <= 512 and lib.dm_route_decode_kernel_enabled()
+    return "dm_route(single launch)" if single else "dm_route"
 
 
 def check(rc: int, what: str) -> None:

@@ -964,6 +964,8 @@ extern "C" int dm_set_blockscaled_wide(int enabled) {
   return previous;
 }
 
+extern "C" int dm_blockscaled_wide_enabled(void) { return g_bs_wide; }
+
 static int bs_prepare_launch();
 
 // Launches the 128 x 256 kernel, or the 128 x 128 one when the wide tiles are switched off.

@@ -432,6 +432,8 @@ extern "C" int dm_set_route_decode_kernel(int enabled) {
   return previous;
 }
 
+extern "C" int dm_route_decode_kernel_enabled(void) { return g_route_decode; }
+
 static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
                         int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
                         int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,

@@ -127,6 +127,7 @@ int dm_route_static(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs,
  * dist_moe/_routing_metadata.py:265-300); zero keeps every call on the three general kernels.  Both produce the
  * same tables bit for bit (rows ordered by local expert, source rank, token).  Returns the previous setting. */
 int dm_set_route_decode_kernel(int enabled);
+int dm_route_decode_kernel_enabled(void); /* the current setting, without changing it */
 
 /* ---------------------------------------------------------------------------
  * Activation-arena planner, BF16
@@ -295,6 +296,7 @@ int dm_gemm_blockscaled_swiglu_mxfp8(dm_operand a, dm_operand sfa, const void* w
  * backward GEMMs use.  Returns the previous setting.  Results agree to fp32 accumulation order.  No
  * counterpart in the reference (tile geometry is chosen by BlockScaledKernelConfig, dist_moe/api.py:233-329). */
 int dm_set_blockscaled_wide(int enabled);
+int dm_blockscaled_wide_enabled(void); /* the current setting, without changing it */
 
 /* MXFP8 training backward GEMMs (dist_moe/_blockscaled_ops.py: `dist_blockscaled_grouped_gemm_dgrad_dispatch`,
  * `..._dgrad_swiglu_bwd_combine`, `blockscaled_grouped_gemm_wgrad`; sequencing dist_moe/_blockscaled.py:2284-2512).

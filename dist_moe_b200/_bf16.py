@@ -297,8 +297,10 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
                                         2 * F, D, state.num_sms, status, st, what="gemm_wgrad(w13)")
         grad_w13 = dst.view(w13_param.shape) if ret else None
     grad_x = None
+    # The closing barrier is unconditional (dist_moe/api.py:2580): peers may still be pulling grad_h3 out of this
+    # rank's combine buffer, and the next call on this context overwrites it.
+    state.barrier(state.dispatch)
     if need_x:
-        state.barrier(state.dispatch)
         grad_x = torch.empty(x_shape, dtype=torch.bfloat16, device=dev)
         nat.check(nat.lib.dm_scale_and_sum(state.dispatch.local().data_ptr(), None, 0, ids.data_ptr(),
                                            int(ids.dtype == torch.int64), grad_x.data_ptr(), T, K, D, None, None,
@@ -327,8 +329,9 @@ class _Bf16Function(torch.autograd.Function):
         w13 = w13_param.detach().reshape(state.e_local, 2 * cfg.intermediate_dim, cfg.hidden_dim)
         w2 = w2_param.detach().reshape(state.e_local, cfg.hidden_dim, cfg.intermediate_dim)
         needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
-        gx, gs, gw13, gw2 = backward_impl(state, ctx.call, ctx.x_shape, ids, scores.detach(), w13, w2, w13_param,
-                                          w2_param, grad_out.contiguous(), ctx.options, needs)
+        with torch.cuda.device(state.device):
+            gx, gs, gw13, gw2 = backward_impl(state, ctx.call, ctx.x_shape, ids, scores.detach(), w13, w2, w13_param,
+                                              w2_param, grad_out.contiguous(), ctx.options, needs)
         return gx, None, gs, gw13, gw2, None, None
 
 

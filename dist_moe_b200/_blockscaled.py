@@ -586,8 +586,9 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
                                                     state.num_sms, status, st), "dm_gemm_blockscaled_wgrad(w13)")
         grad_w13 = dst.view(w13_param.shape) if ret else None
     grad_x = None
+    # unconditional, as in the reference (dist_moe/api.py:2580): peers may still be reading this rank's combine buffer
+    state.barrier(state.dispatch)
     if need_x:
-        state.barrier(state.dispatch)
         grad_x = torch.empty(x_shape, dtype=torch.bfloat16, device=dev)
         nat.check(nat.lib.dm_scale_and_sum(state.dispatch.local().data_ptr(), None, 0, ids.data_ptr(),
                                            int(ids.dtype == torch.int64), grad_x.data_ptr(), T, K, D, None, None, None,
@@ -611,6 +612,7 @@ class _Mxfp8Function(torch.autograd.Function):
     def backward(ctx, grad_out):
         ids, scores, w13_param, w2_param = ctx.saved_tensors
         needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
-        gx, gs, gw13, gw2 = _mxfp8_backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param, w2_param,
-                                            grad_out.contiguous(), ctx.options, needs)
+        with torch.cuda.device(ctx.state.device):
+            gx, gs, gw13, gw2 = _mxfp8_backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param,
+                                                w2_param, grad_out.contiguous(), ctx.options, needs)
         return gx, None, gs, gw13, gw2, None, None, None, None

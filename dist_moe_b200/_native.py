@@ -142,7 +142,7 @@ for _name, (_res, _args) in _SIGNATURES.items():
 
 # Kernel launches issued through this binding (benchmarks report the count).
 LAUNCHES = [0]
-_LAUNCHES_PER_CALL = {"dm_route": 3, "dm_route_static": 3}
+_LAUNCHES_PER_CALL = {"dm_route": 3}
 
 
 def route_call_name(ep: int, tokens: int, e_local: int) -> str:

@@ -594,23 +594,27 @@ def routed_experts(x_TD: torch.Tensor, topk_expert_ids_TK: torch.Tensor, topk_sc
     w13_EFD, w2_EDF = _reshape_weights(src13, src2, state.e_local, context.config)
     if options.weights_preprocess_fn is None:
         _validate_inputs(x_TD, topk_expert_ids_TK, topk_scores_TK, w13_EFD, w2_EDF, context, prepared=prepared)
+    if x_TD.device != state.device:
+        raise ValueError(f"x_TD is on {x_TD.device} but the context was created on {state.device}")
     post = options.experts_output_postprocess
     norm_weight = post.weight if isinstance(post, RMSNormPostprocess) else None
     grads = [t for t in (x_TD, topk_scores_TK, w13_EFD, w2_EDF, norm_weight) if t is not None and t.requires_grad]
     if context.config.inference and grads:
         raise RuntimeError("inference contexts do not support autograd")
     save_for_backward = torch.is_grad_enabled() and bool(grads)
-    if context.config.block_scaled is not None:
-        from ._blockscaled import run_block_scaled
+    # every launch below goes to the context's device and to that device's current stream
+    with torch.cuda.device(state.device):
+        if context.config.block_scaled is not None:
+            from ._blockscaled import run_block_scaled
 
-        return run_block_scaled(x_TD, topk_expert_ids_TK, topk_scores_TK, w13_weight, w2_weight, context, options,
-                                save_for_backward=save_for_backward)
-    if prepared:
-        raise ValueError("prepared weights require block-scaled execution")
-    from ._bf16 import run_bf16
+            return run_block_scaled(x_TD, topk_expert_ids_TK, topk_scores_TK, w13_weight, w2_weight, context, options,
+                                    save_for_backward=save_for_backward)
+        if prepared:
+            raise ValueError("prepared weights require block-scaled execution")
+        from ._bf16 import run_bf16
 
-    return run_bf16(x_TD, topk_expert_ids_TK, topk_scores_TK, w13_weight, w2_weight, w13_EFD, w2_EDF, context, options,
-                    save_for_backward=save_for_backward)
+        return run_bf16(x_TD, topk_expert_ids_TK, topk_scores_TK, w13_weight, w2_weight, w13_EFD, w2_EDF, context,
+                        options, save_for_backward=save_for_backward)
 
 
 def prepare_block_scaled_weight(weight: torch.Tensor, config: Config, *, fuse_swiglu: bool = False,

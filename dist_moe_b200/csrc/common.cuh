@@ -426,6 +426,51 @@ __device__ __forceinline__ void swiglu_bwd_f32(float x, float y, float dz, const
   }
 }
 
+// ---- per-device host state ------------------------------------------------------------------------------
+// cudaFuncSetAttribute and the SM count belong to ONE device; a process may drive several, so every cache of
+// such a fact is indexed by the current device.
+constexpr int kMaxDevices = 64;
+
+static inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+struct PerDeviceOnce {
+  bool done[kMaxDevices] = {};
+};
+
+// Runs `setup` (returning a cudaError_t-compatible int) once per device; on an unknown device, every call.
+template <class Fn>
+static inline int once_per_device(PerDeviceOnce& once, Fn&& setup) {
+  const int slot = current_device_slot();
+  if (slot >= 0 && once.done[slot]) return 0;
+  const int rc = setup();
+  if (rc == 0 && slot >= 0) once.done[slot] = true;
+  return rc;
+}
+
+static inline int sm_count() {
+  static int cached[kMaxDevices] = {};
+  const int slot = current_device_slot();
+  if (slot >= 0 && cached[slot] > 0) return cached[slot];
+  int n = 0;
+  if (slot < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, slot) != cudaSuccess || n <= 0) return 148;
+  cached[slot] = n;
+  return n;
+}
+
+// Grid of a persistent one-CTA-per-SM kernel: the caller's wish, never more than the device has SMs.  The fused
+// dispatch launches make CTAs wait on counters that other CTAs publish, so every CTA must be resident.
+static inline int persistent_grid(int num_sms) {
+  const int n = sm_count();
+  return (num_sms > 0 && num_sms < n) ? num_sms : n;
+}
+
+// Grid cap for grid-stride kernels: `per_sm` CTAs per SM of the current device.
+static inline int grid_cap(int per_sm) { return sm_count() * per_sm; }
+
 __host__ __device__ constexpr int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ constexpr int64_t align_up64(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 

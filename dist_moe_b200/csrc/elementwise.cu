@@ -224,7 +224,7 @@ extern "C" int dm_swiglu_fwd(const void* h1_base, const int64_t* h1_offset, void
   if (!h1_base || !h2_base || !num_rows || F <= 0 || (F % 8) != 0 || max_rows < 0) return kRcBadArg;
   if (max_rows == 0) return kRcOk;
   const int vec = static_cast<int>(F / 8);
-  const int blocks = grid_for(max_rows * vec, 256, 148 * 8);
+  const int blocks = grid_for(max_rows * vec, 256, grid_cap(8));
   ActParams act{clamped, alpha, limit};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (clip_stats)
@@ -246,7 +246,7 @@ extern "C" int dm_swiglu_bwd(const void* h1_base, const int64_t* h1_offset, cons
     return kRcBadArg;
   if (max_rows == 0) return kRcOk;
   const int vec = static_cast<int>(F / 8);
-  const int blocks = grid_for(max_rows * vec, 256, 148 * 8);
+  const int blocks = grid_for(max_rows * vec, 256, grid_cap(8));
   ActParams act{clamped, alpha, limit};
   swiglu_bwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(h1_base), h1_offset, static_cast<const uint8_t*>(grad_h2_base), grad_h2_offset,
@@ -259,7 +259,7 @@ extern "C" int dm_scale_and_sum(const void* h3, const void* scores, int scores_a
                                 const int64_t* save_offset, const int* save_cond, int save_expect, void* stream) {
   if (!h3 || !ids || !out || T <= 0 || K <= 0 || D <= 0 || (D % 8) != 0) return kRcBadArg;
   const int vec = static_cast<int>(D / 8);
-  const int blocks = grid_for(T * vec, 256, 148 * 16);
+  const int blocks = grid_for(T * vec, 256, grid_cap(16));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ids_are_int64)
     scale_and_sum_kernel<int64_t><<<blocks, 256, 0, st>>>(static_cast<const uint4*>(h3), scores, scores_are_bf16,
@@ -279,7 +279,7 @@ extern "C" int dm_broadcast_and_scale(const void* grad_out, const void* scores, 
                                       float* grad_scores, int64_t T, int K, int64_t D, void* stream) {
   if (!grad_out || !scores || !ids || !grad_h3 || T <= 0 || K <= 0 || D <= 0 || (D % 8) != 0) return kRcBadArg;
   const int vec = static_cast<int>(D / 8);
-  const int blocks = grid_for(T * K * 32, 256, 148 * 16);
+  const int blocks = grid_for(T * K * 32, 256, grid_cap(16));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ids_are_int64)
     broadcast_and_scale_kernel<int64_t><<<blocks, 256, 0, st>>>(

@@ -626,14 +626,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 
 template <int kMode>
 static int launch(const GemmParams& p, int num_sms, cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kGemmSmemBytes));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
-  const int grid = num_sms > 0 ? num_sms : sm_count();
+  static PerDeviceOnce attr_set;
+  const int rc = once_per_device(attr_set, [] {
+    return static_cast<int>(cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kGemmSmemBytes)));
+  });
+  if (rc != 0) return rc;
+  const int grid = persistent_grid(num_sms);
   grouped_gemm_kernel<kMode><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }

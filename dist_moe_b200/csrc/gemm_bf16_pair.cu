@@ -565,13 +565,12 @@ int dm::dm_pair_launch(const dm_operand& b, const void* w, dm_operand c, dm_oper
                    const int64_t* gather_ptrs, int32_t* gather_flags, const int32_t* expert_offsets, int e_local,
                    int64_t max_rows, int64_t N, int64_t Kd, int fused, int dgrad, int clamped, float alpha, float limit,
                    const int* cond, int num_sms, int* status, cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(paired_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kPSmemBytes));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_set;
+  const int rc_attr = once_per_device(attr_set, [] {
+    return static_cast<int>(cudaFuncSetAttribute(paired_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kPSmemBytes)));
+  });
+  if (rc_attr != 0) return rc_attr;
   PairParams p{};
   int rc;
   if (dgrad)
@@ -614,7 +613,7 @@ int dm::dm_pair_launch(const dm_operand& b, const void* w, dm_operand c, dm_oper
     const cudaError_t e = cudaMemsetAsync(gather_flags, 0, sizeof(int32_t) * static_cast<size_t>((max_rows + 127) / 128 + 1), st);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  int grid = num_sms > 0 ? num_sms : sm_count();
+  int grid = persistent_grid(num_sms);
   grid &= ~1;
   if (grid < 2) return kRcBadArg;
   paired_gemm_kernel<<<grid, kPThreads, kPSmemBytes, st>>>(p);

@@ -970,15 +970,14 @@ static int bs_prepare_launch();
 
 // Launches the 128 x 256 kernel, or the 128 x 128 one when the wide tiles are switched off.
 static int bs_launch(const BsParams& p, int num_sms, cudaStream_t st) {
-  const int grid = num_sms > 0 ? num_sms : sm_count();
+  const int grid = persistent_grid(num_sms);
   if (g_bs_wide) {
-    static bool wide_attr_set = false;
-    if (!wide_attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4));
-      if (e != cudaSuccess) return static_cast<int>(e);
-      wide_attr_set = true;
-    }
+    static PerDeviceOnce wide_attr_set;
+    const int rc = once_per_device(wide_attr_set, [] {
+      return static_cast<int>(cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4)));
+    });
+    if (rc != 0) return rc;
     blockscaled_wide_kernel<<<grid, kWdThreads, p.fp4 ? kWdSmemFp4 : kWdSmemFp8, st>>>(p);
   } else {
     int rc = bs_prepare_launch();
@@ -989,14 +988,11 @@ static int bs_launch(const BsParams& p, int num_sms, cudaStream_t st) {
 }
 
 static int bs_prepare_launch() {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(blockscaled_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kBsSmemBytes));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
-  return kRcOk;
+  static PerDeviceOnce attr_set;
+  return once_per_device(attr_set, [] {
+    return static_cast<int>(cudaFuncSetAttribute(blockscaled_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kBsSmemBytes)));
+  });
 }
 
 extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w, const void* sfb,

@@ -206,14 +206,4 @@ int dm_pair_launch(const dm_operand& b, const void* w, dm_operand c, dm_operand 
                    int64_t max_rows, int64_t N, int64_t Kd, int fused, int dgrad, int clamped, float alpha, float limit,
                    const int* cond, int num_sms, int* status, cudaStream_t st);
 
-static inline int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
-
 }  // namespace dm

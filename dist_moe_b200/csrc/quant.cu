@@ -618,7 +618,7 @@ extern "C" int dm_quant_mxfp8_row(const void* x, const int32_t* num_rows, int64_
   if (max_rows == 0) return kRcOk;
   const int vec = static_cast<int>(C / 8);
   const int atoms = static_cast<int>((C / 32 + 3) / 4);
-  mxfp8_row_kernel<<<blocks_for(max_rows * vec, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  mxfp8_row_kernel<<<blocks_for(max_rows * vec, 256, grid_cap(16)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), num_rows, max_rows, vec, static_cast<uint8_t*>(q), q_row_stride,
       static_cast<uint8_t*>(scales), scale_row_stride, blocked, atoms);
   return static_cast<int>(cudaGetLastError());
@@ -701,13 +701,12 @@ extern "C" int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, co
     return kRcBadArg;
   if (max_rows == 0) return kRcOk;
   constexpr int kSmem = 2 * 32 * kSlabRawStride;
-  static bool attr_set = false;
-  if (!attr_set) {
-    const cudaError_t e =
-        cudaFuncSetAttribute(mxfp8_swiglu_bwd_colrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_set;
+  const int rc_attr = once_per_device(attr_set, [] {
+    return static_cast<int>(
+        cudaFuncSetAttribute(mxfp8_swiglu_bwd_colrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  });
+  if (rc_attr != 0) return rc_attr;
   const dim3 grid(static_cast<unsigned>((F + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
   const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
   const int row_atoms = static_cast<int>((2 * F / 32 + 3) / 4);
@@ -739,7 +738,7 @@ static int nvfp4_token_impl(const int64_t* live, const void* x, const int32_t* n
   const int vec = static_cast<int>(C / 8);
   if (vec <= 256) {
     const int atoms = scales_blocked ? static_cast<int>((C / 16 + 3) / 4) : 0;
-    const int blocks = blocks_for(max_rows, 8, 148 * 8);
+    const int blocks = blocks_for(max_rows, 8, grid_cap(8));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define DM_TOKEN_WARP(VPL)                                                                                            \
     nvfp4_token_warp_kernel<VPL><<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), num_rows, max_rows, vec,         \
@@ -756,7 +755,7 @@ static int nvfp4_token_impl(const int64_t* live, const void* x, const int32_t* n
 #undef DM_TOKEN_WARP
     return static_cast<int>(cudaGetLastError());
   }
-  nvfp4_token_kernel<<<blocks_for(max_rows, 1, 148 * 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  nvfp4_token_kernel<<<blocks_for(max_rows, 1, grid_cap(16)), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), num_rows, max_rows, static_cast<int>(C / 8), static_cast<uint8_t*>(q),
       q_row_stride, static_cast<uint8_t*>(scales), scale_row_stride, static_cast<uint8_t*>(scale_inv),
       inv_row_stride, scales_blocked ? static_cast<int>((C / 16 + 3) / 4) : 0, live);
@@ -783,7 +782,7 @@ extern "C" int dm_quant_nvfp4_weight(const void* w, const float* global_scale, i
                                      void* q, void* scales, int blocked, void* stream) {
   if (!w || !global_scale || !q || !scales || experts <= 0 || N <= 0 || K <= 0 || (K % 16) != 0) return kRcBadArg;
   const int vec = static_cast<int>(K / 8);
-  nvfp4_weight_kernel<<<blocks_for(experts * N * vec, 256, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  nvfp4_weight_kernel<<<blocks_for(experts * N * vec, 256, grid_cap(16)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(w), global_scale, N, experts * N, vec, static_cast<uint32_t*>(q),
       static_cast<uint8_t*>(scales), blocked, static_cast<int>((K / 16 + 3) / 4));
   return static_cast<int>(cudaGetLastError());
@@ -793,7 +792,7 @@ extern "C" int dm_sf_swizzle(const void* natural, void* blocked_out, int64_t row
   if (!natural || !blocked_out || rows <= 0 || cols <= 0) return kRcBadArg;
   const int64_t padded_rows = (rows + 127) / 128 * 128;
   const int atoms = static_cast<int>((cols + 3) / 4);
-  sf_swizzle_kernel<<<blocks_for(padded_rows * atoms * 4, 256, 148 * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  sf_swizzle_kernel<<<blocks_for(padded_rows * atoms * 4, 256, grid_cap(8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(natural), static_cast<uint8_t*>(blocked_out), rows, static_cast<int>(cols),
       padded_rows, atoms);
   return static_cast<int>(cudaGetLastError());
@@ -807,7 +806,7 @@ extern "C" int dm_gather_packed_rows(const int64_t* ptrs, const int32_t* num_row
     return kRcBadArg;
   if (has_inv && !scale_inv.base) return kRcBadArg;
   if (max_rows == 0) return kRcOk;
-  gather_packed_kernel<<<blocks_for(max_rows * 32, 256, 148 * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  gather_packed_kernel<<<blocks_for(max_rows * 32, 256, grid_cap(8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       ptrs, num_rows, max_rows, static_cast<int>(q_bytes / 16), static_cast<int>(scale_cols), has_inv,
       static_cast<uint8_t*>(q.base), q.offset, static_cast<uint8_t*>(scales_blocked.base), scales_blocked.offset,
       static_cast<uint8_t*>(scale_inv.base), scale_inv.offset, cond);

@@ -177,7 +177,7 @@ extern "C" int dm_rmsnorm_combine_fwd(const void* h3, const void* scores, int sc
                                       int save_expect, void* stream) {
   if (!h3 || !scores || !ids || !out || T <= 0 || K <= 0 || K > kNormMaxK || D <= 0 || (D % 8) != 0) return kRcBadArg;
   const int vec = static_cast<int>(D / 8);
-  const int blocks = static_cast<int>(T < 148 * 8 ? T : 148 * 8);
+  const int blocks = static_cast<int>(T < grid_cap(8) ? T : grid_cap(8));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ids_are_int64)
     rmsnorm_combine_fwd_kernel<int64_t><<<blocks, 256, 0, st>>>(
@@ -200,7 +200,7 @@ extern "C" int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, 
     return kRcBadArg;
   const int vec = static_cast<int>(D / 8);
   int64_t blocks = (T * K + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > grid_cap(16)) blocks = grid_cap(16);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ids_are_int64)
     rmsnorm_combine_bwd_kernel<int64_t><<<static_cast<int>(blocks), 256, 0, st>>>(

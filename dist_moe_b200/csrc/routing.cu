@@ -188,6 +188,8 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(RouteParams p) {
     base[p.e_local] = static_cast<int32_t>(acc);
     overflow = (acc > p.capacity_rows || acc > p.ptrs_size) ? 1 : 0;
     if (overflow) set_status(p.status, kCapacityExceeded, static_cast<int>(acc), static_cast<int>(p.capacity_rows));
+    // ranks that disagree on T cannot be routed: the call becomes a no-op (zero rows), like an overflow
+    if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) == kTokenCountMismatch) overflow = 1;
   }
   __syncthreads();
   const bool bad = overflow != 0;
@@ -261,7 +263,9 @@ __global__ void __launch_bounds__(kDecodeThreads) route_decode_kernel(RouteParam
   int32_t* total = hist_s + p.E;                                          // [e_local] real rows
   int32_t* base = total + p.e_local;                                      // [e_local + 1] padded exclusive prefix
   __shared__ int overflow;
+  __shared__ int mismatch;
   const int i = threadIdx.x, warp = i >> 5, lane = i & 31;
+  if (i == 0) mismatch = 0;
   for (int j = i; j < kDecodeWarps * p.e_local; j += kDecodeThreads) mask[j] = 0u;
   for (int j = i; j < p.E; j += kDecodeThreads) hist_s[j] = 0;
   __syncthreads();
@@ -272,7 +276,10 @@ __global__ void __launch_bounds__(kDecodeThreads) route_decode_kernel(RouteParam
   if (live) {
     if (tok == 0) {
       const int peer_t = *reinterpret_cast<const int32_t*>(p.routing_ptrs[s]);
-      if (peer_t != p.T) set_status(p.status, kTokenCountMismatch, s, peer_t, p.T);
+      if (peer_t != p.T) {
+        set_status(p.status, kTokenCountMismatch, s, peer_t, p.T);
+        mismatch = 1;
+      }
     }
     ids = reinterpret_cast<const int16_t*>(p.routing_ptrs[s] + DM_ROUTING_HEADER_BYTES) + static_cast<int64_t>(tok) * p.K;
     for (int k = 0; k < p.K; ++k) {
@@ -302,6 +309,7 @@ __global__ void __launch_bounds__(kDecodeThreads) route_decode_kernel(RouteParam
     base[p.e_local] = static_cast<int32_t>(acc);
     overflow = (acc > p.capacity_rows || acc > p.ptrs_size) ? 1 : 0;
     if (overflow) set_status(p.status, kCapacityExceeded, static_cast<int>(acc), static_cast<int>(p.capacity_rows));
+    if (mismatch) overflow = 1;  // ranks that disagree on T: zero rows, the call becomes a no-op
   }
   __syncthreads();
   const bool bad = overflow != 0;
@@ -390,7 +398,7 @@ extern "C" int dm_publish(const void* x_bf16, const void* ids, int ids_are_int64
   const int64_t n_ids = T * K;
   const int64_t work = n_vec > n_ids ? n_vec : n_ids;
   int blocks = static_cast<int>((work + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > grid_cap(16)) blocks = grid_cap(16);
   if (blocks < 1) blocks = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ids_are_int64)
@@ -480,13 +488,13 @@ static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (g_route_decode && static_cast<int64_t>(ep) * T <= kDecodeThreads && p.e_local <= 512) {
     const size_t smem = sizeof(uint32_t) * (2 * kDecodeWarps * p.e_local + E + 2 * p.e_local + 1);
-    static bool attr_set = false;
-    if (!attr_set) {
-      const cudaError_t ea = cudaFuncSetAttribute(route_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  static_cast<int>(sizeof(uint32_t) * (2 * kDecodeWarps * 512 + kMaxExpertsSmem + 1025)));
-      if (ea != cudaSuccess) return static_cast<int>(ea);
-      attr_set = true;
-    }
+    static PerDeviceOnce attr_set;
+    const int rc_attr = once_per_device(attr_set, [] {
+      return static_cast<int>(
+          cudaFuncSetAttribute(route_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(sizeof(uint32_t) * (2 * kDecodeWarps * 512 + kMaxExpertsSmem + 1025))));
+    });
+    if (rc_attr != 0) return rc_attr;
     route_decode_kernel<<<1, kDecodeThreads, smem, st>>>(p);
     return static_cast<int>(cudaGetLastError());
   }
@@ -521,7 +529,6 @@ extern "C" int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
 namespace dm {
 constexpr int64_t kStaticRouteWords = DM_ROUTE_STATIC_MAX_WORDS;
 static __device__ __align__(256) int32_t g_route_scratch[kStaticRouteWords];
-constexpr int kMaxDevices = 64;
 static int32_t* g_route_scratch_addr[kMaxDevices];  // device address of the array, per device
 }  // namespace dm
 
@@ -559,7 +566,7 @@ extern "C" int dm_gather_rows(const int64_t* ptrs, const int32_t* num_rows, void
   if (max_rows == 0) return kRcOk;
   const int warps = 8;
   int64_t blocks = (max_rows + warps - 1) / warps;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > grid_cap(8)) blocks = grid_cap(8);
   gather_rows_kernel<<<static_cast<int>(blocks), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       ptrs, num_rows, static_cast<uint8_t*>(dst_base), dst_offset, static_cast<int>(row_bytes / 16), max_rows, cond);
   return static_cast<int>(cudaGetLastError());
@@ -571,7 +578,7 @@ extern "C" int dm_cond_copy(const void* src_base, const int64_t* src_offset, voi
   if (bytes == 0) return kRcOk;
   const int64_t n_vec = bytes / 16;
   int64_t blocks = (n_vec + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > grid_cap(16)) blocks = grid_cap(16);
   cond_copy_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src_base), src_offset, static_cast<uint8_t*>(dst_base), dst_offset, n_vec, cond,
       expect);

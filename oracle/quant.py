@@ -17,10 +17,11 @@ Scale storage: natural row-major, or the 128x4 blocked atom
 ``atom*512 + (row%32)*16 + (row//32 % 4)*4 + col%4`` with atoms ordered (row atom, column atom)
 (blockscaled_quantize.py:1012-1043).
 
-Pin status: the MXFP8 parts are pinned against the reference's Triton quantiser run under the Triton
-CPU interpreter (``tests/golden/quant_mxfp8.npz``).  The NVFP4 parts are **parity unpinned**: every
-reference NVFP4 path needs inline PTX that no CPU can execute and the reference ships no golden bytes;
-they are held to round-trip and minimality properties instead (``tests/test_quant_oracle.py``).
+Pin status: every function here is pinned, byte for byte with nothing masked out, against outputs of the
+reference's own quantisers executed on a B200 (``tests/golden/*_gpu.npz``, produced by
+``tests/golden/gen_golden_gpu.py``): the Triton quantiser for MXFP8 rows / columns / 32x32 tiles and NVFP4 rows
+and weights, the CuTe-DSL quantisers for the same MXFP8 modes and for per-token NVFP4, and the two
+weight-preparation operators (``tests/test_quant_oracle.py``).
 """
 
 from __future__ import annotations

@@ -11,6 +11,9 @@ What runs, unmodified, from the reference:
   kernels (``dist_moe/_activation_buffer_planner_kernel.py``) under Triton's CPU
   interpreter (``TRITON_INTERPRET=1``) -> ``routing_*.npz``, ``planner_bf16.json``.
 
+Quantised bytes and floating-point outputs come from the reference's GPU kernels run on a B200 instead:
+see ``gen_golden_gpu.py`` in this directory.
+
 Three shims make the interpreter accept those kernels; none changes arithmetic:
 ``range`` inside the kernel module yields interpreter scalars (the kernels call
 ``.to(...)`` on loop indices), ``device_trap_if`` (inline PTX ``trap``) becomes a
@@ -300,56 +303,13 @@ def gen_planner(ref):
     print("planner_bf16.json:", len(out), "scenarios")
 
 
-def gen_quant(ref):
-    """MXFP8 E4M3 row quantisation through the reference's Triton quantiser kernel
-    (``_triton_quantize_blockscaled_row1d_tile``; its pre-Blackwell pure-Triton scale path is the one the
-    interpreter executes), natural and cuBLAS-blocked scale layouts."""
-    import numpy as np
-    import torch
-
-    from dist_moe.kernels.triton_quantization import blockscaled_quantize as Q
-
-    def run(x, blocked):
-        rows, cols = x.shape
-        sc = cols // 32
-        q = torch.zeros(rows, cols, dtype=torch.uint8)
-        n_col_atoms = (sc + 3) // 4
-        if blocked:
-            s = torch.full(((rows + 127) // 128 * 128 * n_col_atoms * 4,), 0xEE, dtype=torch.uint8)
-        else:
-            s = torch.full((rows, sc), 0xEE, dtype=torch.uint8)
-        Q._triton_quantize_blockscaled_row1d_tile[((rows + 3) // 4, (sc + 3) // 4)](
-            x, None, 0, 0, cols, 1, None, 0, 0, PRODUCER_ID=0, q_ptr=q.view(torch.float8_e4m3fn), scale_ptr=s,
-            SCALE_FACTOR_LAYOUT=1 if blocked else 0, FORMAT_ID=0, USE_HALF_RANGE_SCALE=False, FAST_MATH=False,
-            CLAMPED=False, ALPHA=1.702, LIMIT=7.0, n_rows=rows, N_COLS=cols, Q_COLS=cols, SCALE_COLS=sc,
-            rows_per_group=rows, N_COL_BLOCKS=n_col_atoms, group_output_elems=0, HAS_GROUPS=False,
-            USE_64BIT_OFFSETS=False, USE_64BIT_COL_OFFSETS=False, HAS_GLOBAL_SCALE=False, GLOBAL_SCALE_RANK=1,
-            GLOBAL_SCALE_ROWS_PER_GROUP=1, ROW_TILE=4, SCALE_COL_TILE=4, BLOCK_SIZE=32)
-        return q.numpy(), s.numpy()
-
-    g = torch.Generator().manual_seed(2027)
-    a = (torch.randn(37, 256, generator=g) * torch.logspace(-6, 4, 37)[:, None]).bfloat16()
-    a[0, :32] = 0
-    a[1, 5] = float("inf")
-    a[3, :64] = torch.tensor(2.0**-120).bfloat16()  # tiny but normal in fp32
-    a[4, :32] = 448.0
-    a[5, :32] = 449.0
-    a[6, :32] = torch.tensor([2.0**k for k in range(-16, 16)]).bfloat16()
-    b = (torch.randn(200, 384, generator=g) * 0.02).bfloat16()
-    blob = {"a": a.view(torch.int16).numpy(), "b": b.view(torch.int16).numpy()}
-    blob["a_q"], blob["a_s"] = run(a, False)
-    blob["b_q"], blob["b_s_blocked"] = run(b, True)
-    np.savez_compressed(HERE / "quant_mxfp8.npz", **blob)
-    print("quant_mxfp8.npz ok")
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("DIST_MOE_REFERENCE", "reference"))
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
-    steps = {"plan": gen_plan_memory, "routing": gen_routing, "planner": gen_planner, "quant": gen_quant}
+    steps = {"plan": gen_plan_memory, "routing": gen_routing, "planner": gen_planner}
     for name, fn in steps.items():
         if not args.only or name in args.only.split(","):
             fn(args.reference)

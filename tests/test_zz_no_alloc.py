@@ -47,12 +47,12 @@ def _route(nat, static, bufs, ids_shape, rank, E, m_mult, dev, status):
             out["fwd"].data_ptr(), out["bwd"].data_ptr(), out["sct"].data_ptr())
     if static:
         rc = nat.lib.dm_route_static(*head, status.data_ptr(), nat.stream_ptr())
-        nat.check(rc, "dm_route_static")
+        nat.check(rc, nat.route_call_name(ep, T, el))
     else:
         words = nat.lib.dm_route_workspace_words(T, ep, E)
         ws = torch.empty(words, dtype=torch.int32, device=dev)
         rc = nat.lib.dm_route(*head, ws.data_ptr(), words, status.data_ptr(), nat.stream_ptr())
-        nat.check(rc, "dm_route")
+        nat.check(rc, nat.route_call_name(ep, T, el))
     torch.cuda.synchronize()
     rows = int(out["offsets"][-1])
     return {k: (v[:rows] if k in ("fwd", "bwd", "sct") else v).cpu().numpy() for k, v in out.items()}
@@ -64,9 +64,14 @@ def test_static_routing_matches_workspace_routing_on_two_calls_in_a_row():
     dev = torch.device("cuda", 0)
     status = torch.zeros(8, dtype=torch.int32, device=dev)
     rng = np.random.default_rng(11)
-    # Two different shapes back to back: the second call sees the first call's leftovers in the array.
-    shapes = [(4, 1000, 6, 64, 0), (2, 300, 4, 16, 128)]
+    # Different shapes back to back.  The first two have ep * T > 1024, so they run the three general kernels, the
+    # only ones that use the array: the second of them (other chunk counts, padded expert segments) starts from the
+    # first one's leftovers.  The third is in the single-launch decode regime, which keeps its counters in shared
+    # memory and must give the same tables through this entry point too.
+    shapes = [(4, 1000, 6, 64, 0), (2, 700, 4, 16, 128), (2, 300, 4, 16, 128)]
     for ep, T, K, E, m_mult in shapes:
+        general = ep * T > 1024
+        assert nat.route_call_name(ep, T, E // ep) == ("dm_route" if general else "dm_route(single launch)")
         ids = np.argsort(-rng.standard_normal((ep, T, E)), axis=-1)[..., :K].astype(np.int64)
         ids[rng.random(ids.shape) < 0.05] = -1
         bufs = _publish_all(nat, ids, E, dev, status)

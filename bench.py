@@ -8,9 +8,10 @@ synthetic data: x ~ N(0,1), weights ~ N(0,0.02), router logits ~ N(0,1).
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 For N > 1 launch one process per GPU with ``python -m torch.distributed.run``.  Rank 0 prints
-one JSON line.  ``--impl reference`` times the CPU restatement of the reference's math
-(``oracle/moe.py``; the reference itself has no CPU path and its GPU kernels need a newer
-software stack than this image) on the host cores, on a bounded token sample.
+one JSON line.  ``--impl reference`` times the unmodified reference installed under ``baseline/_ref``
+on one GPU through its own ``routed_experts`` (one-rank group, all experts local); if that is not
+available it times the CPU restatement of the reference's math (``oracle/moe.py``; the reference has
+no CPU path) on the host cores, on a bounded token sample.
 """
 
 from __future__ import annotations
@@ -32,6 +33,7 @@ sys.path.insert(0, str(ROOT))
 
 T, D, F, E, K = 4096, 2048, 1408, 64, 6
 CPU_SAMPLE_TOKENS = int(os.environ.get("DIST_MOE_BENCH_CPU_TOKENS", "256"))  # bounded CPU sample
+CPU_STEPS, CPU_WARMUP = 3, 1  # the same in both places that time the CPU restatement
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -43,6 +45,58 @@ def peaks():
         except Exception:
             pass
     return FALLBACK_PEAKS, "fallback"
+
+
+def kernel_source_digest() -> str:
+    """Digest of the grouped-GEMM sources; a recorded ncu traffic figure is only reported for the sources it was
+    captured on."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for name in ("gemm_bf16.cu", "gemm_common.cuh", "common.cuh"):
+        h.update((ROOT / "dist_moe_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def recorded_dram_traffic():
+    """(bytes per working GEMM launch, note) from profiles/grouped_gemm_dram_traffic.json, or (None, why)."""
+    path = ROOT / "profiles" / "grouped_gemm_dram_traffic.json"
+    try:
+        rec = json.loads(path.read_text())
+    except (OSError, ValueError):
+        return None, "no ncu capture recorded"
+    if rec.get("kernel_source_digest") != kernel_source_digest():
+        return None, f"stale: captured on kernel sources {rec.get('kernel_source_digest')}, commit {rec.get('commit')}"
+    return rec["dram_bytes_per_launch"], f"ncu dram read+write per launch, N=1 capture on commit {rec.get('commit')}"
+
+
+def sampled_parity(dm, ctx, opts, x, ids, scores, w13, w2, grad_out, sample=64):
+    """One forward + backward outside every timed region, checked on a token sample against the CPU oracle: an output
+    row, and the gradients of that token's input and scores, depend only on the token's own K experts, so 64 tokens
+    need 64 x K small products on the host.  Bounds are the reference's BF16 ones (tests/test_dist_moe.py:317-325)."""
+    from oracle import moe as oracle_moe
+
+    xs, ss = x.detach().clone().requires_grad_(True), scores.detach().clone().requires_grad_(True)
+    out = dm.routed_experts(xs, ids, ss, w13, w2, ctx, options=opts)
+    out.backward(grad_out)
+    ctx.check_status()
+    idx = torch.linspace(0, x.shape[0] - 1, sample).long()
+    gw = torch.Generator().manual_seed(2027)
+    w13_all = (torch.randn(E, 2, F, D, generator=gw) * 0.02).bfloat16().reshape(E, 2 * F, D)
+    w2_all = (torch.randn(E, D, F, generator=gw) * 0.02).bfloat16()
+    xr, sr = x[idx.to(x.device)].cpu().requires_grad_(True), scores[idx.to(x.device)].cpu().requires_grad_(True)
+    ref = oracle_moe.moe_forward(xr, ids[idx.to(x.device)].cpu(), sr, w13_all, w2_all)
+    ref.backward(grad_out[idx.to(x.device)].cpu())
+    report, ok = {}, True
+    for name, got, want, l2_max, cos_min in (("out", out[idx.to(x.device)], ref, 5e-3, 0.999),
+                                             ("grad_x", xs.grad[idx.to(x.device)], xr.grad, 1e-2, 0.995),
+                                             ("grad_scores", ss.grad[idx.to(x.device)], sr.grad, 1e-2, 0.995)):
+        got, want = got.detach().float().cpu(), want.detach().float()
+        l2 = ((got - want).norm() / want.norm().clamp_min(1e-30)).item()
+        cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0).item()
+        report[name] = {"rel_l2": l2, "cosine": cos}
+        ok = ok and l2 < l2_max and cos > cos_min
+    return ok, report
 
 
 def make_inputs(rank: int, world: int, device, tokens: int = T):
@@ -169,24 +223,157 @@ def base_line(args, world):
     }
 
 
+REFERENCE_DIR = ROOT / "baseline" / "_ref"
+
+
+def reference_gpu_step_times(args):
+    """Time the unmodified reference (installed under baseline/_ref) on GPU 0 through its own public API:
+    ``dist_moe.routed_experts`` forward + backward on this benchmark's inputs with all 64 experts on one rank.
+
+    The expert-parallel group is PyTorch's one-rank fake process group, for which the reference aliases its peer
+    buffers to local memory and skips its signal-pad barriers (they spin without a bound); with one rank that is
+    numerically the real thing.  Steps are CUDA-graph replays when the reference's step captures, eager calls
+    otherwise.  Returns None when the reference is not installed or does not run (the caller falls back to the CPU
+    restatement)."""
+    if not (REFERENCE_DIR / "dist_moe" / "__init__.py").exists() or not torch.cuda.is_available():
+        return None
+    sys.path.insert(0, str(REFERENCE_DIR))
+    try:
+        import importlib
+
+        ref = importlib.import_module("dist_moe")
+        dist = importlib.import_module("torch.distributed")
+        importlib.import_module("torch.testing._internal.distributed.fake_pg")  # registers the "fake" backend
+
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        if not dist.is_initialized():
+            dist.init_process_group("fake", rank=0, world_size=1)
+        x_h, ids_h, scores_h, w13_h, w2_h = make_inputs(0, 1, dev)
+        x_pin, ids_pin, scores_pin = x_h.pin_memory(), ids_h.pin_memory(), scores_h.pin_memory()
+        out_host = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
+        w13 = w13_h.reshape(E, 2 * F, D).to(dev).requires_grad_(True)
+        w2 = w2_h.to(dev).requires_grad_(True)
+        w13.grad, w2.grad = torch.zeros_like(w13), torch.zeros_like(w2)
+        cfg = ref.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                         max_moe_layers_per_activation_slot=1, activation_slot_capacity_factor=1.0,
+                         device_scratch_capacity_factor=1.0)
+        ctx = ref.create_context(group=dist.group.WORLD, config=cfg, device=dev, emulate_peer_buffers=True)
+        opts = ref.ExecutionOptions(inplace_wgrad_accum=True)
+        x, ids, scores = x_h.to(dev), ids_h.to(dev), scores_h.to(dev)
+        grad_out = torch.randn(T, D, generator=torch.Generator().manual_seed(4000)).bfloat16().to(dev)
+
+        def step():
+            xs, ss = x.detach().requires_grad_(True), scores.detach().requires_grad_(True)
+            out = ref.routed_experts(xs, ids, ss, w13, w2, ctx, options=opts)
+            out.backward(grad_out)
+            return out
+
+        warm = max(3, args.warmup)
+        for _ in range(warm):
+            step()
+        torch.cuda.synchronize()
+        graph, out_static = None, None
+        if not args.no_graph:
+            try:
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    step()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out_static = step()
+                graph.replay()
+                torch.cuda.synchronize()
+            except Exception as exc:  # noqa: BLE001 -- eager timing is still the reference's own code path
+                print(f"[bench] reference step did not capture ({exc!r}); timing eager calls", file=sys.stderr, flush=True)
+                graph = None
+                torch.cuda.synchronize()
+
+        def run_step():
+            if graph is not None:
+                graph.replay()
+                return out_static
+            return step()
+
+        def run_e2e():
+            x.copy_(x_pin, non_blocking=True)
+            ids.copy_(ids_pin, non_blocking=True)
+            scores.copy_(scores_pin, non_blocking=True)
+            out_host.copy_(run_step().detach(), non_blocking=True)
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(args.steps):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            return s.elapsed_time(e) / args.steps
+
+        sampler = ClockSampler(0)
+        sampler.start()
+        time.sleep(0.3)
+        sampler.mark()
+        ms = timed(run_step)
+        e2e_ms = timed(run_e2e)
+        sampler.mark()
+        clocks = sampler.stop()
+        ctx.close()
+        return {"ms": ms, "e2e_ms": e2e_ms, "warmup": warm, "mode": "cuda-graph replay" if graph is not None else "eager",
+                "clocks": clocks,
+                "h2d": x_pin.numel() * 2 + ids_pin.numel() * 8 + scores_pin.numel() * 4, "d2h": out_host.numel() * 2}
+    except Exception as exc:  # noqa: BLE001
+        print(f"[bench] the reference's GPU path did not run ({exc!r}); timing its CPU restatement", file=sys.stderr,
+              flush=True)
+        return None
+
+
 def run_reference(args):
+    """Reference arm: rank 0 alone works.  First choice is the reference's own GPU implementation on one GPU; if it is
+    not installed or fails, the CPU restatement of its math on the host cores (a bounded token sample)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 5))
-    cb = cpu_baseline(steps, max(1, min(args.warmup, 2)))
     line = base_line(args, world)
+    line["impl"] = "reference"
+    gpu = None if args.reference_on_cpu else reference_gpu_step_times(args)
+    if gpu is not None:
+        value = T / (gpu["ms"] * 1e-3)
+        line["config"]["workload"] = (f"BF16 training layer, the reference's own kernels on ONE GPU (EP=1, fake one-rank group): "
+                                      f"T={T} tokens, D={D}, F={F}, E={E} (all local), K={K}, plain SwiGLU, fwd+bwd, "
+                                      f"in-place wgrad accumulation")
+        line.update({
+            "value": value, "ms_per_step": gpu["ms"], "warmup": gpu["warmup"], "n_gpus_used": 1,
+            "step_mode": gpu["mode"], "clocks": gpu["clocks"],
+            "e2e": {"value": T / (gpu["e2e_ms"] * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": gpu["h2d"],
+                    "d2h_bytes_per_step": gpu["d2h"], "ms_per_step": gpu["e2e_ms"]},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                             "sample": "not a CPU run: the unmodified reference (baseline/_ref) on one B200, whole workload"},
+            "note": "unmodified reference from baseline/_ref through dist_moe.routed_experts; its Triton and CuTe-DSL "
+                    "kernels JIT on this image (torch 2.11 / triton 3.6 / cutlass-dsl 4.5)",
+        })
+        print(json.dumps(line), flush=True)
+        return
+    steps, warm = CPU_STEPS, CPU_WARMUP
+    cb = cpu_baseline(steps, warm)
     line.update({
-        "impl": "reference",
+        "steps": steps, "warmup": warm,
         "value": cb["value"],
-        "ms_per_step": cb["ms_per_step"],
-        "dtype": "bf16",
+        # one step of the stated workload (T tokens) at the sample's rate; the sample itself took sample_ms_per_step
+        "ms_per_step": T / cb["value"] * 1e3,
+        "sample_ms_per_step": cb["ms_per_step"],
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "CPU restatement of the reference's math on the host cores; the reference has no CPU path and its "
-                "CuTe-DSL/Triton kernels need torch>=2.14, triton>=3.8, cutlass-dsl>=4.6 (this image: 2.11/3.6/4.5)",
+        "note": "CPU restatement of the reference's math on the host cores (the reference has no CPU path); used "
+                "because the reference's GPU path was not available to this run",
     })
     print(json.dumps(line), flush=True)
 
@@ -423,11 +610,26 @@ def run_ours(args):
         "avg_launch_ms": gemm_ms / n_gemm if n_gemm else None,
         "launches": n_gemm,
         "timing": "CUDA events around every grouped-GEMM launch in an eager pass of the same K steps",
-        # dram__bytes_read + dram__bytes_write per working launch, from one ncu capture of this exact workload at
-        # N=1 (5.88 GB per step over 6 launches; summary under profiles/).  Not captured for N>1.
-        "traffic": 0.98e9 if world == 1 else None,
-        "traffic_unit": "bytes per launch (ncu dram read+write, N=1 capture)",
     }
+    traffic, traffic_note = recorded_dram_traffic() if world == 1 else (None, "not captured for N > 1")
+    roofline["traffic"] = traffic
+    roofline["traffic_unit"] = f"bytes per launch ({traffic_note})"
+
+    # ---- NVLink: bytes this rank moves to or from peers inside the four GEMM launches that carry the exchange
+    nvlink = None
+    if world > 1:
+        local_rows = int(((ids_h // (E // world)) == rank).sum().item())
+        remote_bytes = max(0, rows - local_rows) * D * 2
+        nvlink = {"remote_bytes_per_launch": remote_bytes, "peak": 900.0, "unit": "GB/s per direction",
+                  "note": "remote rows x D x 2 bytes / CUDA-event time of the whole launch (GEMM included): a lower "
+                          "bound on the link rate while it overlaps the tensor cores; rank 0"}
+        for key, name in (("dispatch_pull_w13_fprop", "gemm_fprop_dispatch(w13)"), ("combine_push_w2_fprop", "gemm_fprop(w2)"),
+                          ("dispatch_pull_w2_dgrad", "gemm_dgrad_dispatch(w2)"), ("combine_push_w13_dgrad", "gemm_dgrad(w13)")):
+            if breakdown.get(name):
+                nvlink[key] = {"us": breakdown[name], "GBps": remote_bytes / (breakdown[name] * 1e-6) / 1e9,
+                               "frac": remote_bytes / (breakdown[name] * 1e-6) / 1e9 / 900.0}
+
+    parity_ok, parity = sampled_parity(dm, ctx, opts, x, ids, scores, w13, w2, grad_out)
 
     if rank == 0:
         line = base_line(args, world)
@@ -445,12 +647,35 @@ def run_ours(args):
             "roofline": roofline,
             "routed_rows_rank0": rows,
             "gemm_us_per_launch": breakdown,
+            "parity_checked": bool(parity_ok),
+            "parity": parity,
         })
+        if nvlink is not None:
+            line["nvlink"] = nvlink
         if world == 1 and not args.no_cpu_baseline:
-            cb = cpu_baseline(2, 1)
+            cb = cpu_baseline(CPU_STEPS, CPU_WARMUP)
             line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
     ctx.close()
+    del ctx, w13, w2
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_extras:
+        # the other configurations of the reference's benchmark table, one short run each, same process
+        extras = {}
+        for name, tokens, experts in (("mxfp8-train", 0, 0), ("nvfp4-decode", 0, 0), ("nvfp4-decode", 0, 32),
+                                      ("nvfp4-prefill", 0, 32), ("mxfp8-infer", 0, 0)):
+            sub = argparse.Namespace(**{**vars(args), "workload": name, "tokens": tokens, "experts": experts,
+                                        "steps": 10 if name == "mxfp8-train" else 50, "warmup": 3})
+            key = name + (f"-E{experts}" if experts else "")
+            try:
+                res = run_mxfp8_train(sub, emit=False) if name == "mxfp8-train" else run_inference(sub, emit=False)
+                extras[key] = {k: res[k] for k in ("value", "unit", "ms_per_step", "p50_us", "p90_us", "steps", "step_mode",
+                                                    "tflops_balanced", "achieved") if k in res}
+                extras[key]["workload"] = res["config"]["workload"]
+            except Exception as exc:  # noqa: BLE001 -- an extra must not cost the headline line
+                extras[key] = {"error": repr(exc)[:300]}
+        line["other_workloads"] = extras
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -465,7 +690,7 @@ INFERENCE_WORKLOADS = {
 }
 
 
-def run_mxfp8_train(args):
+def run_mxfp8_train(args, emit=True):
     """MXFP8 E4M3 training layer (forward + backward, prepared weights, in-place weight-gradient accumulation) at
     the reference's EP=8 MXFP8 configuration: T=8192 tokens/rank, D=4096, F=1536, E=128, K=8, router logits N(0,1)
     plus a per-expert bias drawn from Zipf(1.1).  Steps are eager calls timed with CUDA events; a second pass
@@ -484,7 +709,8 @@ def run_mxfp8_train(args):
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
@@ -572,8 +798,9 @@ def run_mxfp8_train(args):
         setattr(_native.lib, n, saved[n])
     breakdown = [[n[3:], round(a0.elapsed_time(a1) * 1e3, 1)] for n, a0, a1 in events]
     rows = int(padded) if world == 1 else None
+    line = None
     if rank == 0:
-        print(json.dumps({
+        line = ({
             "metric": "MoE layer tokens/s (MXFP8 E4M3 training layer, fwd+bwd), whole job", "value": world * Tn / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e8m0 block scales",
@@ -584,14 +811,19 @@ def run_mxfp8_train(args):
                        "capacity_factor": factor},
             "gpu_launches": launches, "step_mode": "eager", "clocks": clocks, "padded_rows_busiest_rank": rows,
             "flops_per_step_rank0_balanced": 18.0 * Tn * Kn * Dn * Fn,
-            "tflops_balanced": 18.0 * Tn * Kn * Dn * Fn / (ms * 1e-3) / 1e12, "us_per_call": breakdown}), flush=True)
+            "tflops_balanced": 18.0 * Tn * Kn * Dn * Fn / (ms * 1e-3) / 1e12, "us_per_call": breakdown})
+        if emit:
+            print(json.dumps(line), flush=True)
     ctx.close()
-    if world > 1:
+    del ctx, p13, p2, w13, w2
+    torch.cuda.empty_cache()
+    if world > 1 and emit:
         dist.barrier()
         dist.destroy_process_group()
+    return line
 
 
-def run_inference(args):
+def run_inference(args, emit=True):
     """Forward-only inference workloads with prepared block-scaled weights, timed as CUDA-graph replays.
 
     Every replay is bracketed by its own pair of CUDA events, so the line carries the median (p50) and the
@@ -615,7 +847,8 @@ def run_inference(args):
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
@@ -701,6 +934,7 @@ def run_inference(args):
     weight_bytes = hit * 3 * Dn * Fn * bits / 8
     flops = 6.0 * rows * Dn * Fn
     pk, src = peaks()
+    line = None
     if rank == 0:
         line = {
             "metric": f"MoE layer tokens/s ({fmt} inference forward, prepared weights, CUDA-graph replay), whole job",
@@ -718,12 +952,16 @@ def run_inference(args):
             "achieved": {"weight_stream_GBps": weight_bytes / (p50 * 1e-3) / 1e9, "hbm_peak_GBps": pk["hbm_gbs"],
                          "tflops": flops / (p50 * 1e-3) / 1e12, "peak_source": src},
         }
-        print(json.dumps(line), flush=True)
+        if emit:
+            print(json.dumps(line), flush=True)
     _ = out
     ctx.close()
-    if world > 1:
+    del ctx, graph, p13, p2
+    torch.cuda.empty_cache()
+    if world > 1 and emit:
         dist.barrier()
         dist.destroy_process_group()
+    return line
 
 
 def run_micro(args):
@@ -820,6 +1058,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="N=1: skip the short runs of the MXFP8 / NVFP4 workloads added to the line as other_workloads")
+    ap.add_argument("--reference-on-cpu", action="store_true",
+                    help="--impl reference: time the CPU restatement even when the reference's GPU build is installed")
     ap.add_argument("--separate-gather", action="store_true",
                     help="gather routed rows with a separate kernel instead of inside the GEMM launches")
     ap.add_argument("--no-graph", action="store_true",

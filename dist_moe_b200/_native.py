@@ -35,9 +35,16 @@ class NativeError(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
-    if not _LIB_PATH.exists():
-        from .build import build
+    # build() compares a digest of the sources with the one the library was built from and returns at once when they
+    # agree, so a library left over from older sources is never loaded silently.
+    from .build import build, find_nvcc
 
+    try:
+        find_nvcc()
+        have_nvcc = True
+    except RuntimeError:
+        have_nvcc = False
+    if have_nvcc or not _LIB_PATH.exists():
         build()
     if not _LIB_PATH.exists():
         raise ImportError(f"dist_moe_b200: CUDA library missing at {_LIB_PATH}; run python -m dist_moe_b200.build")
@@ -81,6 +88,7 @@ _SIGNATURES = {
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
     "dm_set_gemm_pairs": (c_int, [c_int]),
+    "dm_set_gemm_prefetch": (c_int, [c_int]),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
     "dm_blockscaled_wide_enabled": (c_int, []),
     "dm_set_route_decode_kernel": (c_int, [c_int]),

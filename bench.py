@@ -334,6 +334,163 @@ def reference_gpu_step_times(args):
         return None
 
 
+def _reference_modules():
+    import importlib
+
+    sys.path.insert(0, str(REFERENCE_DIR))
+    ref = importlib.import_module("dist_moe")
+    dist = importlib.import_module("torch.distributed")
+    importlib.import_module("torch.testing._internal.distributed.fake_pg")  # registers the "fake" backend
+    if not dist.is_initialized():
+        dist.init_process_group("fake", rank=0, world_size=1)
+    return ref, dist
+
+
+def _time_replays(fn, steps, warmup):
+    """p50 / p90 / mean in milliseconds of ``steps`` calls, each bracketed by its own CUDA events."""
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    pairs = []
+    for _ in range(steps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        pairs.append((s, e))
+    torch.cuda.synchronize()
+    times = sorted(s.elapsed_time(e) for s, e in pairs)
+    return times[len(times) // 2], times[min(len(times) - 1, (len(times) * 9) // 10)], sum(times) / len(times)
+
+
+def _capture(step, dev, no_graph):
+    """CUDA graph of ``step`` (or None when capture is off or fails) and its static result."""
+    if no_graph:
+        return None, None
+    try:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = step()
+        graph.replay()
+        torch.cuda.synchronize()
+        return graph, out
+    except Exception as exc:  # noqa: BLE001
+        print(f"[bench] step did not capture ({exc!r}); timing eager calls", file=sys.stderr, flush=True)
+        torch.cuda.synchronize()
+        return None, None
+
+
+def reference_blockscaled(args):
+    """The unmodified reference (baseline/_ref) on GPU 0 for the block-scaled workloads, one rank, same inputs as
+    this repository's arm.  Both of its pipelines are tried ("mega" = its chunk-pipelined fused launch, "staged");
+    the faster one that runs is the line's value, both are listed."""
+    ref, dist = _reference_modules()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tried = {}
+    train = args.workload == "mxfp8-train"
+    case = mxfp8_train_case(args, 0, 1, dev) if train else inference_case(args, 0, 1, dev)
+    Tn, Dn, Fn, En, Kn = (case[k] for k in ("T", "D", "F", "E", "K"))
+    x, ids, scores = case["x"], case["ids"], case["scores"]
+    fmt = "MXFP8_E4M3" if train else case["fmt"]
+    if train:
+        padded = ((case["per_expert"] + 127) // 128 * 128).sum().item()
+        factor = min(1.0, max(1.0, 1.02 * padded / float(Tn * Kn)))
+        # leaves of their own (the reference resolves a view to its base to find the gradient's owner)
+        w13 = case.pop("w13").reshape(En, 2 * Fn, Dn).clone().requires_grad_(True)
+        w2 = case.pop("w2").clone().requires_grad_(True)
+        w13.grad, w2.grad = torch.zeros_like(w13), torch.zeros_like(w2)
+    else:
+        factor = 1.0
+        gen = case["weights"]()
+        w13 = next(gen).reshape(En, 2 * Fn, Dn)
+        w2 = next(gen)
+    extra = {"activation": "swiglu_clamped", "swiglu_limit": 7.0} if (not train and case["clamped"]) else {}
+    for pipeline in ("mega", "staged"):
+        ctx = None
+        try:
+            policy = ref.BlockScaledConfig(format=getattr(ref.BlockScaledFormat, fmt), pipeline=pipeline)
+            if train:
+                cfg = ref.Config(max_num_local_input_tokens=Tn, hidden_dim=Dn, intermediate_dim=Fn, top_k=Kn, num_experts=En,
+                                 max_moe_layers_per_activation_slot=1, block_scaled=policy,
+                                 activation_slot_capacity_factor=1.0, device_scratch_capacity_factor=factor)
+            else:
+                cfg = ref.Config(max_num_local_input_tokens=Tn, hidden_dim=Dn, intermediate_dim=Fn, top_k=Kn, num_experts=En,
+                                 max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0,
+                                 block_scaled=policy, device_scratch_capacity_factor=factor, **extra)
+            ctx = ref.create_context(group=dist.group.WORLD, config=cfg, device=dev, emulate_peer_buffers=True)
+            if train:
+                p13 = ref.prepare_block_scaled_weight(w13, policy)
+                p2 = ref.prepare_block_scaled_weight(w2, policy)
+                opts = ref.ExecutionOptions(inplace_wgrad_accum=True)
+                grad_out = case["grad_out"]
+
+                def step():
+                    xs, ss = x.detach().requires_grad_(True), scores.detach().requires_grad_(True)
+                    out = ref.routed_experts(xs, ids, ss, p13, p2, ctx, options=opts)
+                    out.backward(grad_out)
+                    return out
+            else:
+                p13 = ref.prepare_block_scaled_weight(w13, policy, inference=True, fuse_swiglu=pipeline == "mega")
+                p2 = ref.prepare_block_scaled_weight(w2, policy, inference=True)
+
+                def step():
+                    with torch.no_grad():
+                        return ref.routed_experts(x, ids, scores, p13, p2, ctx)
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            graph, _out = _capture(step, dev, args.no_graph)
+            p50, p90, mean = _time_replays(graph.replay if graph is not None else step, args.steps, args.warmup)
+            tried[pipeline] = {"p50_ms": p50, "p90_ms": p90, "mean_ms": mean,
+                               "step_mode": "cuda-graph replay" if graph is not None else "eager"}
+            del graph, p13, p2
+        except Exception as exc:  # noqa: BLE001 -- the other pipeline may still run
+            tried[pipeline] = {"error": repr(exc)[:400]}
+            torch.cuda.synchronize()
+        finally:
+            if ctx is not None:
+                ctx.close()
+            torch.cuda.empty_cache()
+    ok = {k: v for k, v in tried.items() if "mean_ms" in v}
+    if not ok:
+        return None, tried, case
+    best = min(ok, key=lambda k: ok[k]["mean_ms"])
+    return best, tried, case
+
+
+def run_reference_blockscaled(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    best, tried, case = reference_blockscaled(args)
+    Tn = case["T"]
+    line = {"impl": "reference", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "n_gpus_used": 1, "steps": args.steps,
+            "warmup": max(3, args.warmup), "unit": "tokens/s", "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "data": "synthetic, the same seeded inputs as this repository's arm",
+            "metric": f"MoE layer tokens/s ({args.workload}), the reference's own kernels on one GPU",
+            "config": {"workload": f"{args.workload}: T={Tn}, D={case['D']}, F={case['F']}, E={case['E']} (all local), "
+                                   f"K={case['K']}; reference from baseline/_ref, one-rank fake group"},
+            "pipelines": tried}
+    if best is None:
+        line["unavailable"] = "neither pipeline of the reference ran for this workload (errors under 'pipelines')"
+    else:
+        r = tried[best]
+        line.update({"pipeline": best, "value": Tn / (r["mean_ms"] * 1e-3), "ms_per_step": r["mean_ms"],
+                     "p50_us": r["p50_ms"] * 1e3, "p90_us": r["p90_ms"] * 1e3, "step_mode": r["step_mode"],
+                     "e2e": {"value": Tn / (r["mean_ms"] * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                             "d2h_bytes_per_step": 0},
+                     "cpu_baseline": {"value": Tn / (r["mean_ms"] * 1e-3), "unit": "tokens/s", "cores": 0, "kind": "reference",
+                                      "sample": "not a CPU run: the unmodified reference on one B200, whole workload"}})
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args):
     """Reference arm: rank 0 alone works.  First choice is the reference's own GPU implementation on one GPU; if it is
     not installed or fails, the CPU restatement of its math on the host cores (a bounded token sample)."""
@@ -690,6 +847,56 @@ INFERENCE_WORKLOADS = {
 }
 
 
+def mxfp8_train_case(args, rank, world, dev):
+    """Inputs of the MXFP8 training workload (shared by both arms): tokens, Zipf-skewed top-8 routing, bf16 weights
+    and the scratch capacity factor the skew needs."""
+    import numpy as np
+
+    Tn, Dn, Fn, En, Kn = args.tokens or 8192, 4096, 1536, args.experts or 128, 8
+    e_local = En // world
+    g = torch.Generator().manual_seed(1000 + rank)
+    x = torch.randn(Tn, Dn, generator=g).bfloat16().to(dev)
+    bias = torch.from_numpy(np.random.default_rng(2027).zipf(1.1, En).clip(max=64).astype("float32")).log()
+    logits = torch.randn(Tn, En, generator=g) + bias
+    top = torch.topk(torch.softmax(logits, -1), Kn)
+    scores = (top.values / top.values.sum(-1, keepdim=True)).float().to(dev)
+    ids = top.indices.to(dev)
+    per_expert = torch.bincount(top.indices.flatten(), minlength=En).float()
+    grad_out = torch.randn(Tn, Dn, generator=g).bfloat16().to(dev)
+    gw = torch.Generator(device=dev).manual_seed(2027 + rank)
+    w13 = (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16()
+    w2 = (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16()
+    return dict(T=Tn, D=Dn, F=Fn, E=En, K=Kn, e_local=e_local, x=x, ids=ids, scores=scores, per_expert=per_expert,
+                grad_out=grad_out, w13=w13, w2=w2)
+
+
+def inference_case(args, rank, world, dev):
+    """Inputs of a forward-only inference workload (shared by both arms)."""
+    fmt, Tn, Dn, Fn, En, Kn, clamped, routing = INFERENCE_WORKLOADS[args.workload]
+    if args.tokens:
+        Tn = args.tokens
+    if args.experts:
+        En = args.experts  # e.g. E / 8: one rank's share of the experts of the EP=8 configuration on one GPU
+    e_local = En // world
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    x = torch.randn(Tn, Dn, device=dev, generator=g).bfloat16()
+    logits = torch.randn(Tn, En, device=dev, generator=g)
+    top = torch.topk(logits, Kn)
+    if routing == "sigmoid":   # sigmoid scores of the top-k logits, not renormalised
+        scores, ids = torch.sigmoid(top.values).float(), top.indices
+    else:                      # uniform random distinct experts, softmax-renormalised scores
+        scores, ids = torch.softmax(top.values, -1).float(), top.indices
+    gw = torch.Generator(device=dev).manual_seed(2027 + rank)
+
+    def weights():
+        """W13 then W2, generated one after the other so that only one bf16 weight is alive next to its quantised form."""
+        yield (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16()
+        yield (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16()
+
+    return dict(fmt=fmt, T=Tn, D=Dn, F=Fn, E=En, K=Kn, e_local=e_local, clamped=clamped, x=x, ids=ids, scores=scores,
+                weights=weights)
+
+
 def run_mxfp8_train(args, emit=True):
     """MXFP8 E4M3 training layer (forward + backward, prepared weights, in-place weight-gradient accumulation) at
     the reference's EP=8 MXFP8 configuration: T=8192 tokens/rank, D=4096, F=1536, E=128, K=8, router logits N(0,1)
@@ -700,7 +907,6 @@ def run_mxfp8_train(args, emit=True):
     import dist_moe_b200 as dm
     from dist_moe_b200 import _native
 
-    Tn, Dn, Fn, En, Kn = args.tokens or 8192, 4096, 1536, args.experts or 128, 8
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -714,27 +920,19 @@ def run_mxfp8_train(args, emit=True):
         group = dist.group.WORLD
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
-    e_local = En // world
-    g = torch.Generator().manual_seed(1000 + rank)
-    x = torch.randn(Tn, Dn, generator=g).bfloat16().to(dev)
-    bias = torch.from_numpy(__import__("numpy").random.default_rng(2027).zipf(1.1, En).clip(max=64).astype("float32")).log()
-    logits = torch.randn(Tn, En, generator=g) + bias
-    top = torch.topk(torch.softmax(logits, -1), Kn)
-    scores = (top.values / top.values.sum(-1, keepdim=True)).float().to(dev)
-    ids = top.indices.to(dev)
+    case = mxfp8_train_case(args, rank, world, dev)
+    Tn, Dn, Fn, En, Kn, e_local = (case[k] for k in ("T", "D", "F", "E", "K", "e_local"))
+    x, ids, scores, grad_out = case["x"], case["ids"], case["scores"], case["grad_out"]
     # rows the busiest rank receives (every expert's rows padded to 128), relative to T*K: the plan's capacity factor
-    per_expert = torch.bincount(top.indices.flatten(), minlength=En).float()
+    per_expert = case["per_expert"]
     if world > 1:
         t = per_expert.to(dev)
         dist.all_reduce(t)
         per_expert = t.cpu()
     padded = ((per_expert + 127) // 128 * 128).view(world, e_local).sum(1).max().item()
     factor = min(float(world), max(1.0, 1.02 * padded / float(Tn * Kn)))
-    gw = torch.Generator(device=dev).manual_seed(2027 + rank)
-    w13 = (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16().requires_grad_(True)
-    w2 = (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16().requires_grad_(True)
+    w13, w2 = case["w13"].requires_grad_(True), case["w2"].requires_grad_(True)
     w13.grad, w2.grad = torch.zeros_like(w13), torch.zeros_like(w2)
-    grad_out = torch.randn(Tn, Dn, generator=g).bfloat16().to(dev)
     cfg = dm.Config(max_num_local_input_tokens=Tn, hidden_dim=Dn, intermediate_dim=Fn, top_k=Kn, num_experts=En,
                     max_moe_layers_per_activation_slot=1, block_scaled=dm.BlockScaledConfig(),
                     device_scratch_capacity_factor=factor)
@@ -834,11 +1032,6 @@ def run_inference(args, emit=True):
 
     import dist_moe_b200 as dm
 
-    fmt, Tn, Dn, Fn, En, Kn, clamped, routing = INFERENCE_WORKLOADS[args.workload]
-    if args.tokens:
-        Tn = args.tokens
-    if args.experts:
-        En = args.experts  # e.g. E / 8: one rank's share of the experts of the EP=8 configuration on one GPU
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -852,16 +1045,9 @@ def run_inference(args, emit=True):
         group = dist.group.WORLD
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
-    e_local = En // world
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    x = torch.randn(Tn, Dn, device=dev, generator=g).bfloat16()
-    logits = torch.randn(Tn, En, device=dev, generator=g)
-    if routing == "sigmoid":   # sigmoid scores of the top-k logits, not renormalised
-        top = torch.topk(logits, Kn)
-        scores, ids = torch.sigmoid(top.values).float(), top.indices
-    else:                      # uniform random distinct experts, softmax-renormalised scores
-        top = torch.topk(logits, Kn)
-        scores, ids = torch.softmax(top.values, -1).float(), top.indices
+    case = inference_case(args, rank, world, dev)
+    fmt, Tn, Dn, Fn, En, Kn, e_local, clamped = (case[k] for k in ("fmt", "T", "D", "F", "E", "K", "e_local", "clamped"))
+    x, ids, scores = case["x"], case["ids"], case["scores"]
     bs = dm.BlockScaledConfig(format=getattr(dm.BlockScaledFormat, fmt))
     extra = {"activation": "swiglu_clamped", "swiglu_limit": 7.0} if clamped else {}
     rows_max = int(torch.bincount((ids // e_local).flatten(), minlength=world).max().item())
@@ -875,11 +1061,11 @@ def run_inference(args, emit=True):
                     max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0, block_scaled=bs,
                     device_scratch_capacity_factor=factor, **extra)
     ctx = dm.create_context(group=group, config=cfg, device=dev)
-    gw = torch.Generator(device=dev).manual_seed(2027 + rank)
-    w13 = (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16()
+    gen = case["weights"]()
+    w13 = next(gen)
     p13 = dm.prepare_block_scaled_weight(w13, cfg, fuse_swiglu=True, inference=True)
     del w13
-    w2 = (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16()
+    w2 = next(gen)
     p2 = dm.prepare_block_scaled_weight(w2, cfg, inference=True)
     del w2
     torch.cuda.empty_cache()
@@ -1081,6 +1267,8 @@ def main():
         _native.lib.dm_set_gemm_pairs(1)
     if args.micro:
         run_micro(args)
+    elif args.impl == "reference" and args.workload != "bf16-train":
+        run_reference_blockscaled(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "mxfp8-train":

@@ -88,7 +88,6 @@ _SIGNATURES = {
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
     "dm_set_gemm_pairs": (c_int, [c_int]),
-    "dm_set_gemm_prefetch": (c_int, [c_int]),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
     "dm_blockscaled_wide_enabled": (c_int, []),
     "dm_set_route_decode_kernel": (c_int, [c_int]),

@@ -151,16 +151,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, in
       : "memory");
 }
 
-// Prefetch of one box of a tensor map into L2 (no shared-memory destination, no barrier): issued a few pipeline
-// stages ahead of the load of the same box, so that the load finds its lines in L2 instead of waiting for DRAM.
-__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), no multicast.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(

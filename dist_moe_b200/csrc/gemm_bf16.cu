@@ -65,7 +65,6 @@ struct GemmParams {
   int fused;    // fprop: W13 gate/up pairing + SwiGLU epilogue (N = 2F)
   int out_fp32; // wgrad
   int accumulate;
-  int prefetch;  // pipeline stages the producer prefetches into L2 ahead of its loads (0 = off)
   ActParams act;
 };
 
@@ -178,56 +177,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     bool ok = true;
     int ready_blocks = 0;  // row blocks [0, ready_blocks) are known to have landed
     const int total_rows = s_off[p.e_local];
-    // L2 prefetch cursor: runs p.prefetch stages ahead of the load cursor through the same (tile, k) sequence and
-    // asks the copy engine to bring the boxes of that stage into L2.  A stage is usable only when its slowest
-    // line has arrived, so without this nearly every stage waits for a DRAM miss.
-    int pf_tile = blockIdx.x, pf_e = 0, pf_kb = 0;
-    bool pf_valid = false;
-    Tile pf_t{};
-    auto prefetch_stage = [&]() {
-      while (!pf_valid && pf_tile < total_tiles) {
-        pf_t = decode_tile<kMode>(pf_tile, pf_e, s_tile_start, s_off, n_tiles, p.Kd);
-        pf_kb = 0;
-        if (pf_t.k_iters > 0)
-          pf_valid = true;
-        else
-          pf_tile += gridDim.x;
-      }
-      if (!pf_valid) return;
-      const Tile& t = pf_t;
-      const int kb = pf_kb;
-      if (kMode == kWgrad) {
-        const int row = t.row0 + kb * kBK;
-        if (wgrad_part == 0) {
-#pragma unroll
-          for (int b = 0; b < kBM / 64; ++b) tma_prefetch_3d(&p.tm_a, 0, a_line0 + t.m_blk * (kBM / 64) + b, row);
-        } else {
-          const int b0 = (wgrad_part - 1) * 2;
-#pragma unroll
-          for (int b = b0; b < b0 + 2; ++b) tma_prefetch_3d(&p.tm_b, 0, b_line0 + t.n_blk * (kBN / 64) + b, row);
-        }
-      } else {
-        if (p.gather_flags == nullptr) tma_prefetch_3d(&p.tm_a, 0, a_line0 + kb, t.row0);  // gathered rows are in L2 already
-        if (kMode == kFprop) {
-          if (p.fused) {
-            const int r0 = t.e * p.N + t.n_blk * (kBN / 2);
-            tma_prefetch_2d(&p.tm_b, kb * kBK, r0);
-            tma_prefetch_2d(&p.tm_b, kb * kBK, r0 + p.N / 2);
-          } else {
-            tma_prefetch_2d(&p.tm_b256, kb * kBK, t.e * p.N + t.n_blk * kBN);
-          }
-        } else {
-#pragma unroll
-          for (int b = 0; b < kBN / 64; ++b) tma_prefetch_2d(&p.tm_b, t.n_blk * kBN + b * 64, t.e * p.Kd + kb * kBK);
-        }
-      }
-      if (++pf_kb >= pf_t.k_iters) {
-        pf_valid = false;
-        pf_tile += gridDim.x;
-      }
-    };
-    if (lane == 0)
-      for (int i = 0; i < p.prefetch; ++i) prefetch_stage();
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const Tile t = decode_tile<kMode>(tile, e, s_tile_start, s_off, n_tiles, p.Kd);
       if (kMode != kWgrad && p.gather_flags != nullptr && lane == 0) {
@@ -259,8 +208,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           if (ok) {
             uint8_t* sa = smem + stage * kStageBytes;
             uint8_t* sb = sa + kABytes;
+#ifdef DM_EXP_NOLOAD
+            if (kMode != kWgrad || wgrad_part == 0) mbar_arrive(&full_bar[stage]);
+            if (false) {
+#else
             if (kMode != kWgrad || wgrad_part == 0) mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
             if (kMode == kWgrad) {
+#endif
               const int row = t.row0 + kb * kBK;
               if (wgrad_part == 0) {
 #pragma unroll
@@ -272,7 +226,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                 for (int b = b0; b < b0 + 2; ++b)
                   tma_load_3d(sb + b * 8192, &p.tm_b, 0, b_line0 + t.n_blk * (kBN / 64) + b, row, &full_bar[stage]);
               }
+#ifdef DM_EXP_NOLOAD
+            } else if (false) {
+#else
             } else {
+#endif
               tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
               if (kMode == kFprop) {
                 int r0, r1;
@@ -297,7 +255,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                               &full_bar[stage]);
               }
             }
-            if (p.prefetch > 0) prefetch_stage();
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -391,10 +348,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           if (!ok) break;
           const uint32_t a_lo = a_lo0 + st * (kStageBytes >> 4), b_lo = b_lo0 + st * (kStageBytes >> 4);
           const int ksteps = (kMode == kWgrad && kb == t.k_iters - 1) ? (valid_last + 15) >> 4 : kBK / 16;
+#ifndef DM_EXP_NOMMA
           umma_bf16_lo(d_tmem, a_lo, b_lo, kDescHi, idesc, kb > 0 ? 1u : 0u);
           if (ksteps > 1) umma_bf16_lo(d_tmem, a_lo + a_step, b_lo + b_step, kDescHi, idesc, 1u);
           if (ksteps > 2) umma_bf16_lo(d_tmem, a_lo + 2 * a_step, b_lo + 2 * b_step, kDescHi, idesc, 1u);
           if (ksteps > 3) umma_bf16_lo(d_tmem, a_lo + 3 * a_step, b_lo + 3 * b_step, kDescHi, idesc, 1u);
+#else
+          (void)a_lo; (void)b_lo; (void)ksteps;
+#endif
           tcgen05_commit_addr(empty0 + st * 8);
           if (++st == kStages) {
             st = 0;
@@ -538,7 +499,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;
-
+#ifdef DM_EXP_NOEPI
+      if (false) {
+      } else if (kMode != kWgrad) {
+      } else
+#endif
       if (kMode == kWgrad) {
         for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
           uint32_t r[32];
@@ -632,7 +597,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                 const int rr = i * 8 + (lane >> 2), j = lane & 3;
                 const uint4 v = stage64_get(stg, rr, j);
                 const uint64_t rp = __shfl_sync(0xffffffffu, base, rr);
+#ifdef DM_EXP_NOSTORE
+                if (rp == 1 && v.x == 0x12345u)
+#else
                 if (rp != 0 && col + 8 * j + 8 <= F)
+#endif
                   *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col_out + 8 * j) * 2) = v;
               }
               __syncwarp();
@@ -652,7 +621,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
               const int rr = i * 8 + (lane >> 2), j = lane & 3;
               const uint4 v = stage64_get(stg, rr, j);
               const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+#ifdef DM_EXP_NOSTORE
+              if (rp == 1 && v.x == 0x12345u)
+#else
               if (rp != 0 && col + 8 * j + 8 <= p.N)
+#endif
                 *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
             }
             __syncwarp();
@@ -676,13 +649,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   }
 }
 
-// Stages of L2 prefetch the producers run ahead of their loads (see prefetch_stage in the kernel).
-static int g_gemm_prefetch = 8;
-
 template <int kMode>
-static int launch(const GemmParams& params, int num_sms, cudaStream_t st) {
-  GemmParams p = params;
-  p.prefetch = g_gemm_prefetch;
+static int launch(const GemmParams& p, int num_sms, cudaStream_t st) {
   static PerDeviceOnce attr_set;
   const int rc = once_per_device(attr_set, [] {
     return static_cast<int>(cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -702,12 +670,6 @@ using namespace dm;
 // Measured on B200 the two kernels are level for large experts (3072 rows per expert: 235 vs 236 us for the
 // W13 forward) and the single-CTA kernel is ahead for small ones (384 rows: 265 vs 306 us), so pairs are opt-in.
 static int g_use_pairs = 0;
-
-extern "C" int dm_set_gemm_prefetch(int stages) {
-  const int previous = g_gemm_prefetch;
-  g_gemm_prefetch = stages < 0 ? 0 : (stages > 64 ? 64 : stages);
-  return previous;
-}
 
 extern "C" int dm_set_gemm_pairs(int enabled) {
   const int previous = g_use_pairs;

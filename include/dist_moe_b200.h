@@ -258,10 +258,6 @@ int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int ac
  * accumulation order.  No counterpart in the reference (it selects kernels through GemmKernelConfig,
  * dist_moe/api.py:233-262). */
 int dm_set_gemm_pairs(int enabled);
-/* Pipeline stages of L2 prefetch (cp.async.bulk.prefetch.tensor) that the TMA producers of the BF16 grouped GEMMs
- * run ahead of their loads; 0 switches it off.  Returns the previous setting.  Tuning knob, no effect on results;
- * no counterpart in the reference. */
-int dm_set_gemm_prefetch(int stages);
 
 
 /* ---------------------------------------------------------------------------

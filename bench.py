@@ -953,20 +953,27 @@ def run_mxfp8_train(args, emit=True):
     for _ in range(max(3, args.warmup)):
         step()
     ctx.check_status()
+    l0 = _native.LAUNCHES[0]
+    step()
+    launches_per_step = _native.LAUNCHES[0] - l0
+    graph, _ = _capture(step, dev, args.no_graph)  # one step = one CUDA-graph replay, as in the BF16 workload
+    run_step = graph.replay if graph is not None else step
+    for _ in range(3):
+        run_step()
+    ctx.check_status()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     sync_all()
     sampler.mark()
-    l0 = _native.LAUNCHES[0]
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s0.record()
     for _ in range(args.steps):
-        step()
+        run_step()
     s1.record()
     sync_all()
     sampler.mark()
-    launches = _native.LAUNCHES[0] - l0
+    launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     ctx.check_status()
     ms = torch.tensor([s0.elapsed_time(s1) / args.steps], device=dev, dtype=torch.float64)
@@ -1007,7 +1014,8 @@ def run_mxfp8_train(args, emit=True):
                                    f"plain SwiGLU, fwd+bwd, prepared weights, in-place wgrad accumulation",
                        "l2": "no flush: weights and routed activations exceed the 126 MB L2",
                        "capacity_factor": factor},
-            "gpu_launches": launches, "step_mode": "eager", "clocks": clocks, "padded_rows_busiest_rank": rows,
+            "gpu_launches": launches, "step_mode": "cuda-graph replay" if graph is not None else "eager", "clocks": clocks,
+            "padded_rows_busiest_rank": rows,
             "flops_per_step_rank0_balanced": 18.0 * Tn * Kn * Dn * Fn,
             "tflops_balanced": 18.0 * Tn * Kn * Dn * Fn / (ms * 1e-3) / 1e12, "us_per_call": breakdown})
         if emit:
@@ -1252,8 +1260,6 @@ def main():
                     help="gather routed rows with a separate kernel instead of inside the GEMM launches")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager routed_experts calls instead of CUDA-graph replays of the same step")
-    ap.add_argument("--cta-pairs", action="store_true",
-                    help="run forward / input-gradient GEMMs on the CTA-pair kernel (tcgen05 cta_group::2)")
     ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8", "quant-mxfp8"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
     ap.add_argument("--workload", default="bf16-train", choices=["bf16-train", "mxfp8-train"] + sorted(INFERENCE_WORKLOADS),
@@ -1261,10 +1267,6 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank of an inference workload (sweeps)")
     ap.add_argument("--experts", type=int, default=0, help="total experts of an inference workload (default: the config's)")
     args = ap.parse_args()
-    if args.cta_pairs and args.impl == "ours":
-        from dist_moe_b200 import _native
-
-        _native.lib.dm_set_gemm_pairs(1)
     if args.micro:
         run_micro(args)
     elif args.impl == "reference" and args.workload != "bf16-train":

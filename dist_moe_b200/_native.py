@@ -7,6 +7,7 @@ of this module raises: there is no CPU or eager fallback behind it.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_float, c_int, c_int32, c_int64, c_uint64, c_void_p
 from pathlib import Path
 
@@ -35,6 +36,9 @@ class NativeError(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
+    override = os.environ.get("DIST_MOE_B200_LIB")
+    if override:  # an alternative build of the same library (A/B timing of kernel variants)
+        return ctypes.CDLL(override)
     # build() compares a digest of the sources with the one the library was built from and returns at once when they
     # agree, so a library left over from older sources is never loaded silently.
     from .build import build, find_nvcc
@@ -87,7 +91,6 @@ _SIGNATURES = {
         [c_int, Operand, Operand, _P, _P, Operand, Operand, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64,
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
-    "dm_set_gemm_pairs": (c_int, [c_int]),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
     "dm_blockscaled_wide_enabled": (c_int, []),
     "dm_set_route_decode_kernel": (c_int, [c_int]),

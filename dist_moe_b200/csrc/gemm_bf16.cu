@@ -31,6 +31,8 @@ constexpr int kBK = 64;
 constexpr int kStages = 4;
 constexpr int kGemmThreads = 480;  // TMA warp, MMA warp, eight epilogue warps, four gather warps, one accumulator watcher
 constexpr int kGatherWarps = 4;
+constexpr int kGatherUnitRows = 8;                      // rows one gather warp pulls before it reports
+constexpr int kGatherUnitsPerBlock = 128 / kGatherUnitRows;  // reports that make a 128-row block ready
 constexpr int kMaxGroups = 256;
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;  // 32 KiB
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           const uint64_t t0 = globaltimer_ns();
           for (int b = ready_blocks > (t.row0 >> 7) ? ready_blocks : (t.row0 >> 7); b <= last && ok; ++b) {
             uint32_t spins = 0;
-            while (ld_acquire_gpu(p.gather_flags + b) < kGatherWarps) {
+            while (ld_acquire_gpu(p.gather_flags + b) < kGatherUnitsPerBlock) {
               if ((++spins & 0xff) == 0 && (abort_flag || globaltimer_ns() - t0 > 2000000000ull)) {
                 abort_flag = 1;
                 ok = false;
@@ -427,22 +429,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     }
   } else if (warp >= 10) {
     // ======================= gather (fused dispatch) =======================
-    // Row blocks of 128 rows are dealt round-robin to the CTAs in ascending order, the order in which
-    // the tiles consume them.  Each warp pulls 32 rows with 16-byte loads (peer memory allowed) into
-    // the A operand and then bumps the block's counter; the TMA producer of whichever CTA needs the
-    // block waits for the counter to reach the number of gather warps.  Gather warps wait on nothing.
+    // Units of 8 rows are dealt round-robin over all gather warps of the grid in ascending row order, the order
+    // in which the tiles consume them.  Each warp pulls its unit with 16-byte loads (peer memory allowed), two rows
+    // x eight loads in flight per lane, and then bumps the counter of the unit's 128-row block; the TMA producer of
+    // whichever CTA needs a block waits for sixteen reports.  Gather warps wait on nothing.  Small units matter at
+    // the start of the launch: a warp keeps 8 KiB in flight, so over NVLink a 32-row unit took about 30 us before
+    // the first tiles could begin, an 8-row unit a quarter of that, and later units are far ahead of the MMAs anyway.
     if (kMode != kWgrad && p.gather_flags != nullptr) {
       const int gw = warp - 10;
       const int total_rows = s_off[p.e_local];
       const int nblocks = (total_rows + 127) >> 7;
       const int vec_per_row = p.Kd / 8;
       uint4* dst_base = reinterpret_cast<uint4*>(p.a_base + a_off);
-      // Units of 32 rows are dealt so that consecutive units go to different SMs: the rows the first
-      // tiles need are pulled by many SMs at once.  Two rows x eight 16-byte loads are in flight per lane.
-      for (int u = gw * gridDim.x + blockIdx.x; u < nblocks * 4; u += kGatherWarps * gridDim.x) {
-        const int blk = u >> 2;
-        const int r_begin = blk * 128 + (u & 3) * 32;
-        for (int rr = 0; rr < 32; rr += 2) {
+      for (int u = gw * gridDim.x + blockIdx.x; u < nblocks * kGatherUnitsPerBlock; u += kGatherWarps * gridDim.x) {
+        const int blk = u / kGatherUnitsPerBlock;
+        const int r_begin = blk * 128 + (u % kGatherUnitsPerBlock) * kGatherUnitRows;
+        for (int rr = 0; rr < kGatherUnitRows; rr += 2) {
           const int r0 = r_begin + rr, r1 = r0 + 1;
           if (r0 >= total_rows) break;
           const uint4* src0 = reinterpret_cast<const uint4*>(p.gather_ptrs[r0]);
@@ -608,27 +610,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             }
           }
         } else {
-          for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + c0, r);
+          // 64 columns per trip: a row segment is 128 contiguous bytes, the unit that peer (NVLink) and local
+          // stores move best.  The staging tile holds 16 rows x 128 bytes, so the warp's 32 rows go in two passes.
+          for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + c0, r0);
+            tmem_ld_32x32(taddr + c0 + 32, r1);
             tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
-            __syncwarp();
             const int col = t.n_blk * kBN + c0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = i * 8 + (lane >> 2), j = lane & 3;
-              const uint4 v = stage64_get(stg, rr, j);
-              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
+            for (int pass = 0; pass < 2; ++pass) {
+              if ((lane >> 4) == pass) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  stage_put(stg, lane & 15, j, pack8_bf16(r0 + 8 * j));
+                  stage_put(stg, lane & 15, j + 4, pack8_bf16(r1 + 8 * j));
+                }
+              }
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = i * 4 + (lane >> 3), j = lane & 7;
+                const uint4 v = stage_get(stg, rr, j);
+                const uint64_t rp = __shfl_sync(0xffffffffu, my_row, pass * 16 + rr);
 #ifdef DM_EXP_NOSTORE
-              if (rp == 1 && v.x == 0x12345u)
+                if (rp == 1 && v.x == 0x12345u)
 #else
-              if (rp != 0 && col + 8 * j + 8 <= p.N)
+                if (rp != 0 && col + 8 * j + 8 <= p.N)
 #endif
-                *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
+                  *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
+              }
+              __syncwarp();
             }
-            __syncwarp();
           }
         }
       }
@@ -666,17 +679,6 @@ static int launch(const GemmParams& p, int num_sms, cudaStream_t st) {
 
 using namespace dm;
 
-// Forward and input-gradient GEMMs can run on the paired (cta_group::2) kernel when the shape allows it.
-// Measured on B200 the two kernels are level for large experts (3072 rows per expert: 235 vs 236 us for the
-// W13 forward) and the single-CTA kernel is ahead for small ones (384 rows: 265 vs 306 us), so pairs are opt-in.
-static int g_use_pairs = 0;
-
-extern "C" int dm_set_gemm_pairs(int enabled) {
-  const int previous = g_use_pairs;
-  g_use_pairs = enabled ? 1 : 0;
-  return previous;
-}
-
 static int setup_gather(GemmParams& p, const dm_operand& a, const int64_t* gather_ptrs, int32_t* gather_flags,
                         int64_t max_rows, cudaStream_t st) {
   if (gather_ptrs == nullptr) return kRcOk;
@@ -699,10 +701,6 @@ static int fprop_impl(dm_operand a, const void* w, dm_operand c, dm_operand h2, 
   if (fuse_swiglu && (((N / 2) % (kBN / 2)) != 0 || !h2.base || !c.base || scatter_ptrs)) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
   if (gather_ptrs != nullptr && gather_flags == nullptr) return kRcBadArg;
-  if (g_use_pairs && dm_pair_supported(N, Kd, fuse_swiglu, 0))
-    return dm_pair_launch(a, w, c, h2, scatter_ptrs, gather_ptrs, gather_flags, expert_offsets, e_local, max_rows, N, Kd,
-                          fuse_swiglu, 0, clamped, alpha, limit, cond, num_sms, status,
-                          static_cast<cudaStream_t>(stream));
   GemmParams p{};
   int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
   if (rc != kRcOk) return rc;
@@ -758,10 +756,6 @@ static int dgrad_impl(dm_operand a, const void* w, dm_operand c, const int64_t* 
   if ((Kd % 64) != 0 || (N % 8) != 0) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
   if (gather_ptrs != nullptr && gather_flags == nullptr) return kRcBadArg;
-  if (g_use_pairs && dm_pair_supported(N, Kd, 0, 1))
-    return dm_pair_launch(a, w, c, dm_operand{nullptr, 0, nullptr}, scatter_ptrs, gather_ptrs, gather_flags,
-                          expert_offsets, e_local, max_rows, N, Kd, 0, 1, 0, 1.0f, 0.0f, cond, num_sms, status,
-                          static_cast<cudaStream_t>(stream));
   GemmParams p{};
   int rc = encode_arena(&p.tm_a, a, Kd * 2, max_rows + 256, kBM);
   if (rc != kRcOk) return rc;

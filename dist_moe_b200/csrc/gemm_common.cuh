@@ -199,11 +199,4 @@ static inline int encode_arena_u8(CUtensorMap* tm, const dm_operand& op, int64_t
   return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
 }
 
-// Paired (cta_group::2) forward / input-gradient kernel, defined in gemm_bf16_pair.cu.
-bool dm_pair_supported(int64_t N, int64_t Kd, int fused, int dgrad);
-int dm_pair_launch(const dm_operand& b, const void* w, dm_operand c, dm_operand h2, const int64_t* scatter_ptrs,
-                   const int64_t* gather_ptrs, int32_t* gather_flags, const int32_t* expert_offsets, int e_local,
-                   int64_t max_rows, int64_t N, int64_t Kd, int fused, int dgrad, int clamped, float alpha, float limit,
-                   const int* cond, int num_sms, int* status, cudaStream_t st);
-
 }  // namespace dm

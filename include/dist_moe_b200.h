@@ -251,13 +251,6 @@ int dm_gemm_dgrad_dispatch(const int64_t* gather_ptrs, int32_t* gather_flags, dm
 int dm_gemm_wgrad(dm_operand dy, dm_operand x, void* dw, int out_is_fp32, int accumulate,
                   const int32_t* expert_offsets, int e_local, int64_t max_rows, int64_t N,
                   int64_t Kd, int num_sms, int* status, void* stream);
-/* Kernel selection for dm_gemm_fprop / dm_gemm_dgrad (and their _dispatch forms): non-zero runs shapes with
- * Kd % 128 == 0 and N % 64 == 0 on CTA pairs (tcgen05.mma.cta_group::2, expert weights on the M side, routed
- * rows on the N side in chunks that follow each expert's row count); zero (default) keeps every call on the
- * single-CTA 128 x 256 kernel.  Returns the previous setting.  Results of the two kernels agree to fp32
- * accumulation order.  No counterpart in the reference (it selects kernels through GemmKernelConfig,
- * dist_moe/api.py:233-262). */
-int dm_set_gemm_pairs(int enabled);
 
 
 /* ---------------------------------------------------------------------------

@@ -17,15 +17,6 @@ def _native():
     return _native
 
 
-@pytest.fixture(autouse=True, params=[1, 0], ids=["pairs", "single"])
-def kernel_choice(request):
-    """Every test runs on the CTA-pair kernel and on the single-CTA kernel (the default)."""
-    nat = _native()
-    previous = nat.lib.dm_set_gemm_pairs(request.param)
-    yield request.param
-    nat.lib.dm_set_gemm_pairs(previous)
-
-
 def _close(got, ref, what):
     got = got.float()
     ref = ref.float()

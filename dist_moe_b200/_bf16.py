@@ -19,6 +19,7 @@ from __future__ import annotations
 from typing import Any
 
 import torch
+from torch.profiler import record_function
 
 from . import _native as nat
 from ._execution import ExecutionOptions, RMSNormPostprocess
@@ -73,7 +74,7 @@ class _Call:
     """Per-call device tensors produced by routing and planning."""
 
     __slots__ = ("T", "counts", "per_rank", "offsets", "recv_rows", "fwd", "bwd", "sct", "need", "cond", "fwd_state",
-                 "max_rows", "rstd")
+                 "max_rows", "rstd", "callback_state")
 
 
 def _op(state, t: torch.Tensor | None) -> nat.Operand:
@@ -93,10 +94,11 @@ def _route_and_plan(state, x, ids, scratch_only: bool, validate: bool) -> _Call:
     T, D, K, E = x.shape[0], cfg.hidden_dim, cfg.top_k, cfg.num_experts
     dev, st = x.device, nat.stream_ptr()
     el, ep = state.e_local, state.ep
-    nat.check(nat.lib.dm_publish(x.data_ptr(), ids.data_ptr(), int(ids.dtype == torch.int64),
-                                 state.dispatch.local().data_ptr(), state.routing.local().data_ptr(), T, D, K, E,
-                                 int(validate), state.status.data_ptr(), st), "dm_publish")
-    state.barrier(state.dispatch)
+    with record_function("dist_moe_preprocess"):  # publish ids and rows, then the barrier every peer waits on
+        nat.check(nat.lib.dm_publish(x.data_ptr(), ids.data_ptr(), int(ids.dtype == torch.int64),
+                                     state.dispatch.local().data_ptr(), state.routing.local().data_ptr(), T, D, K, E,
+                                     int(validate), state.status.data_ptr(), st), "dm_publish")
+        state.barrier(state.dispatch)
     c = _Call()
     c.T = T
     size = ep * el * T
@@ -126,6 +128,7 @@ def _route_and_plan(state, x, ids, scratch_only: bool, validate: bool) -> _Call:
                                        state.slot_bytes, state.num_slots, state.num_layers_in_slot,
                                        int(scratch_only), state.status.data_ptr(), st), "dm_plan_fwd_bf16")
     c.rstd = None
+    c.callback_state = None
     state.last_call = c
     return c
 
@@ -149,12 +152,13 @@ def _expert_forward(state, c: _Call, w13, w2, xg_off, h1_off, h2_off, *, fuse: b
                                     status, st, what="gemm_fprop(w2)")
 
 
-def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save_for_backward: bool):
+def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save_for_backward: bool, hooks=None):
     cfg = state.config
     T, D, K, F = x.shape[0], cfg.hidden_dim, cfg.top_k, cfg.intermediate_dim
     st = nat.stream_ptr()
     scratch_only = (not save_for_backward) or cfg.inference or state.num_slots == 0
-    c = _route_and_plan(state, x, ids, scratch_only, options.validate_expert_ids)
+    with record_function("dist_moe_routing"):  # the reference's profiler range names (dist_moe/api.py:1979-2072)
+        c = _route_and_plan(state, x, ids, scratch_only, options.validate_expert_ids)
     fs = c.fwd_state
     if not scratch_only:
         nat.check(nat.lib.dm_cond_copy(x.data_ptr(), None, state.arena.data_ptr(), fs[0:1].data_ptr(), T * D * 2,
@@ -163,8 +167,9 @@ def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save
     if clip is not None:
         clip.zero_()
     fuse = clip is None and F % 128 == 0
-    _expert_forward(state, c, w13, w2, fs[1:2], fs[2:3], fs[3:4], fuse=fuse, cond=None, clip=clip,
-                    clip_limit=options.swiglu_clip_limit)
+    with record_function("dist_moe_forward"):
+        _expert_forward(state, c, w13, w2, fs[1:2], fs[2:3], fs[3:4], fuse=fuse, cond=None, clip=clip,
+                        clip_limit=options.swiglu_clip_limit)
     state.barrier(state.combine)
     out = torch.empty(T, D, dtype=torch.bfloat16, device=x.device)
     post = options.experts_output_postprocess
@@ -173,7 +178,9 @@ def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save
 
         c.rstd = rmsnorm_combine_forward(state, c, post, scores, ids, out, save=not scratch_only)
     elif post is not None:
-        raise NotImplementedError("Python expert-output callbacks are not supported by dist_moe_b200")
+        if hooks is None:
+            raise RuntimeError("a callable expert-output post-process runs on the eager path only")
+        hooks.postprocess_forward(state, c, post, scores, ids, out, save=not scratch_only)
     else:
         nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
                                            int(scores.dtype == torch.bfloat16), ids.data_ptr(),
@@ -185,11 +192,16 @@ def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save
 
 
 def _wgrad_destination(param: torch.Tensor, shape, options: ExecutionOptions, cfg, owner: torch.Tensor | None,
-                       explicit=None):
+                       explicit=None, hooks=None, name: str = ""):
     """Return (tensor, accumulate, returned_to_autograd).
 
     ``explicit`` is used by the registered operators: a tensor to accumulate into, or a dtype for a fresh result.
+    ``hooks`` (eager path) may name the destination through ``wgrad_destination_fn``.
     """
+    if hooks is not None:
+        named = hooks.wgrad_destination(name, shape, cfg.wgrad_dtype or param.dtype, param.device)
+        if named is not None:
+            return named[0], int(named[1]), False
     if isinstance(explicit, torch.Tensor):
         if not explicit.is_contiguous() or explicit.dtype not in (torch.bfloat16, torch.float32) \
                 or explicit.numel() != param.numel():
@@ -217,7 +229,7 @@ def _wgrad_destination(param: torch.Tensor, shape, options: ExecutionOptions, cf
 
 
 def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_param, grad_out,
-                  options: ExecutionOptions, needs, wgrad_explicit=(None, None)):
+                  options: ExecutionOptions, needs, wgrad_explicit=(None, None), hooks=None):
     cfg = state.config
     T, D, K, F, el = c.T, cfg.hidden_dim, cfg.top_k, cfg.intermediate_dim, state.e_local
     dev, st, status = grad_out.device, nat.stream_ptr(), state.status.data_ptr()
@@ -233,7 +245,10 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     arena = state.arena.data_ptr()
     post = options.experts_output_postprocess
     is_norm = isinstance(post, RMSNormPostprocess)
+    is_callback = post is not None and not is_norm  # the callable kept its own input and output (eager path)
     # ---- recompute block (device-predicated on need_recompute) ----------------
+    span = record_function("dist_moe_recompute")
+    span.__enter__()
     nat.check(nat.lib.dm_cond_copy(arena, fs[0:1].data_ptr(), state.dispatch.local().data_ptr(), None, T * D * 2,
                                    cond.data_ptr(), 1, st), "dm_cond_copy(republish x)")
     state.barrier(state.dispatch, cond)
@@ -242,7 +257,7 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     # h2 is always rebuilt from h1: only x_gathered, h1 and h3 are ever saved.
     nat.check(nat.lib.dm_swiglu_fwd(arena, bo[1:2].data_ptr(), arena, bo[2:3].data_ptr(), c.recv_rows.data_ptr(),
                                     c.max_rows, F, clamped, alpha, limit, None, 0.0, None, st), "dm_swiglu_fwd(bwd)")
-    need_h3 = need_scores or is_norm
+    need_h3 = (need_scores or is_norm) and not is_callback
     if need_h3:
         _gemm_fprop(_op(state, bo[2:3]), w2.data_ptr(), _none(), _none(), c.sct.data_ptr(),
                                         c.offsets.data_ptr(), el, c.max_rows, D, F, 0, 0, 1.0, 0.0, cond.data_ptr(),
@@ -250,6 +265,9 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
         nat.check(nat.lib.dm_cond_copy(arena, fs[4:5].data_ptr(), state.combine.local().data_ptr(), None,
                                        T * K * D * 2, cond.data_ptr(), 0, st), "dm_cond_copy(load h3)")
         state.barrier(state.combine, cond)
+    span.__exit__(None, None, None)
+    span = record_function("dist_moe_backward")
+    span.__enter__()
     # ---- grad wrt expert outputs and scores ------------------------------------
     grad_scores = torch.empty(T, K, dtype=torch.float32, device=dev) if need_scores else None
     combine = state.combine.local().data_ptr()
@@ -257,6 +275,8 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
         from ._postprocess import rmsnorm_combine_backward
 
         rmsnorm_combine_backward(state, c, post, grad_out, scores, ids, grad_scores)
+    elif is_callback:
+        hooks.postprocess_backward(state, c, grad_out, scores, ids, grad_scores)
     else:
         nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(),
                                                  int(scores.dtype == torch.bfloat16), ids.data_ptr(),
@@ -277,11 +297,13 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     grad_w13 = grad_w2 = None
     owners = options.wgrad_parameter_owners or (None, None)
     if need_w2:
-        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1])
+        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1], hooks, "w2")
         _gemm_wgrad(_op(state, bo[4:5]), _op(state, bo[2:3]), dst.data_ptr(),
                                         int(dst.dtype == torch.float32), acc, c.offsets.data_ptr(), el, c.max_rows,
                                         D, F, state.num_sms, status, st, what="gemm_wgrad(w2)")
         grad_w2 = dst.view(w2_param.shape) if ret else None
+        if hooks is not None:
+            grad_w2 = hooks.wgrad_postprocess("w2", grad_w2)
     # ---- SwiGLU backward, W13 input gradient (scattered to the owners) and weight gradient
     nat.check(nat.lib.dm_swiglu_bwd(arena, bo[1:2].data_ptr(), arena, bo[3:4].data_ptr(), arena, bo[5:6].data_ptr(),
                                     c.recv_rows.data_ptr(), c.max_rows, F, clamped, alpha, limit, st),
@@ -291,11 +313,14 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
                                         c.offsets.data_ptr(), el, c.max_rows, D, 2 * F, None, state.num_sms, status,
                                         st, what="gemm_dgrad(w13)")
     if need_w13:
-        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0])
+        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0], hooks,
+                                           "w13")
         _gemm_wgrad(_op(state, bo[5:6]), _op(state, bo[0:1]), dst.data_ptr(),
                                         int(dst.dtype == torch.float32), acc, c.offsets.data_ptr(), el, c.max_rows,
                                         2 * F, D, state.num_sms, status, st, what="gemm_wgrad(w13)")
         grad_w13 = dst.view(w13_param.shape) if ret else None
+        if hooks is not None:
+            grad_w13 = hooks.wgrad_postprocess("w13", grad_w13)
     grad_x = None
     # The closing barrier is unconditional (dist_moe/api.py:2580): peers may still be pulling grad_h3 out of this
     # rank's combine buffer, and the next call on this context overwrites it.
@@ -307,6 +332,7 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
                                            None, 0, st), "dm_scale_and_sum(reduce_from_topk)")
     if grad_scores is not None and scores.dtype != torch.float32:
         grad_scores = grad_scores.to(scores.dtype)
+    span.__exit__(None, None, None)
     return grad_x, grad_scores, grad_w13, grad_w2
 
 
@@ -335,13 +361,89 @@ class _Bf16Function(torch.autograd.Function):
         return gx, None, gs, gw13, gw2, None, None
 
 
+def _rmsnorm_args(post):
+    """The RMSNorm arguments of the registered operators (weight, enabled, eps, norm dtype, output dtype, bitwise,
+    gain centre, Kahan, recompute rstd); disabled values when there is no RMSNorm post-process."""
+    if isinstance(post, RMSNormPostprocess):
+        return (post.weight, True, float(post.eps), post.norm_output_dtype, post.output_dtype, bool(post.require_bitwise),
+                float(post.gain_center), bool(post.use_kahan), bool(post.recompute_rstd))
+    return (None, False, 1e-6, torch.float32, torch.bfloat16, False, 0.0, False, False)
+
+
+class _RegisteredBf16Function(torch.autograd.Function):
+    """Training call through the registered operators ``dist_moe::bf16_forward`` (``..._with_clip_stats``) and
+    ``dist_moe::bf16_backward`` / ``bf16_backward_accumulate_`` (dist_moe/api.py:4027-4042 applies its
+    ``_RegisteredBf16Autograd`` the same way), so that FakeTensor propagation, ``make_fx`` and ``torch.compile`` of
+    the caller's code see operator nodes with the reference's names and schemas."""
+
+    @staticmethod
+    def forward(ctx, x, ids, scores, w13_param, w2_param, context, options):
+        state = context._state
+        rms = _rmsnorm_args(options.experts_output_postprocess)
+        head = (x.detach().contiguous(), ids, scores.detach(), w13_param.detach(), w2_param.detach(), *rms,
+                state.slot_selector, state.num_layers_in_slot, bool(options.validate_expert_ids))
+        clip = options.swiglu_clip_stats_out_3
+        if clip is None:
+            out, st = torch.ops.dist_moe.bf16_forward(*head, context._context_id)
+        else:
+            out, st, counters = torch.ops.dist_moe.bf16_forward_with_clip_stats(*head, float(options.swiglu_clip_limit),
+                                                                                  context._context_id)
+            clip.copy_(counters)  # graph-visible copy into the caller's tensor
+        ctx.context, ctx.options, ctx.n_state = context, options, len(st)
+        ctx.save_for_backward(ids, scores, w13_param, w2_param, *st)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import _ops
+
+        ids, scores, w13_param, w2_param, *st = ctx.saved_tensors
+        context, options = ctx.context, ctx.options
+        cfg = context.config
+        rms = _rmsnorm_args(options.experts_output_postprocess)
+        tail = (rms[1], rms[2], rms[3], rms[4], rms[5], rms[7], rms[8])
+        needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
+        e_local = context._state.e_local
+        D, F = cfg.hidden_dim, cfg.intermediate_dim
+        _ops.NEEDS_HINT.append(needs)
+        try:
+            if options.inplace_wgrad_accum:
+                owners = options.wgrad_parameter_owners or (None, None)
+                acc13, _, _ = _wgrad_destination(w13_param, (e_local, 2 * F, D), options, cfg, owners[0])
+                acc2, _, _ = _wgrad_destination(w2_param, (e_local, D, F), options, cfg, owners[1])
+                gx, gs = torch.ops.dist_moe.bf16_backward_accumulate_(
+                    grad_out.contiguous(), w13_param.detach(), w2_param.detach(), acc13, acc2, ids, scores.detach(), st,
+                    *tail, acc13.dtype, context._context_id)
+                g13 = g2 = None
+            else:
+                dtype = cfg.wgrad_dtype or w13_param.dtype
+                gx, gs, g13, g2 = torch.ops.dist_moe.bf16_backward(
+                    grad_out.contiguous(), w13_param.detach(), w2_param.detach(), ids, scores.detach(), st, *tail, dtype,
+                    context._context_id)
+        finally:
+            _ops.NEEDS_HINT.clear()
+        if gs is not None and needs[1] and gs.dtype != scores.dtype:
+            gs = gs.to(scores.dtype)
+        return (gx if needs[0] else None, None, gs if needs[1] else None, g13 if needs[2] else None,
+                g2 if needs[3] else None, None, None)
+
+
+def _registered_ops_are_ours() -> bool:
+    from . import _ops
+
+    return "bf16_forward" in _ops.REGISTERED
+
+
 def run_bf16(x, ids, scores, w13_weight, w2_weight, w13_EFD, w2_EDF, context: Any, options: ExecutionOptions, *,
              save_for_backward: bool) -> torch.Tensor:
     state = context._state
-    if options.weights_preprocess_fn is not None or options.wgrad_postprocess_fn is not None \
-            or options.wgrad_destination_fn is not None:
-        raise NotImplementedError("Python weight/WGRAD callbacks are not supported by dist_moe_b200")
+    if options.requires_eager:
+        from ._eager import run_bf16_eager
+
+        return run_bf16_eager(x, ids, scores, w13_weight, w2_weight, context, options, save_for_backward=save_for_backward)
     if save_for_backward:
+        if _registered_ops_are_ours():
+            return _RegisteredBf16Function.apply(x, ids, scores, w13_weight, w2_weight, context, options)
         return _Bf16Function.apply(x, ids, scores, w13_weight, w2_weight, state, options)
     out, _ = forward_impl(state, x.detach(), ids, scores.detach(), w13_EFD.detach(), w2_EDF.detach(), options, False)
     return out

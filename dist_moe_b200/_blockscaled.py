@@ -36,6 +36,7 @@ from __future__ import annotations
 from typing import Any
 
 import torch
+from torch.profiler import record_function
 
 from . import _native as nat
 from ._execution import ExecutionOptions, PreparedWeight, RMSNormPostprocess
@@ -602,8 +603,9 @@ class _Mxfp8Function(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, ids, scores, w13_param, w2_param, state, options, p13, p2):
         p13, p2 = _training_weights(w13_param, w2_param, p13, p2, state.config)
-        out, call = _mxfp8_forward(state, x.detach().contiguous(), ids, scores.detach(), p13, p2, options,
-                                   need_h3=scores.requires_grad)
+        with record_function("dist_moe_forward"):
+            out, call = _mxfp8_forward(state, x.detach().contiguous(), ids, scores.detach(), p13, p2, options,
+                                       need_h3=scores.requires_grad)
         ctx.state, ctx.call, ctx.options, ctx.x_shape = state, call, options, x.shape
         ctx.save_for_backward(ids, scores, w13_param, w2_param)
         return out
@@ -612,7 +614,7 @@ class _Mxfp8Function(torch.autograd.Function):
     def backward(ctx, grad_out):
         ids, scores, w13_param, w2_param = ctx.saved_tensors
         needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
-        with torch.cuda.device(ctx.state.device):
+        with torch.cuda.device(ctx.state.device), record_function("dist_moe_backward"):
             gx, gs, gw13, gw2 = _mxfp8_backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param,
                                                 w2_param, grad_out.contiguous(), ctx.options, needs)
         return gx, None, gs, gw13, gw2, None, None, None, None

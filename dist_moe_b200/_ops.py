@@ -54,8 +54,21 @@ def _select_slot(state, activation_slot_id_1: torch.Tensor, num_moe_layers_in_sl
 # ---------------------------------------------------------------------------------------------
 # BF16
 # ---------------------------------------------------------------------------------------------
+# Eager calls hand the forward's per-call record to the matching backward through this table (keyed by the address
+# of the call's planner-state tensor), so the backward does not rebuild offsets and predicates with extra launches.
+# A backward that finds no entry (a traced graph replayed later, another process) rebuilds them from the state list.
+_LIVE_CALLS: dict[int, object] = {}
+_LIVE_CALLS_MAX = 256
+# Which of (x, scores, w13, w2) need gradients in the backward about to run; set by the autograd function that
+# dispatches to the operator, consumed once.  Absent means all four.
+NEEDS_HINT: list = []
+
+
 def _pack_bf16_state(call, device) -> list[torch.Tensor]:
     rstd = call.rstd if call.rstd is not None else torch.empty(0, dtype=torch.float32, device=device)
+    if len(_LIVE_CALLS) >= _LIVE_CALLS_MAX:
+        _LIVE_CALLS.pop(next(iter(_LIVE_CALLS)))
+    _LIVE_CALLS[call.fwd_state.data_ptr()] = call
     return [call.counts, call.bwd, call.fwd, call.sct, call.per_rank, call.recv_rows.clone(), call.need,
             call.fwd_state, rstd]
 
@@ -65,6 +78,11 @@ def _unpack_bf16_state(state, tensors, T: int):
 
     if len(tensors) != 9:
         raise RuntimeError(f"BF16 backward received {len(tensors)} state tensors")
+    live = _LIVE_CALLS.pop(tensors[7].data_ptr(), None)
+    if live is not None and live.T == T and live.fwd.data_ptr() == tensors[2].data_ptr():
+        rstd = tensors[8]
+        live.rstd = rstd if rstd.numel() else None
+        return live
     c = _Call()
     c.counts, c.bwd, c.fwd, c.sct, c.per_rank, recv, c.need, c.fwd_state, rstd = tensors
     c.T = T
@@ -102,6 +120,11 @@ def _fake_bf16_state(x, ids, context_id, rmsnorm_enabled):
             x.new_empty(P, dtype=i64), x.new_empty(state.ep, dtype=i32), x.new_empty(1, dtype=i32),
             x.new_empty(1, dtype=torch.uint8), x.new_empty(6, dtype=i64),
             x.new_empty((T, K) if rmsnorm_enabled else (0,), dtype=torch.float32)]
+
+
+def _or_empty(t, like):
+    """An operator output cannot be None: a gradient that was not asked for comes back as an (unused) empty-like."""
+    return t if t is not None else torch.empty_like(like)
 
 
 def _register_bf16() -> None:
@@ -161,8 +184,9 @@ def _register_bf16() -> None:
         w13v = w13.reshape(state.e_local, 2 * cfg.intermediate_dim, cfg.hidden_dim)
         w2v = w2.reshape(state.e_local, cfg.hidden_dim, cfg.intermediate_dim)
         options = ExecutionOptions(experts_output_postprocess=post)
+        needs = NEEDS_HINT.pop() if NEEDS_HINT else (True, True, True, True)
         return backward_impl(state, c, grad_out.shape, ids, scores, w13v, w2v, w13, w2, grad_out.contiguous(), options,
-                             (True, True, True, True), wgrad_explicit=explicit)
+                             needs, wgrad_explicit=explicit)
 
     @torch.library.custom_op(f"{_NS}::bf16_backward", mutates_args=(), device_types="cuda")
     def bf16_backward(grad_output_TD: torch.Tensor, w13_EFD: torch.Tensor, w2_EDF: torch.Tensor,
@@ -176,7 +200,8 @@ def _register_bf16() -> None:
                         rmsnorm_require_bitwise, 0.0, rmsnorm_use_kahan, rmsnorm_recompute_rstd)
         gx, gs, g13, g2 = run_backward(grad_output_TD, w13_EFD, w2_EDF, topk_expert_ids_TK, topk_scores_TK,
                                        state_tensors, post, context_id, (wgrad_output_dtype, wgrad_output_dtype))
-        return gx, gs, g13.reshape(w13_EFD.shape), g2.reshape(w2_EDF.shape)
+        return (_or_empty(gx, grad_output_TD), _or_empty(gs, topk_scores_TK),
+                _or_empty(g13, w13_EFD).reshape(w13_EFD.shape), _or_empty(g2, w2_EDF).reshape(w2_EDF.shape))
 
     @bf16_backward.register_fake
     def _(grad_output_TD, w13_EFD, w2_EDF, topk_expert_ids_TK, topk_scores_TK, state_tensors, rmsnorm_enabled,
@@ -198,7 +223,7 @@ def _register_bf16() -> None:
                         rmsnorm_require_bitwise, 0.0, rmsnorm_use_kahan, rmsnorm_recompute_rstd)
         gx, gs, _, _ = run_backward(grad_output_TD, w13_EFD, w2_EDF, topk_expert_ids_TK, topk_scores_TK, state_tensors,
                                     post, context_id, (accumulator_grad_w13_EFD, accumulator_grad_w2_EDF))
-        return gx, gs
+        return _or_empty(gx, grad_output_TD), _or_empty(gs, topk_scores_TK)
 
     @bf16_backward_accumulate_.register_fake
     def _(grad_output_TD, w13_EFD, w2_EDF, accumulator_grad_w13_EFD, accumulator_grad_w2_EDF, topk_expert_ids_TK,

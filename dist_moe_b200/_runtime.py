@@ -14,6 +14,7 @@ rendezvous; all traffic is issued by this library's own kernels.
 
 from __future__ import annotations
 
+import dataclasses
 import os
 from typing import Any
 
@@ -21,6 +22,30 @@ import torch
 
 from . import _native as nat
 from .formats import BlockScaledFormat, format_constants
+
+
+@dataclasses.dataclass
+class ScratchInfo:
+    """Peak use of the shared scratch region and of every activation slot since the last ``reset``
+    (dist_moe/_activation_buffer.py:179-207 ``ScratchInfo``; the per-slot list is this library's addition)."""
+
+    scratch_min_free: float      # smallest free byte count seen; negative = overflow by that many bytes
+    scratch_size: float
+    scratch_max_used: float
+    device_scratch_size: float
+    device_scratch_used: float
+    host_scratch_size: float | None
+    host_scratch_used: float | None
+    slot_max_used: list
+
+
+@dataclasses.dataclass
+class PendingOverflowCheck:
+    """A device-to-host copy of the planner's peak counters in flight (dist_moe/_activation_buffer.py:210-221)."""
+
+    host_peaks: torch.Tensor
+    ready: Any
+
 
 ROUTING_HEADER_BYTES = 128
 GUARD_ROWS = 256
@@ -139,6 +164,40 @@ class ContextState:
             raise RuntimeError(
                 f"dist_moe_b200 device contract violation: {nat.STATUS_NAMES.get(words[0], words[0])} "
                 f"(details {words[1:4]})")
+
+    # ---- peak-usage metrics (dist_moe/_activation_buffer.py:690-800) --------------------
+    def _scratch_info(self, peaks: list) -> ScratchInfo:
+        n = self.num_slots
+        scratch_size = float(self.arena_bytes - n * self.slot_bytes)
+        min_free = float(peaks[n])
+        slots = [float(self.slot_bytes - peaks[i]) for i in range(n)]
+        overflow = min_free < 0 or any(peaks[i] < 0 for i in range(n))
+        info = ScratchInfo(scratch_min_free=min_free, scratch_size=scratch_size, scratch_max_used=scratch_size - min_free,
+                           device_scratch_size=scratch_size, device_scratch_used=scratch_size - min_free,
+                           host_scratch_size=None, host_scratch_used=None, slot_max_used=slots)
+        if overflow:
+            raise RuntimeError(f"dist_moe_b200 activation buffer overflow: {info}")
+        return info
+
+    def check_overflow(self) -> ScratchInfo:
+        """Blocking read of the planner's peak counters; raises if a slot or the scratch region overflowed."""
+        return self._scratch_info(self.peak_min_free.tolist())
+
+    def begin_check_overflow(self) -> PendingOverflowCheck:
+        """Start the device-to-host copy of the counters on the current stream without draining the GPU."""
+        staging = getattr(self, "_overflow_staging", None)
+        if staging is None:
+            staging = torch.empty_like(self.peak_min_free, device="cpu", pin_memory=True)
+            self._overflow_staging = staging
+        with torch.cuda.device(self.device):
+            staging.copy_(self.peak_min_free, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record()
+        return PendingOverflowCheck(host_peaks=staging, ready=ready)
+
+    def finish_check_overflow(self, pending: PendingOverflowCheck) -> ScratchInfo:
+        pending.ready.synchronize()
+        return self._scratch_info(pending.host_peaks.tolist())
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)

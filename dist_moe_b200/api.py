@@ -478,6 +478,17 @@ class Context:
         """
         self._state.check_status()
 
+    def check_overflow(self):
+        """Peak scratch / slot usage since the last ``reset`` (blocking); raises on overflow.  The asynchronous pair
+        is ``begin_check_overflow`` / ``finish_check_overflow`` (dist_moe/_activation_buffer.py:690-760)."""
+        return self._state.check_overflow()
+
+    def begin_check_overflow(self):
+        return self._state.begin_check_overflow()
+
+    def finish_check_overflow(self, pending):
+        return self._state.finish_check_overflow(pending)
+
     def close(self) -> None:
         with _CONTEXT_LOCK:
             _CONTEXTS.pop(self._context_id, None)
@@ -591,8 +602,14 @@ def routed_experts(x_TD: torch.Tensor, topk_expert_ids_TK: torch.Tensor, topk_sc
     state = context._state
     src13 = w13_weight.source if prepared else w13_weight
     src2 = w2_weight.source if prepared else w2_weight
-    w13_EFD, w2_EDF = _reshape_weights(src13, src2, state.e_local, context.config)
-    if options.weights_preprocess_fn is None:
+    if options.weights_preprocess_fn is not None:
+        if prepared:
+            raise ValueError("prepared weights cannot be combined with weights_preprocess_fn")
+        # compact source weights: the callback produces the BF16 compute weights (shape-checked there)
+        w13_EFD, w2_EDF = src13, src2
+        _validate_inputs(x_TD, topk_expert_ids_TK, topk_scores_TK, None, None, context, prepared=True)
+    else:
+        w13_EFD, w2_EDF = _reshape_weights(src13, src2, state.e_local, context.config)
         _validate_inputs(x_TD, topk_expert_ids_TK, topk_scores_TK, w13_EFD, w2_EDF, context, prepared=prepared)
     if x_TD.device != state.device:
         raise ValueError(f"x_TD is on {x_TD.device} but the context was created on {state.device}")

@@ -254,6 +254,35 @@ extern "C" int dm_swiglu_bwd(const void* h1_base, const int64_t* h1_offset, cons
   return static_cast<int>(cudaGetLastError());
 }
 
+// Rows of a [T, K, D] route tensor whose expert id is negative are set to zero (one warp per route), so that Python
+// callbacks never see the stale bytes a dropped route leaves in the communication buffer
+// (dist_moe/kernels/triton/conditional_copy.py:215-235 `zero_out_padded_rows_`).
+template <typename IdT>
+__global__ void zero_padded_rows_kernel(uint4* __restrict__ rows, const IdT* __restrict__ ids, int64_t routes, int vec) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < routes; r += warps) {
+    if (static_cast<int64_t>(ids[r]) >= 0) continue;
+    uint4* row = rows + r * vec;
+    for (int v = lane; v < vec; v += 32) row[v] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+extern "C" int dm_zero_padded_rows(void* routes_TKD, const void* ids, int ids_are_int64, int64_t T, int K, int64_t D,
+                                   void* stream) {
+  if (!routes_TKD || !ids || T <= 0 || K <= 0 || D <= 0 || (D % 8) != 0) return kRcBadArg;
+  const int64_t routes = T * K;
+  const int blocks = grid_for(routes * 32, 256, grid_cap(16));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ids_are_int64)
+    zero_padded_rows_kernel<int64_t><<<blocks, 256, 0, st>>>(static_cast<uint4*>(routes_TKD),
+                                                             static_cast<const int64_t*>(ids), routes, static_cast<int>(D / 8));
+  else
+    zero_padded_rows_kernel<int32_t><<<blocks, 256, 0, st>>>(static_cast<uint4*>(routes_TKD),
+                                                             static_cast<const int32_t*>(ids), routes, static_cast<int>(D / 8));
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int dm_scale_and_sum(const void* h3, const void* scores, int scores_are_bf16, const void* ids,
                                 int ids_are_int64, void* out, int64_t T, int K, int64_t D, void* save_base,
                                 const int64_t* save_offset, const int* save_cond, int save_expect, void* stream) {

@@ -210,13 +210,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           if (ok) {
             uint8_t* sa = smem + stage * kStageBytes;
             uint8_t* sb = sa + kABytes;
-#ifdef DM_EXP_NOLOAD
-            if (kMode != kWgrad || wgrad_part == 0) mbar_arrive(&full_bar[stage]);
-            if (false) {
-#else
             if (kMode != kWgrad || wgrad_part == 0) mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
             if (kMode == kWgrad) {
-#endif
               const int row = t.row0 + kb * kBK;
               if (wgrad_part == 0) {
 #pragma unroll
@@ -228,11 +223,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                 for (int b = b0; b < b0 + 2; ++b)
                   tma_load_3d(sb + b * 8192, &p.tm_b, 0, b_line0 + t.n_blk * (kBN / 64) + b, row, &full_bar[stage]);
               }
-#ifdef DM_EXP_NOLOAD
-            } else if (false) {
-#else
             } else {
-#endif
               tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
               if (kMode == kFprop) {
                 int r0, r1;
@@ -350,14 +341,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           if (!ok) break;
           const uint32_t a_lo = a_lo0 + st * (kStageBytes >> 4), b_lo = b_lo0 + st * (kStageBytes >> 4);
           const int ksteps = (kMode == kWgrad && kb == t.k_iters - 1) ? (valid_last + 15) >> 4 : kBK / 16;
-#ifndef DM_EXP_NOMMA
           umma_bf16_lo(d_tmem, a_lo, b_lo, kDescHi, idesc, kb > 0 ? 1u : 0u);
           if (ksteps > 1) umma_bf16_lo(d_tmem, a_lo + a_step, b_lo + b_step, kDescHi, idesc, 1u);
           if (ksteps > 2) umma_bf16_lo(d_tmem, a_lo + 2 * a_step, b_lo + 2 * b_step, kDescHi, idesc, 1u);
           if (ksteps > 3) umma_bf16_lo(d_tmem, a_lo + 3 * a_step, b_lo + 3 * b_step, kDescHi, idesc, 1u);
-#else
-          (void)a_lo; (void)b_lo; (void)ksteps;
-#endif
           tcgen05_commit_addr(empty0 + st * 8);
           if (++st == kStages) {
             st = 0;
@@ -501,11 +488,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;
-#ifdef DM_EXP_NOEPI
-      if (false) {
-      } else if (kMode != kWgrad) {
-      } else
-#endif
       if (kMode == kWgrad) {
         for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
           uint32_t r[32];
@@ -599,11 +581,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                 const int rr = i * 8 + (lane >> 2), j = lane & 3;
                 const uint4 v = stage64_get(stg, rr, j);
                 const uint64_t rp = __shfl_sync(0xffffffffu, base, rr);
-#ifdef DM_EXP_NOSTORE
-                if (rp == 1 && v.x == 0x12345u)
-#else
                 if (rp != 0 && col + 8 * j + 8 <= F)
-#endif
                   *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col_out + 8 * j) * 2) = v;
               }
               __syncwarp();
@@ -633,11 +611,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                 const int rr = i * 4 + (lane >> 3), j = lane & 7;
                 const uint4 v = stage_get(stg, rr, j);
                 const uint64_t rp = __shfl_sync(0xffffffffu, my_row, pass * 16 + rr);
-#ifdef DM_EXP_NOSTORE
-                if (rp == 1 && v.x == 0x12345u)
-#else
                 if (rp != 0 && col + 8 * j + 8 <= p.N)
-#endif
                   *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
               }
               __syncwarp();

@@ -70,6 +70,47 @@ def run_case(dm, group, rank, world, dev, T, D, F, K, E, quickstart, slot_factor
         ctx.close()
 
 
+def run_two_layers_first_input_without_grad(dm, group, rank, world, dev, T, D, F, K, E):
+    """Two layers share one context (two layers per activation slot, saved path).  The first layer's input does
+    not require a gradient, so its backward stops after the weight gradients; it still has to end with the group's
+    barrier, because peers are pulling its output gradients out of this rank's combine buffer when the next call
+    (here the second repetition's forward) overwrites that buffer.  Gradients of both layers match the oracle."""
+    xs, ids, scores, w13, w2 = inputs(world, T, D, F, K, E, False)
+    el = E // world
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=2, activation_slot_capacity_factor=1.0,
+                    device_scratch_capacity_factor=float(world))
+    ctx = dm.create_context(group=group, config=cfg, device=dev)
+    try:
+        sr = [s.clone().requires_grad_(True) for s in scores]
+        a = w13.clone().requires_grad_(True)
+        b = w2.clone().requires_grad_(True)
+        refs = []
+        for r in range(world):
+            h = oracle_moe.moe_forward(xs[r], ids[r], sr[r], a, b)          # layer 1: x is a plain input
+            refs.append(oracle_moe.moe_forward(h, ids[r], sr[r], a, b))     # layer 2 on layer 1's output
+        sum(o.float().sum() for o in refs).backward()
+        for attempt in range(2):
+            ctx.reset()
+            ctx.select_activation_slot(0, 2)
+            x = xs[rank].to(dev)                                            # requires_grad stays False
+            s = scores[rank].to(dev).requires_grad_(True)
+            wa = w13[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
+            wb = w2[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
+            i = ids[rank].to(dev)
+            h = dm.routed_experts(x, i, s, wa, wb, ctx)
+            out = dm.routed_experts(h, i, s, wa, wb, ctx)
+            out.float().sum().backward()
+            ctx.check_status()
+            tag = f"rank {rank} two layers #{attempt}"
+            assert_close(out, refs[rank], what=f"{tag} output", **BF16_FWD)
+            assert_close(s.grad, sr[rank].grad, what=f"{tag} grad scores", **BF16_GRAD)
+            assert_close(wa.grad, a.grad[rank * el:(rank + 1) * el], what=f"{tag} grad w13", **BF16_WGRAD)
+            assert_close(wb.grad, b.grad[rank * el:(rank + 1) * el], what=f"{tag} grad w2", **BF16_WGRAD)
+    finally:
+        ctx.close()
+
+
 def run_block_scaled_case(dm, group, rank, world, dev, fmt, T, D, F, K, E):
     """Inference forward with prepared block-scaled weights across ranks (packed dispatch rows travel over
     NVLink); bounds are the reference's relative-L2 / cosine limits for the format."""
@@ -150,6 +191,7 @@ def main():
     run_case(dm, group, rank, world, dev, 16, 256, 256, 2, 4 * world, True, None)    # quick-start layer, recompute
     run_case(dm, group, rank, world, dev, 128, 1024, 1024, 2, 2 * world, False, 1.0)  # reference's two-rank shape, saved
     run_case(dm, group, rank, world, dev, 300, 512, 384, 4, 8 * world, False, 1.0)
+    run_two_layers_first_input_without_grad(dm, group, rank, world, dev, 96, 256, 256, 2, 4 * world)
     run_block_scaled_case(dm, group, rank, world, dev, "MXFP8_E4M3", 200, 512, 256, 4, 4 * world)
     run_block_scaled_case(dm, group, rank, world, dev, "NVFP4", 130, 512, 256, 2, 4 * world)
     run_mxfp8_training_case(dm, group, rank, world, dev, 512, 1024, 1024, 2, 2 * world)

@@ -228,6 +228,11 @@ def _workspace(state):
     return ws
 
 
+# Inference calls whose experts receive at most this many rows on average take the swapped-operand GEMMs (rows on
+# the MMA's N side in steps of 32); above it a 128-row tile is mostly real rows and the 128 x 256 kernel wins.
+SWAPPED_MAX_ROWS_PER_EXPERT = 48
+
+
 def _wide_tiles_selected() -> bool:
     """Whether the block-scaled GEMMs run on 128x256 tiles (the only ones with the quantising SwiGLU epilogue)."""
     return bool(nat.lib.dm_blockscaled_wide_enabled())
@@ -300,11 +305,13 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     fwd = torch.empty(size, dtype=torch.int64, device=dev)
     sct = torch.empty(size, dtype=torch.int64, device=dev)
     max_rows = min(size, state.capacity_rows)
-    nat.check(nat.lib.dm_route(state.routing.peer_ptrs.data_ptr(), state.dispatch.peer_ptrs.data_ptr(),
-                               state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride, D * 2, 128,
-                               state.capacity_rows, size, counts.data_ptr(), per_rank.data_ptr(), offsets.data_ptr(),
-                               fwd.data_ptr(), None, sct.data_ptr(), state.route_workspace.data_ptr(),
-                               state.route_workspace_words, status, st), nat.route_call_name(ep, T, el))
+    real = torch.empty(el, dtype=torch.int32, device=dev)  # rows per expert before the padding to 128
+    nat.check(nat.lib.dm_route_counted(state.routing.peer_ptrs.data_ptr(), state.dispatch.peer_ptrs.data_ptr(),
+                                       state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride,
+                                       D * 2, 128, state.capacity_rows, size, counts.data_ptr(), real.data_ptr(),
+                                       per_rank.data_ptr(), offsets.data_ptr(), fwd.data_ptr(), None, sct.data_ptr(),
+                                       state.route_workspace.data_ptr(), state.route_workspace_words, status, st),
+              nat.route_call_name(ep, T, el))
     recv = offsets[el:]
     # ---- gather + unpack -----------------------------------------------------------------------
     none = nat.Operand(None, 0, None)
@@ -316,7 +323,18 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     fused = bool(p13._interleaved_fc13)
     row_inv = _view(buf, lay.x_inv) if lay.fp4 else none
     h2_quantised = False
-    if fused and not lay.fp4 and _wide_tiles_selected():
+    # few rows per expert (decode): weights on the MMA's M side, the rows on its N side
+    swapped = fused and ep * T * K <= SWAPPED_MAX_ROWS_PER_EXPERT * E
+    if swapped:
+        h2_dense = lay.dense
+        nat.check(nat.lib.dm_gemm_blockscaled_swapped(f, _view(buf, lay.x_q), _view(buf, lay.x_sf),
+                                                      p13.fprop_data.data_ptr(), p13.fprop_scale.data_ptr(), none,
+                                                      _view(buf, h2_dense), None, row_inv,
+                                                      nat.ptr(p13.global_scale_inv), offsets.data_ptr(),
+                                                      real.data_ptr(), el, max_rows, 2 * F, D, 1, clamped, alpha,
+                                                      limit, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled_swapped(w13+swiglu)")
+    elif fused and not lay.fp4 and _wide_tiles_selected():
         # MXFP8: the SwiGLU epilogue writes h2 already row-quantised, the operand of the W2 GEMM
         h2_dense = lay.dense
         h2_quantised = True
@@ -356,11 +374,20 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
         nat.check(nat.lib.dm_quant_mxfp8_row(h2_ptr, recv.data_ptr(), max_rows, F, buf.data_ptr() + lay.h_q, 0,
                                              buf.data_ptr() + lay.h_sf, 0, 1, st), "dm_quant_mxfp8_row(h2)")
     # ---- W2 + scatter to the owners' combine buffers ---------------------------------------------
-    nat.check(nat.lib.dm_gemm_blockscaled(f, _view(buf, lay.h_q), _view(buf, lay.h_sf), p2.fprop_data.data_ptr(),
-                                          p2.fprop_scale.data_ptr(), none, none, sct.data_ptr(),
-                                          _view(buf, lay.h_inv) if lay.fp4 else none, nat.ptr(p2.global_scale_inv),
-                                          offsets.data_ptr(), el, max_rows, D, F, 0, 0, 1.0, 0.0, None, state.num_sms,
-                                          status, st), "dm_gemm_blockscaled(w2)")
+    if swapped:
+        nat.check(nat.lib.dm_gemm_blockscaled_swapped(f, _view(buf, lay.h_q), _view(buf, lay.h_sf),
+                                                      p2.fprop_data.data_ptr(), p2.fprop_scale.data_ptr(), none, none,
+                                                      sct.data_ptr(), _view(buf, lay.h_inv) if lay.fp4 else none,
+                                                      nat.ptr(p2.global_scale_inv), offsets.data_ptr(),
+                                                      real.data_ptr(), el, max_rows, D, F, 0, 0, 1.0, 0.0, None,
+                                                      state.num_sms, status, st), "dm_gemm_blockscaled_swapped(w2)")
+    else:
+        nat.check(nat.lib.dm_gemm_blockscaled(f, _view(buf, lay.h_q), _view(buf, lay.h_sf), p2.fprop_data.data_ptr(),
+                                              p2.fprop_scale.data_ptr(), none, none, sct.data_ptr(),
+                                              _view(buf, lay.h_inv) if lay.fp4 else none,
+                                              nat.ptr(p2.global_scale_inv), offsets.data_ptr(), el, max_rows, D, F, 0,
+                                              0, 1.0, 0.0, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled(w2)")
     state.barrier(state.combine)
     out = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
     post = options.experts_output_postprocess

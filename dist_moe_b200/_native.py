@@ -69,6 +69,12 @@ _SIGNATURES = {
         + [_P] * 7
         + [c_int64, _P, _P],
     ),
+    "dm_route_counted": (
+        c_int,
+        [_P, _P, _P, c_int, c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int64, c_int64]
+        + [_P] * 8
+        + [c_int64, _P, _P],
+    ),
     "dm_route_static": (
         c_int,
         [_P, _P, _P, c_int, c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int64, c_int64]
@@ -90,6 +96,11 @@ _SIGNATURES = {
     "dm_gemm_blockscaled": (
         c_int,
         [c_int, Operand, Operand, _P, _P, Operand, Operand, _P, Operand, _P, _P, c_int, c_int64, c_int64, c_int64,
+         c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
+    ),
+    "dm_gemm_blockscaled_swapped": (
+        c_int,
+        [c_int, Operand, Operand, _P, _P, Operand, Operand, _P, Operand, _P, _P, _P, c_int, c_int64, c_int64, c_int64,
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
     "dm_set_blockscaled_wide": (c_int, [c_int]),
@@ -153,7 +164,7 @@ for _name, (_res, _args) in _SIGNATURES.items():
 
 # Kernel launches issued through this binding (benchmarks report the count).
 LAUNCHES = [0]
-_LAUNCHES_PER_CALL = {"dm_route": 3}
+_LAUNCHES_PER_CALL = {"dm_route": 3, "dm_route_counted": 3}
 
 
 def route_call_name(ep: int, tokens: int, e_local: int) -> str:

@@ -94,6 +94,7 @@ struct RouteParams {
   int m_mult;
   int64_t capacity_rows, ptrs_size;
   int32_t* counts;
+  int32_t* real_counts;  // optional: rows per expert before padding
   int32_t* per_rank;
   int32_t* expert_offsets;
   int64_t* fwd;
@@ -196,6 +197,7 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(RouteParams p) {
   for (int el = threadIdx.x; el <= p.e_local; el += blockDim.x) {
     p.expert_offsets[el] = bad ? 0 : base[el];
     if (el < p.e_local) p.counts[el] = bad ? 0 : pad_rows(total[el], p.m_mult);
+    if (el < p.e_local && p.real_counts != nullptr) p.real_counts[el] = bad ? 0 : total[el];
   }
   for (int q = threadIdx.x; q < p.ep; q += blockDim.x) {
     int acc = 0;
@@ -316,6 +318,7 @@ __global__ void __launch_bounds__(kDecodeThreads) route_decode_kernel(RouteParam
   for (int el = i; el <= p.e_local; el += kDecodeThreads) {
     p.expert_offsets[el] = bad ? 0 : base[el];
     if (el < p.e_local) p.counts[el] = bad ? 0 : pad_rows(total[el], p.m_mult);
+    if (el < p.e_local && p.real_counts != nullptr) p.real_counts[el] = bad ? 0 : total[el];
   }
   for (int q = i; q < p.ep; q += kDecodeThreads) {
     int acc = 0;
@@ -448,7 +451,7 @@ static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
                         int64_t capacity_rows, int64_t ptrs_size, int32_t* counts, int32_t* per_rank,
                         int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
                         int64_t* scatter_ptrs, int32_t* workspace, int64_t workspace_words, int* status,
-                        void* stream) {
+                        void* stream, int32_t* real_counts = nullptr) {
   if (!routing_ptrs || !dispatch_ptrs || !combine_ptrs || !counts || !per_rank || !expert_offsets ||
       !fwd_gather_ptrs || !scatter_ptrs || !workspace)
     return kRcBadArg;
@@ -475,6 +478,7 @@ static int route_launch(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
   p.capacity_rows = capacity_rows;
   p.ptrs_size = ptrs_size;
   p.counts = counts;
+  p.real_counts = real_counts;
   p.per_rank = per_rank;
   p.expert_offsets = expert_offsets;
   p.fwd = fwd_gather_ptrs;
@@ -520,6 +524,23 @@ extern "C" int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_p
                       bwd_gather_stride_bytes, scatter_stride_bytes, m_multiple_of, capacity_rows, ptrs_size, counts,
                       per_rank, expert_offsets, fwd_gather_ptrs, bwd_gather_ptrs, scatter_ptrs, workspace,
                       workspace_words, status, stream);
+}
+
+// dm_route that also reports the rows of every expert before padding to m_multiple_of (the swapped-operand
+// block-scaled GEMMs size their N side from it).
+extern "C" int dm_route_counted(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs,
+                                const uint64_t* combine_ptrs, int rank, int ep, int64_t T, int K, int E,
+                                int64_t gather_stride_bytes, int64_t bwd_gather_stride_bytes,
+                                int64_t scatter_stride_bytes, int m_multiple_of, int64_t capacity_rows,
+                                int64_t ptrs_size, int32_t* counts, int32_t* real_counts, int32_t* per_rank,
+                                int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
+                                int64_t* scatter_ptrs, int32_t* workspace, int64_t workspace_words, int* status,
+                                void* stream) {
+  if (!real_counts) return kRcBadArg;
+  return route_launch(routing_ptrs, dispatch_ptrs, combine_ptrs, rank, ep, T, K, E, gather_stride_bytes,
+                      bwd_gather_stride_bytes, scatter_stride_bytes, m_multiple_of, capacity_rows, ptrs_size, counts,
+                      per_rank, expert_offsets, fwd_gather_ptrs, bwd_gather_ptrs, scatter_ptrs, workspace,
+                      workspace_words, status, stream, real_counts);
 }
 
 // ---------------------------------------------------------------------------

@@ -90,6 +90,15 @@ int dm_route(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const 
              int32_t* expert_offsets, int64_t* fwd_gather_ptrs, int64_t* bwd_gather_ptrs,
              int64_t* scatter_ptrs, int32_t* workspace, int64_t workspace_words, int* status,
              void* stream);
+/* dm_route that also writes `real_counts[e_local]`, the rows of every local expert before rounding up to
+ * m_multiple_of (zero after a capacity violation).  dm_gemm_blockscaled_swapped sizes its tiles from it. */
+int dm_route_counted(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs, const uint64_t* combine_ptrs,
+                     int rank, int ep, int64_t T, int K, int E, int64_t gather_stride_bytes,
+                     int64_t bwd_gather_stride_bytes, int64_t scatter_stride_bytes, int m_multiple_of,
+                     int64_t capacity_rows, int64_t ptrs_size, int32_t* counts, int32_t* real_counts,
+                     int32_t* per_rank, int32_t* expert_offsets, int64_t* fwd_gather_ptrs,
+                     int64_t* bwd_gather_ptrs, int64_t* scatter_ptrs, int32_t* workspace, int64_t workspace_words,
+                     int* status, void* stream);
 
 /* ---------------------------------------------------------------------------
  * dm_route_static: the same routing metadata without a caller-provided workspace.
@@ -276,6 +285,19 @@ int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w,
                         const float* expert_scale_inv, const int32_t* expert_offsets, int e_local, int64_t max_rows,
                         int64_t N, int64_t Kd, int swiglu_interleaved, int clamped, float alpha, float limit,
                         const int* cond, int num_sms, int* status, void* stream);
+
+/* The same product for experts that received few rows (decode): weights on the 128-row side of the MMA, the
+ * expert's rows on the N side in steps of 32, so that a K stage costs MMAs of N = 32 or 64 instead of a 128-row
+ * tile and the layer is bound by streaming the weights once.  Replaces the reference's compact decode tiles
+ * (dist_moe/kernels/chunked_mega_blockscaled_policy.py:60-95, 32-row M tiles).  Arguments as dm_gemm_blockscaled
+ * plus `expert_counts` (int32 [e_local], real rows inside each 128-padded group; NULL = the whole group).  With
+ * swiglu_interleaved only h2 is written (C must be NULL).  Forward only. */
+int dm_gemm_blockscaled_swapped(int format, dm_operand a, dm_operand sfa, const void* w, const void* sfb, dm_operand c,
+                                dm_operand h2, const int64_t* scatter_ptrs, dm_operand row_scale_inv,
+                                const float* expert_scale_inv, const int32_t* expert_offsets,
+                                const int32_t* expert_counts, int e_local, int64_t max_rows, int64_t N, int64_t Kd,
+                                int swiglu_interleaved, int clamped, float alpha, float limit, const int* cond,
+                                int num_sms, int* status, void* stream);
 
 /* dm_gemm_blockscaled(MXFP8, swiglu_interleaved) whose epilogue quantises h2 on the way out: h2_q receives the
  * E4M3 bytes ([rows, N/2]) and h2_sf the blocked E8M0 scales of 1 x 32 blocks, bit-identical to dm_quant_mxfp8_row

@@ -42,6 +42,8 @@ def _check(out, ref, fmt):
     ("NVFP4", True, False, 200, 512, 256, 8, 16),
     ("NVFP4", False, False, 33, 256, 512, 2, 4),
     ("MXFP8_E4M3", True, False, 1, 256, 128, 1, 2),
+    ("NVFP4", True, False, 24, 512, 256, 8, 16),        # few rows per expert: the swapped-operand GEMMs
+    ("MXFP8_E4M3", True, True, 40, 256, 384, 2, 8),
 ])
 def test_inference_forward_with_prepared_weights(fmt, fuse, clamped, T, D, F, K, E):
     import dist_moe_b200 as dm
@@ -65,6 +67,19 @@ def test_inference_forward_with_prepared_weights(fmt, fuse, clamped, T, D, F, K,
             _check(out, ref, fmt)
             outs.append(out.clone())
         assert torch.equal(outs[0], outs[1]), "repeat execution is not bit-identical"
+        if fuse:
+            # the two GEMM orientations accumulate the same K steps in the same order: forcing either gives equal bits
+            from dist_moe_b200 import _blockscaled as bs
+
+            saved = bs.SWAPPED_MAX_ROWS_PER_EXPERT
+            try:
+                for threshold in (0, 10**9):
+                    bs.SWAPPED_MAX_ROWS_PER_EXPERT = threshold
+                    forced = dm.routed_experts(x.to(dev), ids.to(dev), scores.to(dev), p13, p2, ctx)
+                    ctx.check_status()
+                    assert torch.equal(forced, outs[0]), f"orientation threshold {threshold} changes the output"
+            finally:
+                bs.SWAPPED_MAX_ROWS_PER_EXPERT = saved
         with pytest.raises(TypeError):
             dm.routed_experts(x.to(dev), ids.to(dev), scores.to(dev), p13, w2.to(dev), ctx)
     finally:

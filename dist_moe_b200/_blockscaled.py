@@ -233,11 +233,6 @@ def _workspace(state):
 SWAPPED_MAX_ROWS_PER_EXPERT = 48
 
 
-def _wide_tiles_selected() -> bool:
-    """Whether the block-scaled GEMMs run on 128x256 tiles (the only ones with the quantising SwiGLU epilogue)."""
-    return bool(nat.lib.dm_blockscaled_wide_enabled())
-
-
 def _view(buf: torch.Tensor, offset: int) -> nat.Operand:
     return nat.Operand(buf.data_ptr() + offset, buf.numel() - offset, None)
 
@@ -334,7 +329,7 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
                                                       real.data_ptr(), el, max_rows, 2 * F, D, 1, clamped, alpha,
                                                       limit, None, state.num_sms, status, st),
                   "dm_gemm_blockscaled_swapped(w13+swiglu)")
-    elif fused and not lay.fp4 and _wide_tiles_selected():
+    elif fused and not lay.fp4:
         # MXFP8: the SwiGLU epilogue writes h2 already row-quantised, the operand of the W2 GEMM
         h2_dense = lay.dense
         h2_quantised = True
@@ -398,8 +393,8 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
         nat.check(nat.lib.dm_rmsnorm_combine_fwd(
             state.combine.local().data_ptr(), scores.data_ptr(), int(scores.dtype == torch.bfloat16), ids.data_ptr(),
             int(ids.dtype == torch.int64), nat.ptr(post.weight), float(post.gain_center), float(post.eps),
-            int(post.norm_output_dtype == torch.bfloat16), out.data_ptr(), None, T, K, D, None, None, None, 0, st),
-            "dm_rmsnorm_combine_fwd")
+            int(post.norm_output_dtype == torch.bfloat16), int(bool(post.use_kahan)), out.data_ptr(), None, T, K, D,
+            None, None, None, 0, st), "dm_rmsnorm_combine_fwd")
     else:
         nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
                                            int(scores.dtype == torch.bfloat16), ids.data_ptr(),
@@ -467,7 +462,7 @@ def _training_weights(w13_param, w2_param, p13, p2, cfg):
 
 class _TrainCall:
     __slots__ = ("T", "R", "offsets", "recv", "fwd", "bwd", "sct", "h1", "x_col", "x_col_sf", "h2_col", "h2_col_sf",
-                 "h3", "p13", "p2")
+                 "h3", "p13", "p2", "rstd")
 
 
 def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
@@ -535,13 +530,22 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
                                           0.0, None, state.num_sms, status, st), "dm_gemm_blockscaled(w2)")
     state.barrier(state.combine)
     out = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
-    c.h3 = torch.empty(T * K * D, dtype=torch.bfloat16, device=dev) if need_h3 else None
-    if options.experts_output_postprocess is not None:
-        raise NotImplementedError("expert-output postprocessing is not available on the MXFP8 training path")
-    nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
-                                       int(scores.dtype == torch.bfloat16), ids.data_ptr(),
-                                       int(ids.dtype == torch.int64), out.data_ptr(), T, K, D, nat.ptr(c.h3), None, None,
-                                       0, st), "dm_scale_and_sum")
+    post = options.experts_output_postprocess
+    is_norm = isinstance(post, RMSNormPostprocess)
+    # the expert outputs are kept for the score gradient, and always for the backward of the fused RMSNorm
+    c.h3 = torch.empty(T * K * D, dtype=torch.bfloat16, device=dev) if (need_h3 or is_norm) else None
+    c.rstd = None
+    if is_norm:
+        from ._postprocess import rmsnorm_combine_forward
+
+        c.rstd = rmsnorm_combine_forward(state, c, post, scores, ids, out, save=True, save_to=c.h3)
+    elif post is not None:
+        raise NotImplementedError("callable expert-output post-processing runs on the BF16 eager path only")
+    else:
+        nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
+                                           int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                           int(ids.dtype == torch.int64), out.data_ptr(), T, K, D, nat.ptr(c.h3), None,
+                                           None, 0, st), "dm_scale_and_sum")
     state.last_recv = c.recv
     return out, c
 
@@ -570,10 +574,17 @@ def _mxfp8_backward(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_pa
     d1c, d1csf = ws.take(R * 2 * F), ws.take(_sf_cols_bytes(R, 2 * F))
     combine = state.combine.local().data_ptr()
     grad_scores = torch.empty(T, K, dtype=torch.float32, device=dev) if need_scores else None
-    nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(), int(scores.dtype == torch.bfloat16),
-                                             ids.data_ptr(), int(ids.dtype == torch.int64),
-                                             c.h3.data_ptr() if need_scores else None, None, combine,
-                                             nat.ptr(grad_scores), T, K, D, st), "dm_broadcast_and_scale")
+    post = options.experts_output_postprocess
+    if isinstance(post, RMSNormPostprocess):
+        from ._postprocess import rmsnorm_combine_backward
+
+        rmsnorm_combine_backward(state, c, post, grad_out, scores, ids, grad_scores, h3=c.h3)
+    else:
+        nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(),
+                                                 int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                                 int(ids.dtype == torch.int64),
+                                                 c.h3.data_ptr() if need_scores else None, None, combine,
+                                                 nat.ptr(grad_scores), T, K, D, st), "dm_broadcast_and_scale")
     state.barrier(state.combine)
     # ---- W2 ----------------------------------------------------------------------------------
     if need_w2:

@@ -103,8 +103,6 @@ _SIGNATURES = {
         [c_int, Operand, Operand, _P, _P, Operand, Operand, _P, Operand, _P, _P, _P, c_int, c_int64, c_int64, c_int64,
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
-    "dm_set_blockscaled_wide": (c_int, [c_int]),
-    "dm_blockscaled_wide_enabled": (c_int, []),
     "dm_set_route_decode_kernel": (c_int, [c_int]),
     "dm_route_decode_kernel_enabled": (c_int, []),
     "dm_gemm_blockscaled_swiglu_mxfp8": (
@@ -122,11 +120,12 @@ _SIGNATURES = {
     ),
     "dm_rmsnorm_combine_fwd": (
         c_int,
-        [_P, _P, c_int, _P, c_int, _P, c_float, c_float, c_int, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int, _P],
+        [_P, _P, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int,
+         _P],
     ),
     "dm_rmsnorm_combine_bwd": (
         c_int,
-        [_P, _P, c_int, _P, c_int, _P, _P, _P, c_float, c_int, _P, _P, c_int64, c_int, c_int64, _P],
+        [_P, _P, c_int, _P, c_int, _P, _P, _P, c_float, c_int, c_int, _P, _P, c_int64, c_int, c_int64, _P],
     ),
     "dm_quant_mxfp8_row": (c_int, [_P, _P, c_int64, c_int64, _P, c_int64, _P, c_int64, c_int, _P]),
     "dm_quant_mxfp8_col": (c_int, [_P, _P, c_int64, c_int64, _P, _P, c_int, _P]),

@@ -2,8 +2,8 @@
 //
 //   C[r, n] = sum_k  (A[r,k] * sfa[r, k/V]) * (W[e][n,k] * sfb[e][n, k/V])        V = 32 (MXFP8) or 16 (NVFP4)
 //
-// Same warp-specialised skeleton as the BF16 kernel (TMA producer warp, one MMA-issuing lane,
-// four epilogue warps, double-buffered 128x128 fp32 accumulators in TMEM).  Differences:
+// Same warp-specialised skeleton as the BF16 kernel (TMA producer warp, one MMA-issuing lane, eight
+// epilogue warps, one 128 x 256 fp32 accumulator in TMEM).  Differences:
 //   * a pipeline stage is 128 bytes of K per row: 128 E4M3 or 256 packed E2M1 elements;
 //   * next to the A/B tiles the producer bulk-copies the stage's scale atoms.  Scales are
 //     stored in 128-row x 4-column atoms of 512 bytes (row r, column c at (r%32)*16 + (r/32)*4 + c),
@@ -23,15 +23,8 @@ namespace dm {
 
 constexpr int kBsBM = 128;
 constexpr int kBsBN = 128;
-constexpr int kBsStages = 5;
-constexpr int kBsThreads = 224;  // TMA warp, MMA warp, four epilogue warps, one accumulator watcher
 constexpr uint32_t kBsABytes = kBsBM * 128;  // 16 KiB
-constexpr uint32_t kBsBBytes = kBsBN * 128;  // 16 KiB
-constexpr uint32_t kBsSfBytes = 2048;        // up to 4 atoms for A and for B each
-constexpr uint32_t kBsStageBytes = kBsABytes + kBsBBytes + 2 * kBsSfBytes;
 constexpr uint32_t kBsTmemCols = 512;
-constexpr uint32_t kBsSfTmemBase = 2 * kBsBN;  // scale columns start after the two accumulators
-constexpr size_t kBsSmemBytes = kBsStages * kBsStageBytes + 4 * kStagingBytes + 1024;
 constexpr int kBsMaxGroups = 256;
 
 struct BsParams {
@@ -96,407 +89,13 @@ __device__ __forceinline__ BsTile bs_decode(int tile, int& e, const int* tile_st
   return t;
 }
 
-__global__ void __launch_bounds__(kBsThreads, 1) blockscaled_gemm_kernel(const __grid_constant__ BsParams p) {
-  if (p.cond != nullptr && *p.cond == 0) return;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-
-  __shared__ uint64_t full_bar[kBsStages];
-  __shared__ uint64_t empty_bar[kBsStages];
-  __shared__ uint64_t tmem_full_bar[2];
-  __shared__ uint64_t tmem_empty_bar[2];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ int abort_flag;
-  __shared__ int s_off[kBsMaxGroups + 1];
-  __shared__ int s_tile_start[kBsMaxGroups + 1];
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int n_tiles = p.mode == 2 ? (p.Kw + kBsBN - 1) / kBsBN : (p.N + kBsBN - 1) / kBsBN;
-  const int wgrad_m_tiles = (p.N + kBsBM - 1) / kBsBM;
-  const int atoms = p.fp4 ? 4 : 1;  // scale atoms per stage and operand
-
-  for (int i = threadIdx.x; i <= p.e_local; i += blockDim.x) {
-    const int v = p.expert_offsets[i];
-    s_off[i] = v < p.max_rows ? v : p.max_rows;
-  }
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < kBsStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 4);
-    }
-    mbar_fence_init();
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int e = 0; e < p.e_local; ++e) {
-      s_tile_start[e] = acc;
-      const int rows = s_off[e + 1] - s_off[e];
-      if ((s_off[e] & 127) != 0) set_status(p.status, kCapacityExceeded, -1, e, s_off[e]);  // rows must be 128-padded
-      acc += p.mode == 2 ? wgrad_m_tiles * n_tiles : ((rows + kBsBM - 1) / kBsBM) * n_tiles;
-    }
-    s_tile_start[p.e_local] = acc;
-  }
-  if (warp == 1) {
-    tmem_alloc(&tmem_base_slot, kBsTmemCols);
-    tmem_relinquish();
-  }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&p.tm_a);
-    tma_prefetch_desc(&p.tm_b);
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  tcgen05_fence_after();
-  const uint32_t tmem_base = tmem_base_slot;
-  const int total_tiles = s_tile_start[p.e_local];
-
-  if (warp == 0) {
-    // ======================= producer =======================
-    int stage = 0;
-    uint32_t phase = 0;
-    int e = 0;
-    const int a_line0 = static_cast<int>((p.a_off ? *p.a_off : 0) >> 7);
-    const int b_line0 = static_cast<int>((p.b_off ? *p.b_off : 0) >> 7);
-    const uint8_t* sfa = p.sfa_base + (p.sfa_off ? *p.sfa_off : 0);
-    const uint8_t* sfb_dyn = p.sfb + (p.sfb_off ? *p.sfb_off : 0);
-    const uint32_t sf_bytes = atoms * 512;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
-      const uint8_t* sfa_row;
-      const uint8_t* sfb_row;
-      if (p.mode == 2) {
-        // scales of the column-quantised operands: rows = features, columns = 32-row blocks of the packed rows
-        sfa_row = sfa + (static_cast<int64_t>(t.m_blk) * p.a_col_atoms + (t.row0 >> 7)) * 512;
-        sfb_row = sfb_dyn + (static_cast<int64_t>(t.n_blk) * p.b_col_atoms + (t.row0 >> 7)) * 512;
-      } else {
-        sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
-        sfb_row = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk) * p.b_col_atoms * 512;
-      }
-      for (int kb = 0; kb < t.k_iters; ++kb) {
-        if (lane == 0) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
-          if (ok) {
-            uint8_t* sa = smem + stage * kBsStageBytes;
-            uint8_t* sb = sa + kBsABytes;
-            uint8_t* ssa = sb + kBsBBytes;
-            uint8_t* ssb = ssa + kBsSfBytes;
-            mbar_arrive_expect_tx(&full_bar[stage], kBsABytes + kBsBBytes + 2 * sf_bytes);
-            if (p.mode == 2) {
-              tma_load_3d(sa, &p.tm_a, 0, a_line0 + t.m_blk, t.row0 + kb * 128, &full_bar[stage]);
-              tma_load_3d(sb, &p.tm_b, 0, b_line0 + t.n_blk, t.row0 + kb * 128, &full_bar[stage]);
-            } else {
-              tma_load_3d(sa, &p.tm_a, 0, a_line0 + kb, t.row0, &full_bar[stage]);
-              if (p.mode == 1)
-                tma_load_2d(sb, &p.tm_b, t.n_blk * kBsBN, t.e * p.Kw + kb * 128, &full_bar[stage]);
-              else
-                tma_load_2d(sb, &p.tm_b, kb * 128, t.e * p.N + t.n_blk * kBsBN, &full_bar[stage]);
-            }
-            bulk_load(ssa, sfa_row + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
-            bulk_load(ssb, sfb_row + static_cast<int64_t>(kb) * sf_bytes, sf_bytes, &full_bar[stage]);
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        if (++stage == kBsStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ======================= MMA issuer =======================
-    // One thread runs the whole issue loop (no per-stage warp synchronisation: a stage is only four MMAs).
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int e = 0, it = 0;
-      uint32_t kstep = 0;
-      bool ok = true;
-      const int a_mn = p.mode == 2, b_mn = p.mode != 0;
-      const uint32_t a_step = a_mn ? 4096u : 32u, b_step = b_mn ? 4096u : 32u;
-      const uint32_t idesc4 = umma_idesc_blockscaled(kBsBN, 1, 0, 0);
-      uint32_t idesc8[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) idesc8[j] = umma_idesc_blockscaled(kBsBN, 0, j, j, a_mn, b_mn);
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
-        const int buf = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1u;
-        ok = mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, &abort_flag);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * kBsBN;
-        for (int kb = 0; kb < t.k_iters; ++kb, ++kstep) {
-          ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
-          if (!ok) break;
-          const uint32_t a_addr = smem_u32(smem + stage * kBsStageBytes), b_addr = a_addr + kBsABytes;
-          const uint32_t ssa = b_addr + kBsBBytes, ssb = ssa + kBsSfBytes;
-          const uint32_t sfa_t = tmem_base + kBsSfTmemBase + (kstep & 1u) * 32u;
-          const uint32_t sfb_t = sfa_t + 16u;
-          for (int a = 0; a < atoms; ++a) {
-            tmem_cp_sf_atom(sfa_t + 4 * a, sf_smem_desc(ssa + a * 512));
-            tmem_cp_sf_atom(sfb_t + 4 * a, sf_smem_desc(ssb + a * 512));
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            // K-major: 32 bytes of K per step inside the 128-byte row; MN-major: four 8-row groups of 1 KiB.
-            const uint64_t da = umma_smem_desc(a_addr + j * a_step, 16, 1024);
-            const uint64_t db = umma_smem_desc(b_addr + j * b_step, 16, 1024);
-            const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
-            if (p.fp4)
-              umma_nvf4(d_tmem, da, db, idesc4, sfa_t + 4 * j, sfb_t + 4 * j, acc);
-            else
-              umma_mxf8(d_tmem, da, db, idesc8[j], sfa_t, sfb_t, acc);
-          }
-          tcgen05_commit(&empty_bar[stage]);
-          if (++stage == kBsStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-        if (!ok) break;
-        if (t.k_iters > 0)
-          tcgen05_commit(&tmem_full_bar[buf]);
-        else
-          mbar_arrive(&tmem_full_bar[buf]);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 6) {
-    // ======================= accumulator watcher =======================
-    // Polls the accumulator-ready barriers for the epilogue warps and releases them through a hardware named
-    // barrier, so that waiting epilogue warps take no issue slots from the threads that issue loads and MMAs.
-    // It arrives for every tile, also after a timeout, so that no epilogue warp is left blocked.
-    bool ok = true;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      if (ok && lane == 0) ok = mbar_wait(&tmem_full_bar[buf], acc_phase, &abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      asm volatile("bar.arrive %0, %1;" ::"r"(1 + buf), "r"(4 * 32 + 32) : "memory");
-    }
-  } else {
-    // ======================= epilogue =======================
-    const int quad = warp & 3;
-    const int row_in_tile = quad * 32 + lane;
-    uint8_t* stg = smem + kBsStages * kBsStageBytes + (warp - 2) * kStagingBytes;
-    int e = 0, it = 0;
-    bool ok = true;
-    const int64_t c_off = p.c_off ? *p.c_off : 0;
-    const int64_t h2_off = p.h2_off ? *p.h2_off : 0;
-    const float* row_inv =
-        p.row_inv_base ? reinterpret_cast<const float*>(p.row_inv_base + (p.row_inv_off ? *p.row_inv_off : 0)) : nullptr;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + buf), "r"(4 * 32 + 32) : "memory");  // released by the watcher
-      (void)acc_phase;
-      ok = abort_flag == 0;
-      if (!ok) break;
-      tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBsBN;
-      if (p.mode == 2) {
-        // weight gradient: dW[e][m][n], overwrite or accumulate (fp32 or bf16 destination)
-        const int out_row = t.m_blk * kBsBM + row_in_tile;
-        const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kw;
-        const uint64_t my_row =
-            out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
-        for (int c0 = 0; c0 < kBsBN; c0 += 32) {
-          uint32_t r[32];
-          if (t.k_iters > 0) {
-            tmem_ld_32x32(taddr + c0, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0u;
-          }
-          const int col = t.n_blk * kBsBN + c0;
-          if (p.out_fp32) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              stage_put(stg, lane, j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + (lane >> 3), j = lane & 7;
-              const uint4 v = stage_get(stg, rr, j);
-              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-              if (rp != 0 && col + 4 * j + 4 <= p.Kw) {
-                const uint64_t dst = rp + static_cast<uint64_t>(col + 4 * j) * 4;
-                if (p.accumulate)
-                  red_add_f32x4(dst, v);
-                else
-                  *reinterpret_cast<uint4*>(dst) = v;
-              }
-            }
-            __syncwarp();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = i * 8 + (lane >> 2), j = lane & 3;
-              const uint4 v = stage64_get(stg, rr, j);
-              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-              if (rp != 0 && col + 8 * j + 8 <= p.Kw) {
-                const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
-                if (p.accumulate)
-                  red_add_bf16x8(dst, v);
-                else
-                  *reinterpret_cast<uint4*>(dst) = v;
-              }
-            }
-            __syncwarp();
-          }
-        }
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
-        continue;
-      }
-      const int row = t.row0 + row_in_tile;
-      const bool row_ok = row < t.row_end;
-      float scale = 1.0f;
-      bool scaled = false;
-      if (row_inv != nullptr && row_ok) {
-        scale = row_inv[row];
-        scaled = true;
-      }
-      const float escale = p.expert_inv ? p.expert_inv[t.e] : 1.0f;
-      scaled = scaled || p.expert_inv != nullptr;
-      if (p.swiglu) {
-        // Columns come in groups of 16: 8 gate features then the matching 8 up features.
-        const int F = p.N / 2;
-        const uint64_t my_h2 =
-            row_ok ? reinterpret_cast<uint64_t>(p.h2_base) + h2_off + static_cast<uint64_t>(row) * F * 2 : 0ull;
-        const uint64_t my_h1 = (row_ok && p.c_base)
-                                   ? reinterpret_cast<uint64_t>(p.c_base) + c_off + static_cast<uint64_t>(row) * p.N * 2
-                                   : 0ull;
-        uint4 gate_v[8], up_v[8];
-#pragma unroll
-        for (int c0 = 0; c0 < kBsBN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            uint32_t gw[4], uw[4], zw[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float g0 = __uint_as_float(r[16 * g + 2 * q]), g1 = __uint_as_float(r[16 * g + 2 * q + 1]);
-              float u0 = __uint_as_float(r[16 * g + 8 + 2 * q]), u1 = __uint_as_float(r[16 * g + 8 + 2 * q + 1]);
-              if (scaled) {
-                g0 = (g0 * scale) * escale; g1 = (g1 * scale) * escale;
-                u0 = (u0 * scale) * escale; u1 = (u1 * scale) * escale;
-              }
-              gw[q] = pack_bf16x2(g0, g1);
-              uw[q] = pack_bf16x2(u0, u1);
-              const float z0 = swiglu_f32(__uint_as_float(gw[q] << 16), __uint_as_float(uw[q] << 16), p.act);
-              const float z1 =
-                  swiglu_f32(__uint_as_float(gw[q] & 0xffff0000u), __uint_as_float(uw[q] & 0xffff0000u), p.act);
-              zw[q] = pack_bf16x2(z0, z1);
-            }
-            const int chunk = (c0 >> 5) * 2 + g;  // 8 features = one 16-byte chunk of the 64-feature row segment
-            stage_put(stg, lane, chunk, make_uint4(zw[0], zw[1], zw[2], zw[3]));
-            gate_v[chunk] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
-            up_v[chunk] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
-          }
-        }
-        const int f0 = t.n_blk * (kBsBN / 2);
-#pragma unroll
-        for (int which = 0; which < 3; ++which) {
-          if (which > 0) {
-            if (p.c_base == nullptr) break;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) stage_put(stg, lane, j, which == 1 ? gate_v[j] : up_v[j]);
-          }
-          __syncwarp();
-          const uint64_t base = which == 0 ? my_h2 : my_h1;
-          const int col_out = which == 2 ? F + f0 : f0;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + (lane >> 3), j = lane & 7;
-            const uint4 v = stage_get(stg, rr, j);
-            const uint64_t rp = __shfl_sync(0xffffffffu, base, rr);
-            if (rp != 0 && f0 + 8 * j + 8 <= F)
-              *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col_out + 8 * j) * 2) = v;
-          }
-          __syncwarp();
-        }
-      } else {
-        uint64_t my_row = 0;
-        if (row_ok) {
-          if (p.scatter_ptrs != nullptr)
-            my_row = static_cast<uint64_t>(p.scatter_ptrs[row]);
-          else
-            my_row = reinterpret_cast<uint64_t>(p.c_base) + c_off + static_cast<uint64_t>(row) * p.N * 2;
-        }
-        for (int c0 = 0; c0 < kBsBN; c0 += 64) {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(taddr + c0, r0);
-          tmem_ld_32x32(taddr + c0 + 32, r1);
-          tmem_ld_wait();
-          if (scaled) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              r0[j] = __float_as_uint((__uint_as_float(r0[j]) * scale) * escale);
-              r1[j] = __float_as_uint((__uint_as_float(r1[j]) * scale) * escale);
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            stage_put(stg, lane, j, pack8_bf16(r0 + 8 * j));
-            stage_put(stg, lane, j + 4, pack8_bf16(r1 + 8 * j));
-          }
-          __syncwarp();
-          const int col = t.n_blk * kBsBN + c0;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + (lane >> 3), j = lane & 7;
-            const uint4 v = stage_get(stg, rr, j);
-            const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-            if (rp != 0 && col + 8 * j + 8 <= p.N)
-              *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(col + 8 * j) * 2) = v;
-          }
-          __syncwarp();
-        }
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
-    }
-  }
-
-  tcgen05_fence_before();
-  __syncthreads();
-  if (abort_flag && threadIdx.x == 0) set_status(p.status, kPipelineTimeout, 3, blockIdx.x);
-  if (warp == 1) {
-    tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kBsTmemCols);
-  }
-}
-
-
 // ---------------------------------------------------------------------------------------------------------
-// Wide forward kernel: 128 x 256 output tiles for the K-major forward GEMMs (inference and training forward).
-//
-// Per 128 bytes of K a 128 x 128 tile moves 32 KiB of operands and spends, for NVFP4, more tensor-pipe time
-// on the eight scale-atom copies (about 47 cycles each, they serialise with the MMAs) than on its four MMAs
-// (69 cycles each).  A 256-column tile moves 48 KiB for twice the work and needs twelve copies per four
-// 132-cycle MMAs.  TMEM then holds one 256-column accumulator plus two buffers of scale columns, so the
-// epilogue (eight warps, a few thousand cycles) does not overlap the next tile's MMAs; tiles here are tens of
-// thousands of cycles long.
+// 128 x 256 output tiles.  Per 128 bytes of K the tile moves 48 KiB of operands and needs, for NVFP4, twelve
+// scale-atom copies (about 47 cycles each, they serialise with the MMAs) per four 132-cycle MMAs; a 128 x 128
+// tile would spend more tensor-pipe time on its eight copies than on its four 69-cycle MMAs.  TMEM holds one
+// 256-column accumulator plus two buffers of scale columns, so the epilogue (eight warps, a few thousand
+// cycles) does not overlap the next tile's MMAs; tiles here are tens of thousands of cycles long.  Experts
+// with few rows take the swapped-operand kernel instead (gemm_blockscaled_swapped.cu).
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kWdBN = 256;
 constexpr int kWdThreads = 352;  // TMA warp, MMA warp, eight epilogue warps, accumulator watcher
@@ -956,43 +555,17 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
 
 using namespace dm;
 
-static int g_bs_wide = 1;
-
-extern "C" int dm_set_blockscaled_wide(int enabled) {
-  const int previous = g_bs_wide;
-  g_bs_wide = enabled ? 1 : 0;
-  return previous;
-}
-
-extern "C" int dm_blockscaled_wide_enabled(void) { return g_bs_wide; }
-
-static int bs_prepare_launch();
-
-// Launches the 128 x 256 kernel, or the 128 x 128 one when the wide tiles are switched off.
+// Launches the 128 x 256 kernel.
 static int bs_launch(const BsParams& p, int num_sms, cudaStream_t st) {
   const int grid = persistent_grid(num_sms);
-  if (g_bs_wide) {
-    static PerDeviceOnce wide_attr_set;
-    const int rc = once_per_device(wide_attr_set, [] {
-      return static_cast<int>(cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4)));
-    });
-    if (rc != 0) return rc;
-    blockscaled_wide_kernel<<<grid, kWdThreads, p.fp4 ? kWdSmemFp4 : kWdSmemFp8, st>>>(p);
-  } else {
-    int rc = bs_prepare_launch();
-    if (rc != kRcOk) return rc;
-    blockscaled_gemm_kernel<<<grid, kBsThreads, kBsSmemBytes, st>>>(p);
-  }
-  return static_cast<int>(cudaGetLastError());
-}
-
-static int bs_prepare_launch() {
-  static PerDeviceOnce attr_set;
-  return once_per_device(attr_set, [] {
-    return static_cast<int>(cudaFuncSetAttribute(blockscaled_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(kBsSmemBytes)));
+  static PerDeviceOnce wide_attr_set;
+  const int rc = once_per_device(wide_attr_set, [] {
+    return static_cast<int>(cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4)));
   });
+  if (rc != 0) return rc;
+  blockscaled_wide_kernel<<<grid, kWdThreads, p.fp4 ? kWdSmemFp4 : kWdSmemFp8, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, const void* w, const void* sfb,
@@ -1010,12 +583,10 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   const int64_t row_bytes = fp4 ? Kd / 2 : Kd;
   if ((row_bytes % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
-  int rc = bs_prepare_launch();
-  if (rc != kRcOk) return rc;
   BsParams p{};
-  rc = encode_arena_u8(&p.tm_a, a, row_bytes, max_rows + 256, kBsBM);
+  int rc = encode_arena_u8(&p.tm_a, a, row_bytes, max_rows + 256, kBsBM);
   if (rc != kRcOk) return rc;
-  rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kBsBN);
+  rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kWdBN);
   if (rc != kRcOk) return rc;
   const int64_t scale_cols = Kd / (fp4 ? 16 : 32);
   p.a_col_atoms = static_cast<int>((scale_cols + 3) / 4);
@@ -1043,10 +614,6 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   p.fp4 = fp4;
   p.swiglu = swiglu_interleaved ? 1 : 0;
   p.act = ActParams{clamped, alpha, limit};
-  if (g_bs_wide) {
-    rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * N, row_bytes, kWdBN);
-    if (rc != kRcOk) return rc;
-  }
   return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
 }
 
@@ -1061,7 +628,6 @@ extern "C" int dm_gemm_blockscaled_swiglu_mxfp8(dm_operand a, dm_operand sfa, co
     return kRcBadArg;
   if (e_local > kBsMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
   if ((Kd % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0 || ((N / 2) % 32) != 0) return kRcUnsupportedShape;
-  if (!g_bs_wide) return kRcUnsupportedShape;  // only the 128 x 256 kernel has this epilogue
   if (max_rows == 0) return kRcOk;
   BsParams p{};
   int rc = encode_arena_u8(&p.tm_a, a, Kd, max_rows + 256, kBsBM);
@@ -1107,10 +673,8 @@ extern "C" int dm_gemm_blockscaled_dgrad(dm_operand dy, dm_operand sf_dy, const 
   if (e_local > kBsMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
   if ((Kd % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0) return kRcUnsupportedShape;
   if (max_rows == 0) return kRcOk;
-  int rc = bs_prepare_launch();
-  if (rc != kRcOk) return rc;
   BsParams p{};
-  rc = encode_arena_u8(&p.tm_a, dy, Kd, max_rows + 256, kBsBM);
+  int rc = encode_arena_u8(&p.tm_a, dy, Kd, max_rows + 256, kBsBM);
   if (rc != kRcOk) return rc;
   rc = encode_2d_u8(&p.tm_b, w, static_cast<int64_t>(e_local) * Kd, N, kBsBN);
   if (rc != kRcOk) return rc;
@@ -1149,9 +713,8 @@ extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col
     return kRcBadArg;
   if (e_local > kBsMaxGroups || max_rows > (1 << 30)) return kRcTooLarge;
   if ((M % 128) != 0 || (N % 128) != 0 || (max_rows % 128) != 0) return kRcUnsupportedShape;
-  int rc = bs_prepare_launch();
-  if (rc != kRcOk) return rc;
   BsParams p{};
+  int rc = kRcOk;
   // with no rows at all the kernel still runs so that a non-accumulating call zero-fills dW
   const int64_t rows_extent = max_rows > 0 ? max_rows : 128;
   rc = encode_arena_u8(&p.tm_a, dy_col, M, rows_extent, 128);

@@ -26,13 +26,43 @@ __device__ __forceinline__ void up8(const uint4& v, float (&f)[8]) {
 }
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// Compensated accumulation of the sum of squares (dist_moe/_postprocess.py:44-46 `use_kahan`): every thread keeps a
+// running compensation term, and partial sums are merged with an error-free two-sum, so the result is the fp32
+// rounding of a nearly exact sum whatever the order.
+__device__ __forceinline__ void kahan_add(float& s, float& c, float x) {
+  const float y = __fsub_rn(x, c);
+  const float t = __fadd_rn(s, y);
+  c = __fsub_rn(__fsub_rn(t, s), y);
+  s = t;
+}
+__device__ __forceinline__ void two_sum_merge(float& s, float& c, float s2, float c2) {
+  const float t = __fadd_rn(s, s2);
+  const float bp = __fsub_rn(t, s);
+  const float err = __fadd_rn(__fsub_rn(s, __fsub_rn(t, bp)), __fsub_rn(s2, bp));
+  c = __fsub_rn(__fadd_rn(c, c2), err);  // c follows kahan_add's sign: it holds minus the lost low part
+  s = t;
+}
+__device__ __forceinline__ void warp_reduce_sumsq(float& ss, float& cc, int kahan) {
+  if (kahan) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float s2 = __shfl_xor_sync(0xffffffffu, ss, d), c2 = __shfl_xor_sync(0xffffffffu, cc, d);
+      two_sum_merge(ss, cc, s2, c2);
+    }
+  } else {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+  }
+}
+
 template <typename IdT>
 __global__ void __launch_bounds__(256) rmsnorm_combine_fwd_kernel(
     const uint4* __restrict__ h3, const void* scores, int scores_bf16, const IdT* __restrict__ ids,
     const uint4* __restrict__ gamma, float gain_center, float eps, int norm_bf16, uint4* __restrict__ out,
     float* __restrict__ rstd_out, int64_t T, int K, int vec, uint8_t* save_base, const int64_t* save_offset,
-    const int* save_cond, int save_expect) {
+    const int* save_cond, int save_expect, int kahan) {
   __shared__ float part[kNormMaxK][8];
+  __shared__ float partc[kNormMaxK][8];
   __shared__ float rs[kNormMaxK];
   bool save = save_base != nullptr;
   if (save && save_cond != nullptr) save = ((*save_cond != 0) == (save_expect != 0));
@@ -42,7 +72,7 @@ __global__ void __launch_bounds__(256) rmsnorm_combine_fwd_kernel(
   for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
     for (int k = 0; k < K; ++k) {
       const int64_t route = t * K + k;
-      float ss = 0.f;
+      float ss = 0.f, cc = 0.f;
       for (int v = threadIdx.x; v < vec; v += 256) {
         const uint4 raw = h3[route * vec + v];
         if (save) save_dst[route * vec + v] = raw;
@@ -54,18 +84,32 @@ __global__ void __launch_bounds__(256) rmsnorm_combine_fwd_kernel(
 #pragma unroll
           for (int j = 0; j < 8; ++j) h[j] *= (g[j] + gain_center);
         }
+        if (kahan) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += h[j] * h[j];
+          for (int j = 0; j < 8; ++j) kahan_add(ss, cc, __fmul_rn(h[j], h[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += h[j] * h[j];
+        }
       }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
-      if (lane == 0) part[k][warp] = ss;
+      warp_reduce_sumsq(ss, cc, kahan);
+      if (lane == 0) {
+        part[k][warp] = ss;
+        partc[k][warp] = cc;
+      }
     }
     __syncthreads();
     if (threadIdx.x < K) {
       float ss = 0.f;
+      if (kahan) {
+        float cc = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) ss += part[threadIdx.x][w];
+        for (int w = 0; w < 8; ++w) two_sum_merge(ss, cc, part[threadIdx.x][w], partc[threadIdx.x][w]);
+        ss = __fsub_rn(ss, cc);
+      } else {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) ss += part[threadIdx.x][w];
+      }
       const int64_t route = t * K + threadIdx.x;
       const float r = ids[route] >= 0 ? rsqrtf(ss * inv_d + eps) : 0.f;
       rs[threadIdx.x] = r;
@@ -107,7 +151,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(256) rmsnorm_combine_bwd_kernel(
     const uint4* __restrict__ grad_out, const void* scores, int scores_bf16, const IdT* __restrict__ ids,
     const uint8_t* h3_base, const int64_t* h3_offset, const float* __restrict__ rstd_in, float eps, int norm_bf16,
-    uint4* grad_h3, float* __restrict__ grad_scores, int64_t T, int K, int vec) {
+    uint4* grad_h3, float* __restrict__ grad_scores, int64_t T, int K, int vec, int kahan) {
   const uint4* h3 = reinterpret_cast<const uint4*>(h3_base + (h3_offset ? *h3_offset : 0));
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const float inv_d = 1.0f / static_cast<float>(vec * 8);
@@ -123,21 +167,36 @@ __global__ void __launch_bounds__(256) rmsnorm_combine_bwd_kernel(
     }
     const float w = scores_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(scores)[route])
                                 : static_cast<const float*>(scores)[route];
-    float ss = 0.f, hg = 0.f;
+    float ss = 0.f, cc = 0.f, hg = 0.f;
     for (int v = lane; v < vec; v += 32) {
       float h[8], g[8];
       up8(h3[route * vec + v], h);
       up8(grad_out[t * vec + v], g);
+      if (kahan) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        ss += h[j] * h[j];
-        hg += h[j] * g[j];
+        for (int j = 0; j < 8; ++j) {
+          kahan_add(ss, cc, __fmul_rn(h[j], h[j]));
+          hg += h[j] * g[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ss += h[j] * h[j];
+          hg += h[j] * g[j];
+        }
       }
     }
+    if (kahan) {
+      warp_reduce_sumsq(ss, cc, 1);
+      ss = __fsub_rn(ss, cc);
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-      ss += __shfl_xor_sync(0xffffffffu, ss, d);
-      hg += __shfl_xor_sync(0xffffffffu, hg, d);
+      for (int d = 16; d > 0; d >>= 1) hg += __shfl_xor_sync(0xffffffffu, hg, d);
+    } else {
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        hg += __shfl_xor_sync(0xffffffffu, hg, d);
+      }
     }
     const float r = rstd_in != nullptr ? rstd_in[route] : rsqrtf(ss * inv_d + eps);
     // <go, y> with y = h * r (the rounding of y to bf16 is ignored inside this inner product)
@@ -172,8 +231,8 @@ using namespace dm;
 
 extern "C" int dm_rmsnorm_combine_fwd(const void* h3, const void* scores, int scores_are_bf16, const void* ids,
                                       int ids_are_int64, const void* gamma, float gain_center, float eps,
-                                      int norm_is_bf16, void* out, float* rstd_out, int64_t T, int K, int64_t D,
-                                      void* save_base, const int64_t* save_offset, const int* save_cond,
+                                      int norm_is_bf16, int use_kahan, void* out, float* rstd_out, int64_t T, int K,
+                                      int64_t D, void* save_base, const int64_t* save_offset, const int* save_cond,
                                       int save_expect, void* stream) {
   if (!h3 || !scores || !ids || !out || T <= 0 || K <= 0 || K > kNormMaxK || D <= 0 || (D % 8) != 0) return kRcBadArg;
   const int vec = static_cast<int>(D / 8);
@@ -183,18 +242,18 @@ extern "C" int dm_rmsnorm_combine_fwd(const void* h3, const void* scores, int sc
     rmsnorm_combine_fwd_kernel<int64_t><<<blocks, 256, 0, st>>>(
         static_cast<const uint4*>(h3), scores, scores_are_bf16, static_cast<const int64_t*>(ids),
         static_cast<const uint4*>(gamma), gain_center, eps, norm_is_bf16, static_cast<uint4*>(out), rstd_out, T, K, vec,
-        static_cast<uint8_t*>(save_base), save_offset, save_cond, save_expect);
+        static_cast<uint8_t*>(save_base), save_offset, save_cond, save_expect, use_kahan ? 1 : 0);
   else
     rmsnorm_combine_fwd_kernel<int32_t><<<blocks, 256, 0, st>>>(
         static_cast<const uint4*>(h3), scores, scores_are_bf16, static_cast<const int32_t*>(ids),
         static_cast<const uint4*>(gamma), gain_center, eps, norm_is_bf16, static_cast<uint4*>(out), rstd_out, T, K, vec,
-        static_cast<uint8_t*>(save_base), save_offset, save_cond, save_expect);
+        static_cast<uint8_t*>(save_base), save_offset, save_cond, save_expect, use_kahan ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
                                       int ids_are_int64, const void* h3_base, const int64_t* h3_offset,
-                                      const float* rstd, float eps, int norm_is_bf16, void* grad_h3,
+                                      const float* rstd, float eps, int norm_is_bf16, int use_kahan, void* grad_h3,
                                       float* grad_scores, int64_t T, int K, int64_t D, void* stream) {
   if (!grad_out || !scores || !ids || !h3_base || !grad_h3 || T <= 0 || K <= 0 || D <= 0 || (D % 8) != 0)
     return kRcBadArg;
@@ -206,11 +265,11 @@ extern "C" int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, 
     rmsnorm_combine_bwd_kernel<int64_t><<<static_cast<int>(blocks), 256, 0, st>>>(
         static_cast<const uint4*>(grad_out), scores, scores_are_bf16, static_cast<const int64_t*>(ids),
         static_cast<const uint8_t*>(h3_base), h3_offset, rstd, eps, norm_is_bf16, static_cast<uint4*>(grad_h3),
-        grad_scores, T, K, vec);
+        grad_scores, T, K, vec, use_kahan ? 1 : 0);
   else
     rmsnorm_combine_bwd_kernel<int32_t><<<static_cast<int>(blocks), 256, 0, st>>>(
         static_cast<const uint4*>(grad_out), scores, scores_are_bf16, static_cast<const int32_t*>(ids),
         static_cast<const uint8_t*>(h3_base), h3_offset, rstd, eps, norm_is_bf16, static_cast<uint4*>(grad_h3),
-        grad_scores, T, K, vec);
+        grad_scores, T, K, vec, use_kahan ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
 }

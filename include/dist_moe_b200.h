@@ -303,18 +303,13 @@ int dm_gemm_blockscaled_swapped(int format, dm_operand a, dm_operand sfa, const 
  * E4M3 bytes ([rows, N/2]) and h2_sf the blocked E8M0 scales of 1 x 32 blocks, bit-identical to dm_quant_mxfp8_row
  * applied to the bf16 h2 the plain call writes; h2 itself is not written (the reference's
  * `..._fprop_swiglu_fwd_combine` producers quantise h2 in the same place, dist_moe/_blockscaled_ops.py:172-420).
- * 128 x 256 tiles only (dm_set_blockscaled_wide(1), the default). */
+ */
 int dm_gemm_blockscaled_swiglu_mxfp8(dm_operand a, dm_operand sfa, const void* w, const void* sfb, dm_operand h2_q,
                                      dm_operand h2_sf, const int32_t* expert_offsets, int e_local, int64_t max_rows,
                                      int64_t N, int64_t Kd, int clamped, float alpha, float limit, const int* cond,
                                      int num_sms, int* status, void* stream);
 
-/* Kernel selection for dm_gemm_blockscaled: non-zero (default) runs 128 x 256 output tiles (one 256-column
- * accumulator in TMEM, 3 or 4 stages of 48 KiB operands + scale atoms), zero runs the 128 x 128 tiles the
- * backward GEMMs use.  Returns the previous setting.  Results agree to fp32 accumulation order.  No
- * counterpart in the reference (tile geometry is chosen by BlockScaledKernelConfig, dist_moe/api.py:233-329). */
-int dm_set_blockscaled_wide(int enabled);
-int dm_blockscaled_wide_enabled(void); /* the current setting, without changing it */
+ /* the current setting, without changing it */
 
 /* MXFP8 training backward GEMMs (dist_moe/_blockscaled_ops.py: `dist_blockscaled_grouped_gemm_dgrad_dispatch`,
  * `..._dgrad_swiglu_bwd_combine`, `blockscaled_grouped_gemm_wgrad`; sequencing dist_moe/_blockscaled.py:2284-2512).
@@ -349,12 +344,12 @@ int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operan
  * ------------------------------------------------------------------------- */
 int dm_rmsnorm_combine_fwd(const void* h3, const void* scores, int scores_are_bf16, const void* ids,
                            int ids_are_int64, const void* gamma, float gain_center, float eps, int norm_is_bf16,
-                           void* out, float* rstd_out, int64_t T, int K, int64_t D, void* save_base,
+                           int use_kahan, void* out, float* rstd_out, int64_t T, int K, int64_t D, void* save_base,
                            const int64_t* save_offset, const int* save_cond, int save_expect, void* stream);
 int dm_rmsnorm_combine_bwd(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
                            int ids_are_int64, const void* h3_base, const int64_t* h3_offset, const float* rstd,
-                           float eps, int norm_is_bf16, void* grad_h3, float* grad_scores, int64_t T, int K,
-                           int64_t D, void* stream);
+                           float eps, int norm_is_bf16, int use_kahan, void* grad_h3, float* grad_scores, int64_t T,
+                           int K, int64_t D, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Block-scaled quantisers (dist_moe/_quantization.py:66-133 `quantize_for_format`;

@@ -20,15 +20,6 @@ def _nat():
     return _native
 
 
-@pytest.fixture(autouse=True, params=[1, 0], ids=["tiles128x256", "tiles128x128"])
-def tile_choice(request):
-    """Every test runs on the 128x256 kernel (the default) and on the 128x128 comparison kernel."""
-    nat = _nat()
-    previous = nat.lib.dm_set_blockscaled_wide(request.param)
-    yield request.param
-    nat.lib.dm_set_blockscaled_wide(previous)
-
-
 def _close(got, ref, what):
     got, ref = got.float(), ref.float()
     scale = ref.pow(2).mean().sqrt().item() + 1e-9
@@ -285,11 +276,9 @@ def test_blockscaled_wgrad(counts, M, N, fp32, acc):
         _close(got if fp32 else got.bfloat16(), ref, f"wgrad expert {e}")
 
 
-def test_swiglu_epilogue_that_quantises_h2_equals_gemm_then_row_quantiser(tile_choice):
+def test_swiglu_epilogue_that_quantises_h2_equals_gemm_then_row_quantiser():
     """dm_gemm_blockscaled_swiglu_mxfp8 writes the E4M3 bytes and scales that dm_quant_mxfp8_row produces from the
-    bf16 h2 of the plain SwiGLU call (128x256 tiles only)."""
-    if not tile_choice:
-        pytest.skip("the quantising epilogue exists on the 128x256 kernel only")
+    bf16 h2 of the plain SwiGLU call."""
     nat = _nat()
     torch.manual_seed(11)
     counts, K, F = [128, 384, 0, 256], 512, 320

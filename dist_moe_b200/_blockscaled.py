@@ -193,26 +193,34 @@ def quantize_nvfp4_weight(weight: torch.Tensor, *, fuse_swiglu: bool):
     return _quantize_weight(_as_enk(weight, fuse_swiglu), "nvfp4", True)
 
 
+def inference_layout(fmt: BlockScaledFormat, D: int, F: int, rows: int) -> dict:
+    """Byte offsets of the forward-only block-scaled operands for ``rows`` received rows, and their total: packed
+    rows and blocked scales of x and of h2, the NVFP4 per-row scales, and the dense SwiGLU buffers.  A static carve:
+    nothing in it depends on routing data, so the storage is fixed when the context is created (the role the
+    reference's Mega-inference operand envelope plays, dist_moe/_inference_memory.py:24-110)."""
+    a128 = lambda v: (v + 127) // 128 * 128  # noqa: E731
+    xq, xs = _geometry(fmt, D)
+    hq, hs = _geometry(fmt, F)
+    R = rows
+    out, off = {}, 0
+    for name, nbytes in (("x_q", R * xq), ("x_sf", _blocked_group_bytes(R, xs)), ("x_inv", R * 4), ("h_q", R * hq),
+                         ("h_sf", _blocked_group_bytes(R, hs)), ("h_inv", R * 4),
+                         ("dense", R * 2 * F * 2),      # h1 [R, 2F] (unfused) or h2 [R, F] (fused)
+                         ("h2_dense", R * F * 2)):      # only used by the unfused path
+        out[name] = off
+        off += a128(nbytes)
+    out["total"] = off + 256 * max(D, 2 * F) * 2
+    return out
+
+
 class _Layout:
     """Static carve of the scratch arena for the forward-only block-scaled path (capacity rows)."""
 
     def __init__(self, state):
         cfg, fmt = state.config, state.config.block_scaled.format
-        D, F, R = cfg.hidden_dim, cfg.intermediate_dim, state.capacity_rows
-        a128 = lambda v: (v + 127) // 128 * 128  # noqa: E731
         self.fp4 = fmt is BlockScaledFormat.NVFP4
-        xq, xs = _geometry(fmt, D)
-        hq, hs = _geometry(fmt, F)
-        off = 0
-        self.x_q, off = off, off + a128(R * xq)
-        self.x_sf, off = off, off + a128(_blocked_group_bytes(R, xs))
-        self.x_inv, off = off, off + a128(R * 4)
-        self.h_q, off = off, off + a128(R * hq)
-        self.h_sf, off = off, off + a128(_blocked_group_bytes(R, hs))
-        self.h_inv, off = off, off + a128(R * 4)
-        self.dense, off = off, off + a128(R * 2 * F * 2)   # h1 [R, 2F] (unfused) or h2 [R, F] (fused)
-        self.h2_dense, off = off, off + a128(R * F * 2)    # only used by the unfused path
-        self.total = off + 256 * max(D, 2 * F) * 2
+        for name, value in inference_layout(fmt, cfg.hidden_dim, cfg.intermediate_dim, state.capacity_rows).items():
+            setattr(self, name, value)
 
 
 def _workspace(state):

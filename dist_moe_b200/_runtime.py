@@ -98,6 +98,8 @@ class ContextState:
         self.block_scaled = config.block_scaled is not None
         self.m_multiple = 128 if self.block_scaled else 0
         self.capacity_rows = plan.total_scratch_capacity_rows
+        # static inference operands reserve scratch without going through the planner (dist_moe/api.py:1686-1693)
+        self.reserved_scratch_bytes = plan.inference_operand_bytes or 0
         with torch.cuda.device(device):
             self.routing = SymmetricBuffer(ROUTING_HEADER_BYTES + T * K * 2, device, group, ep_size, self.rank)
             self.dispatch = SymmetricBuffer(T * K * D * 2, device, group, ep_size, self.rank)
@@ -134,7 +136,7 @@ class ContextState:
         offs = [i * self.slot_bytes for i in range(n)] + [self.arena_bytes]
         self.buffer_offsets.copy_(torch.tensor(offs, dtype=torch.int64))
         self.saved_bytes.zero_()
-        peak = [self.slot_bytes] * n + [self.arena_bytes - n * self.slot_bytes]
+        peak = [self.slot_bytes] * n + [self.arena_bytes - n * self.slot_bytes - self.reserved_scratch_bytes]
         self.peak_min_free.copy_(torch.tensor(peak, dtype=torch.int64))
         self.moe_layer_id.zero_()
 

@@ -333,9 +333,10 @@ def _arena_sizing(config: Config, ep_size: int | None, factor: float | None = No
 def plan_memory(config: Config, ep_size: int, *, device: torch.device | str | int | None = None) -> MemoryPlan:
     """Resolve activation-slot, device-scratch and host-scratch sizes (dist_moe/api.py:875-1049).
 
-    The Mega-inference operand envelope and the VMM physical-section rounding of the
-    reference depend on its own kernels and allocator; they are left unresolved here
-    (``inference_operand_bytes`` and the ``vmm_*`` fields stay ``None``).
+    ``inference_operand_bytes`` is resolved under the reference's conditions (inference, block-scaled "mega"
+    pipeline, no VMM, a device or ``num_sms`` given; dist_moe/api.py:962-981) as the size of this library's static
+    operand carve, and the device scratch is raised to hold it.  The VMM physical-section rounding depends on the
+    allocator and is resolved by ``create_context``.
     """
     if ep_size <= 0:
         raise ValueError("ep_size must be positive")
@@ -386,6 +387,14 @@ def plan_memory(config: Config, ep_size: int, *, device: torch.device | str | in
         if slot > max_slot:
             logger.warning("activation_slot_bytes=%d exceeds the maximum useful %d bytes for this context", slot,
                            max_slot)
+    inference_operand_bytes = None
+    if (config.inference and config.block_scaled is not None and config.block_scaled.pipeline == "mega"
+            and config.vmm is None and (device is not None or config.num_sms is not None)):
+        from ._blockscaled import inference_layout
+
+        inference_operand_bytes = inference_layout(config.block_scaled.format, config.hidden_dim,
+                                                   config.intermediate_dim, sizing.capacity_rows)["total"]
+        device_scratch = max(device_scratch, _planning.align(inference_operand_bytes))
     total_act = num_slots * slot
     total_dev = total_act + device_scratch
     return MemoryPlan(
@@ -412,7 +421,7 @@ def plan_memory(config: Config, ep_size: int, *, device: torch.device | str | in
         vmm_host_section_bytes=None,
         vmm_device_scratch_section_bytes=None,
         vmm_padding_bytes=0,
-        inference_operand_bytes=None,
+        inference_operand_bytes=inference_operand_bytes,
     )
 
 

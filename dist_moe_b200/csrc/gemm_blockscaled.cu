@@ -98,14 +98,15 @@ __device__ __forceinline__ BsTile bs_decode(int tile, int& e, const int* tile_st
 // with few rows take the swapped-operand kernel instead (gemm_blockscaled_swapped.cu).
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kWdBN = 256;
-constexpr int kWdThreads = 352;  // TMA warp, MMA warp, eight epilogue warps, accumulator watcher
+constexpr int kWdThreads = 384;  // TMA warp, MMA warp, eight epilogue warps, accumulator watcher, scale copier
 constexpr uint32_t kWdBBytes = kWdBN * 128;                                   // 32 KiB
 constexpr uint32_t kWdStageFp4 = kBsABytes + kWdBBytes + 2048 + 4096;         // 54 KiB: 4 + 8 scale atoms
 constexpr uint32_t kWdStageFp8 = kBsABytes + kWdBBytes + 2048;                // 50 KiB: 1 + 2 scale atoms, padded
 constexpr int kWdStagesFp4 = 3;
 constexpr int kWdStagesFp8 = 4;
 constexpr int kWdMaxStages = 4;
-constexpr uint32_t kWdSfTmemBase = kWdBN;  // scale columns: two buffers of 64 columns after the accumulator
+constexpr uint32_t kWdSfTmemBase = kWdBN;  // scale columns: 64 per stage slot after the accumulator
+static_assert(kWdSfTmemBase + kWdMaxStages * 64 <= kBsTmemCols, "scale columns do not fit");
 constexpr size_t kWdSmemFp4 = kWdStagesFp4 * kWdStageFp4 + 8 * kStaging64Bytes + 1024;
 constexpr size_t kWdSmemFp8 = kWdStagesFp8 * kWdStageFp8 + 8 * kStaging64Bytes + 1024;
 
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
 
   __shared__ uint64_t full_bar[kWdMaxStages];
   __shared__ uint64_t empty_bar[kWdMaxStages];
+  __shared__ uint64_t sf_bar[kWdMaxStages];  // the stage's scale atoms are in TMEM
   __shared__ uint64_t tmem_full_bar;
   __shared__ uint64_t tmem_empty_bar;
   __shared__ uint32_t tmem_base_slot;
@@ -140,6 +142,7 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
     for (int s = 0; s < kWdMaxStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&sf_bar[s], p.fp4 ? 2 : 1);  // NVFP4: two copier threads share the stage's atoms
     }
     mbar_init(&tmem_full_bar, 1);
     mbar_init(&tmem_empty_bar, 8);
@@ -238,9 +241,7 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
       int stage = 0;
       uint32_t phase = 0;
       int e = 0, it = 0;
-      uint32_t kstep = 0;
       bool ok = true;
-      const uint32_t sf_bytes = atoms * 512;
       const int a_mn = p.mode == 2, b_mn = p.mode != 0;
       const uint32_t a_step = a_mn ? 4096u : 32u, b_step = b_mn ? 4096u : 32u;
       const uint32_t b_lbo = b_mn ? kWdBBytes / 2 : 16u;  // MN-major: the two 128-byte-wide halves are 16 KiB apart
@@ -253,20 +254,13 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
         ok = mbar_wait(&tmem_empty_bar, (it & 1u) ^ 1u, &abort_flag);  // the epilogue has drained the accumulator
         if (!ok) break;
         tcgen05_fence_after();
-        for (int kb = 0; kb < t.k_iters; ++kb, ++kstep) {
-          ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, &abort_flag) && mbar_wait(&sf_bar[stage], phase, &abort_flag);
           if (!ok) break;
+          tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * stage_bytes), b_addr = a_addr + kBsABytes;
-          const uint32_t ssa = b_addr + kWdBBytes, ssb = ssa + sf_bytes;
-          const uint32_t sfa_t = tmem_base + kWdSfTmemBase + (kstep & 1u) * 64u;
+          const uint32_t sfa_t = tmem_base + kWdSfTmemBase + stage * 64u;
           const uint32_t sfb_t = sfa_t + 16u;
-          // Scale columns: A atom a (K step a) at +4a; B atoms of the tile's lower and upper 128 columns side
-          // by side, 8 columns per K step.
-          for (int a = 0; a < atoms; ++a) {
-            tmem_cp_sf_atom(sfa_t + 4 * a, sf_smem_desc(ssa + a * 512));
-            tmem_cp_sf_atom(sfb_t + 8 * a, sf_smem_desc(ssb + a * 512));
-            tmem_cp_sf_atom(sfb_t + 8 * a + 4, sf_smem_desc(ssb + sf_bytes + a * 512));
-          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint64_t da = umma_smem_desc(a_addr + j * a_step, 16, 1024);
@@ -291,17 +285,53 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
       }
     }
     __syncwarp();
-  } else if (warp == 10) {
-    // ======================= accumulator watcher =======================
-    // Polls the accumulator-ready barrier for the epilogue warps and releases them through a hardware named
-    // barrier; it arrives for every tile, also after a timeout, so that no epilogue warp is left blocked.
+  } else if (warp == 11 || warp == 10) {
+    // ======================= scale copiers (the second one is also the accumulator watcher) =======================
+    // A thread issues a tcgen05 instruction every 50 to 100 cycles, and an NVFP4 stage needs twelve scale-atom
+    // copies next to its four MMAs; issued by one thread they cost more than the tensor pipe needs to run them.
+    // These two threads move every stage's atoms to the stage slot's TMEM columns and commit to a per-stage
+    // barrier the MMA thread waits on.  Columns: A atom a (K step a) at +4a; B atoms of the tile's lower and
+    // upper 128 columns side by side, 8 columns per K step.  The slot's previous MMAs are complete by then: the
+    // producer refilled the stage only after their commit released it.  NVFP4 has four atoms per stage and
+    // operand and each thread takes two; MXFP8 has one, taken by warp 11.
+    //
+    // Warp 10 then polls the accumulator-ready barrier for the epilogue warps and releases them through a hardware
+    // named barrier; it arrives for every tile, also after a timeout, so that no epilogue warp is left blocked.
+    const bool watcher = warp == 10;
+    const int a_lo = watcher ? 2 : 0, a_hi = p.fp4 ? a_lo + 2 : (watcher ? 0 : 1);
+    int stage = 0;
+    uint32_t phase = 0;
+    int e = 0, it = 0;
     bool ok = true;
-    int it = 0;
+    const uint32_t sf_bytes = atoms * 512;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      if (ok && lane == 0) ok = mbar_wait(&tmem_full_bar, it & 1u, &abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      asm volatile("bar.arrive %0, %1;" ::"r"(1 + (it & 1)), "r"(8 * 32 + 32) : "memory");
+      if (lane == 0 && a_hi > a_lo && ok) {
+        const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, &abort_flag);
+          if (!ok) break;
+          const uint32_t ssa = smem_u32(smem + stage * stage_bytes) + kBsABytes + kWdBBytes, ssb = ssa + sf_bytes;
+          const uint32_t sfa_t = tmem_base + kWdSfTmemBase + stage * 64u;
+          const uint32_t sfb_t = sfa_t + 16u;
+          for (int a = a_lo; a < a_hi; ++a) {
+            tmem_cp_sf_atom(sfa_t + 4 * a, sf_smem_desc(ssa + a * 512));
+            tmem_cp_sf_atom(sfb_t + 8 * a, sf_smem_desc(ssb + a * 512));
+            tmem_cp_sf_atom(sfb_t + 8 * a + 4, sf_smem_desc(ssb + sf_bytes + a * 512));
+          }
+          tcgen05_commit(&sf_bar[stage]);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (watcher) {
+        if (ok && lane == 0) ok = mbar_wait(&tmem_full_bar, it & 1u, &abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        asm volatile("bar.arrive %0, %1;" ::"r"(1 + (it & 1)), "r"(8 * 32 + 32) : "memory");
+      }
     }
+    __syncwarp();
   } else {
     // ======================= epilogue =======================
     // Eight warps: two per TMEM lane quadrant, each owning 128 of the tile's 256 columns.  A lane reads its own

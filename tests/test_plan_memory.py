@@ -82,3 +82,26 @@ def test_public_names_match_the_reference_surface():
         "create_context", "plan_memory", "prepare_block_scaled_weight", "routed_experts",
         "supports_fused_post_expert_rmsnorm",
     ])
+
+
+def test_mega_inference_plan_reserves_the_static_operand_carve():
+    """With a device or an SM count the plan of a Mega inference context names the bytes of the static operand
+    carve and holds them inside the device scratch (dist_moe/api.py:962-981); without either it stays unresolved."""
+    import dist_moe_b200 as dm
+    from dist_moe_b200._blockscaled import inference_layout
+
+    def cfg(**kw):
+        return dm.Config(max_num_local_input_tokens=128, hidden_dim=7168, intermediate_dim=2048, top_k=8,
+                         num_experts=256, max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0,
+                         block_scaled=dm.BlockScaledConfig(format=dm.BlockScaledFormat.NVFP4, pipeline="mega"), **kw)
+
+    assert dm.plan_memory(cfg(), 8).inference_operand_bytes is None
+    plan = dm.plan_memory(cfg(num_sms=148), 8)
+    want = inference_layout(dm.BlockScaledFormat.NVFP4, 7168, 2048, plan.device_scratch_capacity_rows)["total"]
+    assert plan.inference_operand_bytes == want
+    assert plan.device_scratch_bytes >= want and plan.total_device_buffer_bytes >= want
+    assert "physical Mega inference operands" in plan.explain()
+    staged = dm.Config(max_num_local_input_tokens=128, hidden_dim=7168, intermediate_dim=2048, top_k=8, num_experts=256,
+                       max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0, num_sms=148,
+                       block_scaled=dm.BlockScaledConfig(format=dm.BlockScaledFormat.NVFP4))
+    assert dm.plan_memory(staged, 8).inference_operand_bytes is None

@@ -115,7 +115,7 @@ int dm_route_counted(const uint64_t* routing_ptrs, const uint64_t* dispatch_ptrs
  *   - the shape must satisfy dm_route_workspace_words(T, ep, E) <= DM_ROUTE_STATIC_MAX_WORDS,
  *     otherwise the call returns DM_RC_TOO_LARGE and launches nothing;
  *   - the first call on each device looks up the array's device address (with that device
- *     current); make that first call outside any stream capture;
+ *     current);
  *   - the call itself performs no cudaMalloc/cudaFree and calls no allocating routine;
  *     inputs and outputs are still the caller's;
  *   - all calls on a device share the array.  Each call clears the part that must start

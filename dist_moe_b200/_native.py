@@ -103,6 +103,9 @@ _SIGNATURES = {
         [c_int, Operand, Operand, _P, _P, Operand, Operand, _P, Operand, _P, _P, _P, c_int, c_int64, c_int64, c_int64,
          c_int, c_int, c_float, c_float, _P, c_int, _P, _P],
     ),
+    "dm_vmm_granularity": (c_int, [c_int, _P]),
+    "dm_vmm_create": (c_int, [c_int, c_int, _P, _P, _P, _P]),
+    "dm_vmm_destroy": (c_int, [_P]),
     "dm_set_route_decode_kernel": (c_int, [c_int]),
     "dm_route_decode_kernel_enabled": (c_int, []),
     "dm_gemm_blockscaled_swiglu_mxfp8": (
@@ -180,7 +183,7 @@ def check(rc: int, what: str) -> None:
     if rc < 0:
         raise NativeError(f"{what}: {RC_NAMES.get(rc, rc)}")
     if rc >= 1000:
-        raise NativeError(f"{what}: cuTensorMapEncodeTiled failed with CUresult {rc - 1000}")
+        raise NativeError(f"{what}: a CUDA driver call failed with CUresult {rc - 1000}")
     raise NativeError(f"{what}: CUDA error {rc}")
 
 

@@ -105,8 +105,20 @@ class ContextState:
             self.dispatch = SymmetricBuffer(T * K * D * 2, device, group, ep_size, self.rank)
             self.combine = SymmetricBuffer(T * K * D * 2, device, group, ep_size, self.rank)
             guard = GUARD_ROWS * max(D, 2 * F) * 2
-            self.arena_bytes = plan.total_device_buffer_bytes
-            self.arena = torch.zeros(self.arena_bytes + guard, dtype=torch.uint8, device=device)
+            self.vmm_arena = None
+            if plan.vmm_granularity_bytes is not None:
+                # [device: slots | host: overflow scratch | device: hot scratch] in one virtual range
+                from ._vmm import VmmArena
+
+                self.vmm_arena = VmmArena(plan, device, guard)
+                self.arena_bytes = plan.total_virtual_bytes
+                self.arena = self.vmm_arena.tensor
+                self.hot_scratch_bytes = plan.vmm_device_scratch_section_bytes
+                self.host_scratch_bytes = plan.vmm_host_section_bytes
+            else:
+                self.arena_bytes = plan.total_device_buffer_bytes
+                self.arena = torch.zeros(self.arena_bytes + guard, dtype=torch.uint8, device=device)
+                self.hot_scratch_bytes = self.host_scratch_bytes = None
             n = plan.num_activation_slots
             self.num_slots = n
             self.slot_bytes = plan.activation_slot_bytes
@@ -174,9 +186,19 @@ class ContextState:
         min_free = float(peaks[n])
         slots = [float(self.slot_bytes - peaks[i]) for i in range(n)]
         overflow = min_free < 0 or any(peaks[i] < 0 for i in range(n))
-        info = ScratchInfo(scratch_min_free=min_free, scratch_size=scratch_size, scratch_max_used=scratch_size - min_free,
-                           device_scratch_size=scratch_size, device_scratch_used=scratch_size - min_free,
-                           host_scratch_size=None, host_scratch_used=None, slot_max_used=slots)
+        used = scratch_size - min_free
+        if self.hot_scratch_bytes is not None:
+            # scratch fills from the top: hot device section, then the host section, then the device bytes below it
+            hot, host = float(self.hot_scratch_bytes), float(self.host_scratch_bytes)
+            lower = max(0.0, scratch_size - hot - host)
+            device_size = hot + lower
+            device_used = min(used, hot) + max(0.0, used - hot - host)
+            host_size, host_used = host, min(max(0.0, used - hot), host)
+        else:
+            device_size, device_used, host_size, host_used = scratch_size, used, None, None
+        info = ScratchInfo(scratch_min_free=min_free, scratch_size=scratch_size, scratch_max_used=used,
+                           device_scratch_size=device_size, device_scratch_used=device_used,
+                           host_scratch_size=host_size, host_scratch_used=host_used, slot_max_used=slots)
         if overflow:
             raise RuntimeError(f"dist_moe_b200 activation buffer overflow: {info}")
         return info
@@ -203,6 +225,10 @@ class ContextState:
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
+        if getattr(self, "vmm_arena", None) is not None:
+            self.arena = None
+            self.vmm_arena.close()
+            self.vmm_arena = None
         self.arena = torch.empty(0, dtype=torch.uint8, device=self.device)
 
     # ---- barrier -------------------------------------------------------------

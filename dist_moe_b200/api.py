@@ -335,8 +335,8 @@ def plan_memory(config: Config, ep_size: int, *, device: torch.device | str | in
 
     ``inference_operand_bytes`` is resolved under the reference's conditions (inference, block-scaled "mega"
     pipeline, no VMM, a device or ``num_sms`` given; dist_moe/api.py:962-981) as the size of this library's static
-    operand carve, and the device scratch is raised to hold it.  The VMM physical-section rounding depends on the
-    allocator and is resolved by ``create_context``.
+    operand carve, and the device scratch is raised to hold it.  With ``Config.vmm``, host scratch and a device the
+    physical section sizes are resolved at the driver's granularity (dist_moe/api.py:1047-1109).
     """
     if ep_size <= 0:
         raise ValueError("ep_size must be positive")
@@ -397,7 +397,7 @@ def plan_memory(config: Config, ep_size: int, *, device: torch.device | str | in
         device_scratch = max(device_scratch, _planning.align(inference_operand_bytes))
     total_act = num_slots * slot
     total_dev = total_act + device_scratch
-    return MemoryPlan(
+    plan = MemoryPlan(
         balanced_recv_rows=config.max_num_local_input_tokens * config.top_k,
         device_scratch_capacity_rows=sizing.capacity_rows,
         total_scratch_capacity_rows=sizing.rows_at(total_factor),
@@ -423,6 +423,14 @@ def plan_memory(config: Config, ep_size: int, *, device: torch.device | str | in
         vmm_padding_bytes=0,
         inference_operand_bytes=inference_operand_bytes,
     )
+    if config.vmm is not None and host_scratch > 0 and device is not None:
+        from . import _vmm
+
+        dev = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        return _vmm.resolve_physical_plan(plan, _vmm.granularity(dev))
+    return plan
 
 
 # ---------------------------------------------------------------------------
@@ -516,17 +524,15 @@ def create_context(*, group: Any, config: Config, device: torch.device | str | i
     if config.num_experts % ep_size != 0:
         raise ValueError(
             f"num_experts={config.num_experts} must be divisible by the expert-parallel group size {ep_size}")
-    if config.vmm is not None:
-        raise NotImplementedError(
-            "host-backed VMM scratch is not implemented by dist_moe_b200; size device scratch with "
-            "device_scratch_capacity_factor instead")
     if device is None:
         dev = torch.device("cuda", torch.cuda.current_device())
     else:
         dev = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
     if dev.type != "cuda":
         raise ValueError(f"device must be CUDA, got {dev}")
-    plan = memory_plan if memory_plan is not None else plan_memory(config, ep_size)
+    plan = memory_plan if memory_plan is not None else plan_memory(config, ep_size, device=dev)
+    if config.vmm is not None and plan.host_scratch_bytes > 0 and plan.vmm_granularity_bytes is None:
+        raise ValueError("a memory plan with host scratch must be resolved for the device: plan_memory(..., device=...)")
     logger.info("%s", plan.explain())
     ctx = object.__new__(Context)
     ctx.group = group

@@ -421,6 +421,21 @@ int dm_gather_packed_rows(const int64_t* ptrs, const int32_t* num_rows, int64_t 
                           int64_t scale_cols, int has_inv, dm_operand q, dm_operand scales_blocked,
                           dm_operand scale_inv, const int* cond, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Host-backed overflow scratch (dist_moe/_vmm.py:149-427 `VMMRegion`): one contiguous virtual range whose
+ * sections are physical device memory or pinned host memory, readable and writable by `device`.
+ *   dm_vmm_granularity  the recommended physical granularity; section sizes must be multiples of it
+ *   dm_vmm_create       reserves the range, creates and maps one allocation per section (host sections on the
+ *                       GPU's NUMA node where the driver names one), grants access; returns the base address
+ *                       and an opaque handle.  On failure everything created so far is released.
+ *   dm_vmm_destroy      unmaps, releases, frees the range.  After a failure the handle stays valid for a retry.
+ * Positive return codes >= 1000 are 1000 + CUresult of the failing driver call.
+ * ------------------------------------------------------------------------- */
+int dm_vmm_granularity(int device, int64_t* granularity_bytes);
+int dm_vmm_create(int device, int num_sections, const int64_t* section_bytes, const int* section_is_host,
+                  uint64_t* base_out, void** region_out);
+int dm_vmm_destroy(void* region);
+
 #ifdef __cplusplus
 }
 #endif

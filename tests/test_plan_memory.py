@@ -105,3 +105,37 @@ def test_mega_inference_plan_reserves_the_static_operand_carve():
                        max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0, num_sms=148,
                        block_scaled=dm.BlockScaledConfig(format=dm.BlockScaledFormat.NVFP4))
     assert dm.plan_memory(staged, 8).inference_operand_bytes is None
+
+
+def test_vmm_physical_sections_follow_the_driver_granularity():
+    """Section arithmetic of a host-backed plan (dist_moe/api.py:1052-1109), with the granularity given."""
+    import dist_moe_b200 as dm
+    from dist_moe_b200 import _vmm
+
+    cfg = dm.Config(max_num_local_input_tokens=4096, hidden_dim=1024, intermediate_dim=1024, top_k=2, num_experts=8,
+                    max_moe_layers_per_activation_slot=2, activation_slot_capacity_factor=1.0,
+                    device_scratch_capacity_factor=1.0, vmm=dm.VmmConfig(total_scratch_capacity_factor=4.0))
+    logical = dm.plan_memory(cfg, 8)
+    assert logical.uses_host_scratch and logical.vmm_granularity_bytes is None
+    g = 2 * 1024 * 1024
+    plan = _vmm.resolve_physical_plan(logical, g)
+    up = lambda v: (v + g - 1) // g * g  # noqa: E731
+    assert plan.vmm_device_prefix_bytes == up(logical.total_activation_bytes)
+    assert plan.vmm_host_section_bytes == up(logical.host_scratch_bytes)
+    assert plan.vmm_device_scratch_section_bytes == up(logical.device_scratch_bytes)
+    assert plan.total_virtual_bytes == (plan.vmm_device_prefix_bytes + plan.vmm_host_section_bytes
+                                        + plan.vmm_device_scratch_section_bytes)
+    assert plan.vmm_padding_bytes == plan.total_virtual_bytes - logical.total_activation_bytes \
+        - logical.host_scratch_bytes - logical.device_scratch_bytes
+    # a range below 10 MiB is planned as the allocator's 20 MiB block, the slack going to the hot device scratch
+    small = dataclasses_replace(logical, total_activation_bytes=1 << 20, host_scratch_bytes=1 << 20,
+                                device_scratch_bytes=1 << 20)
+    tiny = _vmm.resolve_physical_plan(small, g)
+    assert tiny.total_virtual_bytes == 20 * 1024 * 1024
+    assert tiny.vmm_device_scratch_section_bytes == 20 * 1024 * 1024 - 2 * g
+
+
+def dataclasses_replace(obj, **kw):
+    import dataclasses
+
+    return dataclasses.replace(obj, **kw)

@@ -1208,7 +1208,7 @@ def run_micro(args):
         print(json.dumps({"micro": args.micro, "rows": qr, "cols": qc_cols, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6}),
               flush=True)
         return
-    if args.micro.startswith("bs-"):
+    if args.micro in ("bs-nvfp4", "bs-mxfp8"):
         # block-scaled forward GEMM (W13 with the SwiGLU epilogue) on synthetic quantised bytes: timing does not
         # depend on the values, scale bytes are 1.0 in their format
         fp4 = args.micro == "bs-nvfp4"
@@ -1228,6 +1228,26 @@ def run_micro(args):
             1 if fp4 else 0, op(qa), op(sa), qw.data_ptr(), sw.data_ptr(), none, op(hq), None, op(inv) if fp4 else none,
             einv.data_ptr() if fp4 else None, off.data_ptr(), e, rows, n, k, 1, 0, 1.0, 0.0, None, 0, status.data_ptr(), st)
         flops_bs = 2.0 * rows * n * k
+    if args.micro == "bs-decode":
+        # swapped-operand NVFP4 GEMM at a decode shape: 12 experts x 32 real rows inside 128-row groups, W13 of
+        # D=7168, F=2048 (176 MB of weights + 22 MB of scales per launch: more than L2, streamed once)
+        e, n, k, real = 12, 4096, 7168, 32
+        rows = e * 128
+        off = torch.arange(0, e + 1, dtype=torch.int32, device=dev) * 128
+        cnt = torch.full((e,), real, dtype=torch.int32, device=dev)
+        atoms = (k // 16 + 3) // 4
+        qa = torch.randint(0, 120, (rows + 256, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        qw = torch.randint(0, 120, (e * n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        sa = torch.full(((rows + 256) * atoms * 4,), 0x38, dtype=torch.uint8, device=dev)
+        sw = torch.full((e * n * atoms * 4,), 0x38, dtype=torch.uint8, device=dev)
+        inv = torch.ones(rows + 256, dtype=torch.float32, device=dev)
+        einv = torch.ones(e, dtype=torch.float32, device=dev)
+        hq = torch.zeros(rows + 8, n // 2, dtype=torch.bfloat16, device=dev)
+        calls[args.micro] = lambda: nat.lib.dm_gemm_blockscaled_swapped(
+            1, op(qa), op(sa), qw.data_ptr(), sw.data_ptr(), none, op(hq), None, op(inv), einv.data_ptr(), off.data_ptr(),
+            cnt.data_ptr(), e, rows, n, k, 1, 0, 1.0, 0.0, None, 0, status.data_ptr(), st)
+        flops_bs = 2.0 * e * real * n * k
+        stream_bytes = qw.numel() + sw.numel()
     fn = calls[args.micro]
     flops = flops_bs if args.micro.startswith("bs-") else 2.0 * rows * D * 2 * F
     for _ in range(2):
@@ -1240,8 +1260,11 @@ def run_micro(args):
     t.record()
     torch.cuda.synchronize()
     ms = s.elapsed_time(t) / args.steps
-    print(json.dumps({"micro": args.micro, "rows": rows, "e_local": e, "D": D, "F": F, "ms": ms,
-                      "tflops": flops / ms / 1e9, "status": status.tolist()[:2]}), flush=True)
+    line = {"micro": args.micro, "rows": rows, "e_local": e, "D": D, "F": F, "ms": ms, "tflops": flops / ms / 1e9,
+            "status": status.tolist()[:2]}
+    if args.micro == "bs-decode":
+        line["weight_stream_GBps"] = stream_bytes / ms / 1e6
+    print(json.dumps(line), flush=True)
     _ = none
 
 
@@ -1260,7 +1283,7 @@ def main():
                     help="gather routed rows with a separate kernel instead of inside the GEMM launches")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager routed_experts calls instead of CUDA-graph replays of the same step")
-    ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8", "quant-mxfp8"],
+    ap.add_argument("--micro", default=None, choices=["fprop", "dgrad", "wgrad", "bs-nvfp4", "bs-mxfp8", "bs-decode", "quant-mxfp8"],
                     help="time one grouped-GEMM arrangement alone on a reduced case (for profiler captures)")
     ap.add_argument("--workload", default="bf16-train", choices=["bf16-train", "mxfp8-train"] + sorted(INFERENCE_WORKLOADS),
                     help="bf16-train is the headline training layer; the others are forward-only inference layers")

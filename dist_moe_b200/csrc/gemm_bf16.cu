@@ -46,7 +46,7 @@ struct GemmParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
   CUtensorMap tm_b256;  // forward without SwiGLU pairing: one 256-row box per stage
-  CUtensorMap tm_c;     // wgrad: dW as [e_local][N][Kd], boxes of 32 rows x 64 bytes
+  CUtensorMap tm_c;     // wgrad: dW as [e_local][N][Kd], boxes of 16 rows x 128 bytes
   const int64_t* a_off;  // device byte offsets (may be null = 0)
   const int64_t* b_off;
   const int64_t* c_off;
@@ -489,41 +489,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kBN;
       if (kMode == kWgrad) {
-        for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += 32) {
-          uint32_t r[32];
+        // 128 bytes of output columns per trip (64 bf16 or 32 fp32).  The staging tile is laid out as a 16-row x
+        // 128-byte box in the 128-byte swizzle, so the warp's 32 rows go in two passes; one thread hands each
+        // box to the copy engine, which stores it or adds it to dW in L2 (accumulation rounds the fp32
+        // accumulator to the stored type first, then L2 adds whole 128-byte lines: no read round trip through
+        // the SM) and clips rows and columns past the matrix.
+        const int cols_per_trip = p.out_fp32 ? 32 : 64;
+        for (int c0 = half * (kBN / 2); c0 < (half + 1) * (kBN / 2); c0 += cols_per_trip) {
+          uint32_t r0[32], r1[32];
           if (t.k_iters > 0) {
-            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_32x32(taddr + c0, r0);
+            if (!p.out_fp32) tmem_ld_32x32(taddr + c0 + 32, r1);
             tmem_ld_wait();
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0u;
+            for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
           }
-          const int col = t.n_blk * kBN + c0;
-          // The staging tile is laid out as a 32-row x 64-byte box in the 64-byte swizzle: one thread
-          // hands it to the copy engine, which stores it or adds it to dW in L2 (accumulation rounds
-          // the fp32 accumulator to the stored type first, then L2 adds: no read round trip through
-          // the SM) and clips rows and columns past the matrix.
-          const int box_row = t.m_blk * kBM + quad * 32;
-          const bool box_ok = box_row < p.N;
+          const int cc = t.n_blk * kBN + c0;
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            if (!p.out_fp32 && sub == 1) break;
+          for (int pass = 0; pass < 2; ++pass) {
             if (lane == 0) bulk_wait_read();  // the engine has read the previous box out of the staging tile
             __syncwarp();
-            if (p.out_fp32) {
+            if ((lane >> 4) == pass) {
+              const int rr = lane & 15;
+              if (p.out_fp32) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                stage64_put(stg, lane, j,
-                            make_uint4(r[16 * sub + 4 * j], r[16 * sub + 4 * j + 1], r[16 * sub + 4 * j + 2],
-                                       r[16 * sub + 4 * j + 3]));
-            } else {
+                for (int j = 0; j < 8; ++j)
+                  stage_put(stg, rr, j, make_uint4(r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]));
+              } else {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
+                for (int j = 0; j < 4; ++j) {
+                  stage_put(stg, rr, j, pack8_bf16(r0 + 8 * j));
+                  stage_put(stg, rr, j + 4, pack8_bf16(r1 + 8 * j));
+                }
+              }
             }
             fence_proxy_async_smem();
             __syncwarp();
-            const int cc = col + (p.out_fp32 ? 16 * sub : 0);
-            if (lane == 0 && box_ok && cc < p.Kd) {
+            const int box_row = t.m_blk * kBM + quad * 32 + pass * 16;
+            if (lane == 0 && box_row < p.N && cc < p.Kd) {
               if (p.accumulate)
                 tma_reduce_add_3d(&p.tm_c, stg, cc, box_row, t.e);
               else

@@ -161,10 +161,11 @@ static inline int encode_out_3d(CUtensorMap* tm, void* base, int64_t groups, int
   const cuuint64_t esz = fp32 ? 4 : 2;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * esz, static_cast<cuuint64_t>(cols) * rows * esz};
-  cuuint32_t box[3] = {static_cast<cuuint32_t>(64 / esz), 32, 1};
+  // boxes of 16 rows x 128 bytes: a reduce-add or store then moves whole 128-byte lines of dW
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / esz), 16, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(tm, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kRcOk : 1000 + static_cast<int>(r);
 }

@@ -30,6 +30,7 @@ constexpr int kBsMaxGroups = 256;
 struct BsParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
+  CUtensorMap tm_c;  // weight gradient: dW as [e_local][rows][cols], boxes of 16 rows x 128 bytes
   const int64_t* a_off;
   const int64_t* sfa_off;
   const int64_t* c_off;
@@ -370,57 +371,57 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty_bar);  // accumulator handed back before the stores
-        const int out_row = t.m_blk * kBsBM + row_in_tile;
-        const int64_t row_elems = (static_cast<int64_t>(t.e) * p.N + out_row) * p.Kw;
-        const uint64_t my_row =
-            out_row < p.N ? reinterpret_cast<uint64_t>(p.c_base) + row_elems * (p.out_fp32 ? 4 : 2) : 0ull;
+        // 128 bytes of output columns per trip (64 bf16 or 32 fp32).  The staging tile is laid out as a 16-row x
+        // 128-byte box in the 128-byte swizzle, so the warp's 32 rows go in two passes; one thread hands each box
+        // to the copy engine, which stores it or adds it to dW in L2 in whole 128-byte lines and clips rows and
+        // columns past the matrix.
+        const int col0 = t.n_blk * kWdBN + half * (kWdBN / 2);
+        auto send = [&](int cc, int pass) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int box_row = t.m_blk * kBsBM + quad * 32 + pass * 16;
+          if (lane == 0 && box_row < p.N && cc < p.Kw) {
+            if (p.accumulate)
+              tma_reduce_add_3d(&p.tm_c, stg, cc, box_row, t.e);
+            else
+              tma_store_3d(&p.tm_c, stg, cc, box_row, t.e);
+            bulk_commit();
+          }
+        };
+        if (p.out_fp32) {
 #pragma unroll
-        for (int blk = 0; blk < 4; ++blk) {
-          uint32_t (&r)[32] = blk == 0 ? ra : (blk == 1 ? rb : (blk == 2 ? rc : rd));
-          const int col = t.n_blk * kWdBN + half * (kWdBN / 2) + 32 * blk;
-          if (p.out_fp32) {
+          for (int trip = 0; trip < 4; ++trip) {
+            uint32_t (&r)[32] = trip == 0 ? ra : (trip == 1 ? rb : (trip == 2 ? rc : rd));
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {  // 16 fp32 columns = 64 bytes per row
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                stage64_put(stg, lane, j,
-                            make_uint4(r[16 * sub + 4 * j], r[16 * sub + 4 * j + 1], r[16 * sub + 4 * j + 2],
-                                       r[16 * sub + 4 * j + 3]));
+            for (int pass = 0; pass < 2; ++pass) {
+              if (lane == 0) bulk_wait_read();  // the engine has read the previous box out of the staging tile
               __syncwarp();
+              if ((lane >> 4) == pass) {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int rr = i * 8 + (lane >> 2), j = lane & 3;
-                const uint4 v = stage64_get(stg, rr, j);
-                const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-                const int cc = col + 16 * sub + 4 * j;
-                if (rp != 0 && cc + 4 <= p.Kw) {
-                  const uint64_t dst = rp + static_cast<uint64_t>(cc) * 4;
-                  if (p.accumulate)
-                    red_add_f32x4(dst, v);
-                  else
-                    *reinterpret_cast<uint4*>(dst) = v;
+                for (int j = 0; j < 8; ++j)
+                  stage_put(stg, lane & 15, j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+              }
+              send(col0 + 32 * trip, pass);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int trip = 0; trip < 2; ++trip) {
+            uint32_t (&r0)[32] = trip == 0 ? ra : rc;
+            uint32_t (&r1)[32] = trip == 0 ? rb : rd;
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+              if (lane == 0) bulk_wait_read();
+              __syncwarp();
+              if ((lane >> 4) == pass) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  stage_put(stg, lane & 15, j, pack8_bf16(r0 + 8 * j));
+                  stage_put(stg, lane & 15, j + 4, pack8_bf16(r1 + 8 * j));
                 }
               }
-              __syncwarp();
+              send(col0 + 64 * trip, pass);
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) stage64_put(stg, lane, j, pack8_bf16(r + 8 * j));
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = i * 8 + (lane >> 2), j = lane & 3;
-              const uint4 v = stage64_get(stg, rr, j);
-              const uint64_t rp = __shfl_sync(0xffffffffu, my_row, rr);
-              if (rp != 0 && col + 8 * j + 8 <= p.Kw) {
-                const uint64_t dst = rp + static_cast<uint64_t>(col + 8 * j) * 2;
-                if (p.accumulate)
-                  red_add_bf16x8(dst, v);
-                else
-                  *reinterpret_cast<uint4*>(dst) = v;
-              }
-            }
-            __syncwarp();
           }
         }
         continue;
@@ -760,6 +761,8 @@ extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col
   p.sfa_base = static_cast<const uint8_t*>(sf_dy_col.base);
   p.sfb = static_cast<const uint8_t*>(sf_x_col.base);
   p.c_base = static_cast<uint8_t*>(dw);
+  rc = encode_out_3d(&p.tm_c, dw, e_local, M, N, dw_is_fp32 != 0);
+  if (rc != kRcOk) return rc;
   p.expert_offsets = expert_offsets;
   p.cond = cond;
   p.status = status;

@@ -70,18 +70,6 @@ __device__ __forceinline__ void tcgen05_commit_addr(uint32_t bar_addr) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
 
-// 16-byte fire-and-forget reductions performed by L2 (each output tile has one owner CTA).
-__device__ __forceinline__ void red_add_f32x4(uint64_t addr, uint4 v) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
-               : "memory");
-}
-__device__ __forceinline__ void red_add_bf16x8(uint64_t addr, uint4 v) {
-  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-
 // Bulk tensor store and reduce-add of one staged box (shared memory -> global), issued by one thread.  The
 // staged bytes must have been made visible to the async proxy (fence_proxy_async_smem by every writer, then
 // a barrier) and stay untouched until bulk_wait_read has returned.

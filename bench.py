@@ -440,9 +440,19 @@ def reference_blockscaled(args):
                 p13 = ref.prepare_block_scaled_weight(w13, policy, inference=True, fuse_swiglu=pipeline == "mega")
                 p2 = ref.prepare_block_scaled_weight(w2, policy, inference=True)
 
+                ropts = rmsnorm_options(ref, case)
+                if ropts is not None:
+                    try:  # the reference admits its fused RMSNorm for top_k 2 and 8 only
+                        with torch.no_grad():
+                            ref.routed_experts(x, ids, scores, p13, p2, ctx, options=ropts)
+                    except (ValueError, NotImplementedError, RuntimeError, AssertionError) as exc:
+                        tried.setdefault("notes", []).append(
+                            f"{pipeline}: fused RMSNorm rejected by the reference ({repr(exc)[:160]}); timed without it")
+                        ropts = None
+
                 def step():
                     with torch.no_grad():
-                        return ref.routed_experts(x, ids, scores, p13, p2, ctx)
+                        return ref.routed_experts(x, ids, scores, p13, p2, ctx, options=ropts)
             for _ in range(3):
                 step()
             torch.cuda.synchronize()
@@ -458,7 +468,7 @@ def reference_blockscaled(args):
             if ctx is not None:
                 ctx.close()
             torch.cuda.empty_cache()
-    ok = {k: v for k, v in tried.items() if "mean_ms" in v}
+    ok = {k: v for k, v in tried.items() if isinstance(v, dict) and "mean_ms" in v}
     if not ok:
         return None, tried, case
     best = min(ok, key=lambda k: ok[k]["mean_ms"])
@@ -839,11 +849,11 @@ def run_ours(args):
 
 
 INFERENCE_WORKLOADS = {
-    # name: (format, T, D, F, E, K, clamped SwiGLU, routing)
-    "nvfp4-decode": ("NVFP4", 128, 7168, 2048, 256, 8, False, "sigmoid"),
-    "nvfp4-prefill": ("NVFP4", 8192, 7168, 2048, 256, 8, False, "sigmoid"),
+    # name: (format, T, D, F, E, K, clamped SwiGLU, routing, fused post-expert RMSNorm)
+    "nvfp4-decode": ("NVFP4", 128, 7168, 2048, 256, 8, False, "sigmoid", False),
+    "nvfp4-prefill": ("NVFP4", 8192, 7168, 2048, 256, 8, False, "sigmoid", False),
     # the reference rejects D = F = 2880 for MXFP8 (dimensions must be multiples of 128); 2816 is the nearest legal shape
-    "mxfp8-infer": ("MXFP8_E4M3", 4096, 2816, 2816, 128, 4, True, "uniform"),
+    "mxfp8-infer": ("MXFP8_E4M3", 4096, 2816, 2816, 128, 4, True, "uniform", True),
 }
 
 
@@ -872,7 +882,7 @@ def mxfp8_train_case(args, rank, world, dev):
 
 def inference_case(args, rank, world, dev):
     """Inputs of a forward-only inference workload (shared by both arms)."""
-    fmt, Tn, Dn, Fn, En, Kn, clamped, routing = INFERENCE_WORKLOADS[args.workload]
+    fmt, Tn, Dn, Fn, En, Kn, clamped, routing, rmsnorm = INFERENCE_WORKLOADS[args.workload]
     if args.tokens:
         Tn = args.tokens
     if args.experts:
@@ -881,11 +891,17 @@ def inference_case(args, rank, world, dev):
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     x = torch.randn(Tn, Dn, device=dev, generator=g).bfloat16()
     logits = torch.randn(Tn, En, device=dev, generator=g)
-    top = torch.topk(logits, Kn)
+    if getattr(args, "routing", "config") == "hot":
+        # stress: half of every token's assignments go to the experts rank 0 owns at EP=8 (the first E/8)
+        hot, k_hot = max(Kn, En // 8), Kn // 2
+        a, b = torch.topk(logits[:, :hot], k_hot), torch.topk(logits[:, hot:], Kn - k_hot)
+        top_values, top_ids = torch.cat([a.values, b.values], 1), torch.cat([a.indices, b.indices + hot], 1)
+    else:
+        top_values, top_ids = torch.topk(logits, Kn)
     if routing == "sigmoid":   # sigmoid scores of the top-k logits, not renormalised
-        scores, ids = torch.sigmoid(top.values).float(), top.indices
+        scores, ids = torch.sigmoid(top_values).float(), top_ids
     else:                      # uniform random distinct experts, softmax-renormalised scores
-        scores, ids = torch.softmax(top.values, -1).float(), top.indices
+        scores, ids = torch.softmax(top_values, -1).float(), top_ids
     gw = torch.Generator(device=dev).manual_seed(2027 + rank)
 
     def weights():
@@ -893,8 +909,19 @@ def inference_case(args, rank, world, dev):
         yield (torch.randn(e_local, 2, Fn, Dn, device=dev, generator=gw) * 0.02).bfloat16()
         yield (torch.randn(e_local, Dn, Fn, device=dev, generator=gw) * 0.02).bfloat16()
 
-    return dict(fmt=fmt, T=Tn, D=Dn, F=Fn, E=En, K=Kn, e_local=e_local, clamped=clamped, x=x, ids=ids, scores=scores,
-                weights=weights)
+    return dict(fmt=fmt, T=Tn, D=Dn, F=Fn, E=En, K=Kn, e_local=e_local, clamped=clamped, rmsnorm=rmsnorm, x=x, ids=ids,
+                scores=scores, weights=weights,
+                routing=f"{routing} top-{Kn}" + (", half of the assignments on the first E/8 experts"
+                                                 if getattr(args, "routing", "config") == "hot" else ""))
+
+
+def rmsnorm_options(module, case):
+    """ExecutionOptions of an inference workload for either arm's package: the fused post-expert RMSNorm where the
+    configuration names one."""
+    if not case.get("rmsnorm"):
+        return None
+    post = module.RMSNormPostprocess(eps=1e-6, norm_output_dtype=torch.float32, output_dtype=torch.bfloat16)
+    return module.ExecutionOptions(experts_output_postprocess=post)
 
 
 def run_mxfp8_train(args, emit=True):
@@ -1086,17 +1113,18 @@ def run_inference(args, emit=True):
 
     from dist_moe_b200 import _native
 
+    opts = rmsnorm_options(dm, case)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side), torch.no_grad():
         for _ in range(3):
             l0 = _native.LAUNCHES[0]
-            dm.routed_experts(x, ids, scores, p13, p2, ctx)
+            dm.routed_experts(x, ids, scores, p13, p2, ctx, options=opts)
             launches_per_step = _native.LAUNCHES[0] - l0
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
     with torch.no_grad(), torch.cuda.graph(graph):
-        out = dm.routed_experts(x, ids, scores, p13, p2, ctx)
+        out = dm.routed_experts(x, ids, scores, p13, p2, ctx, options=opts)
     for _ in range(max(3, args.warmup)):
         graph.replay()
     ctx.check_status()
@@ -1138,7 +1166,9 @@ def run_inference(args, emit=True):
             "dtype": "e2m1 x e4m3 block scales" if fmt == "NVFP4" else "e4m3 x e8m0 block scales",
             "data": "synthetic (seeded N(0,1) tokens, N(0,0.02) weights quantised once, top-k router on N(0,1) logits)",
             "config": {"workload": f"{args.workload}: T={Tn} tokens/rank, D={Dn}, F={Fn}, E={En} (E_local={e_local}), "
-                                   f"K={Kn}, {'clamped' if clamped else 'plain'} SwiGLU, forward only",
+                                   f"K={Kn}, {'clamped' if clamped else 'plain'} SwiGLU"
+                                   f"{', fused post-expert RMSNorm' if case['rmsnorm'] else ''}, routing {case['routing']}"
+                                   ", forward only",
                        "l2": "no flush: the prepared weights of the experts hit exceed the 126 MB L2"
                        if weight_bytes > 126e6 else "weights of the experts hit fit in L2 between replays"},
             "gpu_launches": launches_per_step * args.steps, "step_mode": "cuda-graph replay", "clocks": clocks,
@@ -1288,6 +1318,9 @@ def main():
     ap.add_argument("--workload", default="bf16-train", choices=["bf16-train", "mxfp8-train"] + sorted(INFERENCE_WORKLOADS),
                     help="bf16-train is the headline training layer; the others are forward-only inference layers")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank of an inference workload (sweeps)")
+    ap.add_argument("--routing", default="config", choices=["config", "hot"],
+                    help="inference workloads: the configuration's router, or the stress where half of the assignments "
+                         "go to the experts rank 0 owns at EP=8")
     ap.add_argument("--experts", type=int, default=0, help="total experts of an inference workload (default: the config's)")
     args = ap.parse_args()
     if args.micro:

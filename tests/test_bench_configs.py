@@ -21,7 +21,7 @@ def test_inference_workloads_are_legal_configs(ep):
     import dist_moe_b200 as dm
 
     bench = _bench()
-    for name, (fmt, T, D, F, E, K, clamped, _routing) in bench.INFERENCE_WORKLOADS.items():
+    for name, (fmt, T, D, F, E, K, clamped, _routing, _rmsnorm) in bench.INFERENCE_WORKLOADS.items():
         extra = {"activation": "swiglu_clamped", "swiglu_limit": 7.0} if clamped else {}
         cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
                         max_moe_layers_per_activation_slot=1, inference=True, num_activation_slots=0,

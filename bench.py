@@ -442,12 +442,13 @@ def reference_blockscaled(args):
 
                 ropts = rmsnorm_options(ref, case)
                 if ropts is not None:
-                    try:  # the reference admits its fused RMSNorm for top_k 2 and 8 only
+                    try:  # the reference admits its fused RMSNorm for top_k 2 and 8 only, and its norm kernels need
+                        # a newer cutlass-dsl than some stacks carry
                         with torch.no_grad():
                             ref.routed_experts(x, ids, scores, p13, p2, ctx, options=ropts)
-                    except (ValueError, NotImplementedError, RuntimeError, AssertionError) as exc:
+                    except Exception as exc:  # noqa: BLE001 -- whatever the reason, time the layer without it
                         tried.setdefault("notes", []).append(
-                            f"{pipeline}: fused RMSNorm rejected by the reference ({repr(exc)[:160]}); timed without it")
+                            f"{pipeline}: fused RMSNorm not available in the reference ({repr(exc)[:160]}); timed without it")
                         ropts = None
 
                 def step():

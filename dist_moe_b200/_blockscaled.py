@@ -238,7 +238,10 @@ def _workspace(state):
 
 # Inference calls whose experts receive at most this many rows on average take the swapped-operand GEMMs (rows on
 # the MMA's N side in steps of 32); above it a 128-row tile is mostly real rows and the 128 x 256 kernel wins.
-SWAPPED_MAX_ROWS_PER_EXPERT = 48
+# Measured crossovers (whole layer, one B200): NVFP4 wins at 32 rows per expert and loses at 64, MXFP8 wins at 16 and
+# loses at 32 (its MMAs move twice the bytes per row).  ``None`` keeps the per-format value.
+SWAPPED_MAX_ROWS_PER_EXPERT = None
+_SWAPPED_MAX_ROWS = {BlockScaledFormat.NVFP4: 48, BlockScaledFormat.MXFP8_E4M3: 24}
 
 
 def _view(buf: torch.Tensor, offset: int) -> nat.Operand:
@@ -327,7 +330,8 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     row_inv = _view(buf, lay.x_inv) if lay.fp4 else none
     h2_quantised = False
     # few rows per expert (decode): weights on the MMA's M side, the rows on its N side
-    swapped = fused and ep * T * K <= SWAPPED_MAX_ROWS_PER_EXPERT * E
+    limit_rows = _SWAPPED_MAX_ROWS[fmt] if SWAPPED_MAX_ROWS_PER_EXPERT is None else SWAPPED_MAX_ROWS_PER_EXPERT
+    swapped = fused and ep * T * K <= limit_rows * E
     if swapped:
         h2_dense = lay.dense
         nat.check(nat.lib.dm_gemm_blockscaled_swapped(f, _view(buf, lay.x_q), _view(buf, lay.x_sf),

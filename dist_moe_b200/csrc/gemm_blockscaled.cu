@@ -57,6 +57,7 @@ struct BsParams {
   uint8_t* hsf_base;
   const int64_t* hsf_off;
   int h_atoms;
+  int direct_store;  // NVFP4 SwiGLU forward without staging tiles (four stages)
   const int64_t* b_off;
   const int64_t* sfb_off;
   ActParams act;
@@ -109,6 +110,11 @@ constexpr int kWdMaxStages = 4;
 constexpr uint32_t kWdSfTmemBase = kWdBN;  // scale columns: 64 per stage slot after the accumulator
 static_assert(kWdSfTmemBase + kWdMaxStages * 64 <= kBsTmemCols, "scale columns do not fit");
 constexpr size_t kWdSmemFp4 = kWdStagesFp4 * kWdStageFp4 + 8 * kStaging64Bytes + 1024;
+// NVFP4 forward with the SwiGLU epilogue and no h1 output: every lane stores its own 64 bytes of h2 per block
+// straight from registers, the staging tiles go, and a fourth stage fits.  Three 54 KiB stages do not cover the load
+// latency plus the scale-copy phase; the stores of this form are less coalesced but run while the next tile's MMAs do.
+constexpr int kWdStagesFp4Direct = 4;
+constexpr size_t kWdSmemFp4Direct = kWdStagesFp4Direct * kWdStageFp4 + 1024;
 constexpr size_t kWdSmemFp8 = kWdStagesFp8 * kWdStageFp8 + 8 * kStaging64Bytes + 1024;
 
 __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const __grid_constant__ BsParams p) {
@@ -131,7 +137,7 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
   const int n_tiles = p.mode == 2 ? (p.Kw + kWdBN - 1) / kWdBN : (p.N + kWdBN - 1) / kWdBN;
   const int wgrad_m_tiles = (p.N + kBsBM - 1) / kBsBM;
   const int atoms = p.fp4 ? 4 : 1;  // scale atoms per stage and 128 rows
-  const int stages = p.fp4 ? kWdStagesFp4 : kWdStagesFp8;
+  const int stages = p.fp4 ? (p.direct_store ? kWdStagesFp4Direct : kWdStagesFp4) : kWdStagesFp8;
   const uint32_t stage_bytes = p.fp4 ? kWdStageFp4 : kWdStageFp8;
 
   for (int i = threadIdx.x; i <= p.e_local; i += blockDim.x) {
@@ -511,6 +517,14 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
             }
             continue;
           }
+          if (p.direct_store) {
+            if (my_h2 != 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (f0 + 8 * j + 8 <= F) *reinterpret_cast<uint4*>(my_h2 + static_cast<uint64_t>(f0 + 8 * j) * 2) = zv[j];
+            }
+            continue;
+          }
 #pragma unroll
           for (int which = 0; which < 3; ++which) {
             if (which > 0 && p.c_base == nullptr) break;
@@ -592,10 +606,12 @@ static int bs_launch(const BsParams& p, int num_sms, cudaStream_t st) {
   static PerDeviceOnce wide_attr_set;
   const int rc = once_per_device(wide_attr_set, [] {
     return static_cast<int>(cudaFuncSetAttribute(blockscaled_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(kWdSmemFp8 > kWdSmemFp4 ? kWdSmemFp8 : kWdSmemFp4)));
+                                                 static_cast<int>(kWdSmemFp4Direct)));
   });
   if (rc != 0) return rc;
-  blockscaled_wide_kernel<<<grid, kWdThreads, p.fp4 ? kWdSmemFp4 : kWdSmemFp8, st>>>(p);
+  static_assert(kWdSmemFp4Direct >= kWdSmemFp4 && kWdSmemFp4Direct >= kWdSmemFp8, "largest shared-memory request");
+  const size_t smem = p.fp4 ? (p.direct_store ? kWdSmemFp4Direct : kWdSmemFp4) : kWdSmemFp8;
+  blockscaled_wide_kernel<<<grid, kWdThreads, smem, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -644,6 +660,7 @@ extern "C" int dm_gemm_blockscaled(int format, dm_operand a, dm_operand sfa, con
   p.k_iters = static_cast<int>(row_bytes / 128);
   p.fp4 = fp4;
   p.swiglu = swiglu_interleaved ? 1 : 0;
+  p.direct_store = (fp4 && swiglu_interleaved && !c.base) ? 1 : 0;
   p.act = ActParams{clamped, alpha, limit};
   return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
 }

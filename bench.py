@@ -226,6 +226,66 @@ def base_line(args, world):
 REFERENCE_DIR = ROOT / "baseline" / "_ref"
 
 
+def pipelined_e2e(dev, pinned, statics, run_step, out_host):
+    """End-to-end step for either arm: every step copies its inputs from pinned host memory and its output back.
+    Host->device and device->host copies run on a stream each (the link is full duplex) with two staging buffers,
+    so the upload of step i+1 and the download of step i-1 overlap the kernels of step i.  Returns (step, drain)."""
+    x_pin, ids_pin, scores_pin = pinned
+    x_static, ids_static, scores_static = statics
+    copy_stream = torch.cuda.Stream(device=dev)
+    down_stream = torch.cuda.Stream(device=dev)
+    stage_in = [(torch.empty_like(x_static), torch.empty_like(ids_static), torch.empty_like(scores_static))
+                for _ in range(2)]
+    stage_out = [torch.empty(out_host.shape, dtype=out_host.dtype, device=dev) for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_free = [torch.cuda.Event() for _ in range(2)]
+    state = {"k": 0, "primed": False}
+
+    def upload(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(in_free[slot])  # the step that last read this staging buffer has finished
+            xb, ib, sb = stage_in[slot]
+            xb.copy_(x_pin, non_blocking=True)
+            ib.copy_(ids_pin, non_blocking=True)
+            sb.copy_(scores_pin, non_blocking=True)
+            in_ready[slot].record(copy_stream)
+
+    def step():
+        main = torch.cuda.current_stream(dev)
+        k = state["k"]
+        slot = k & 1
+        if not state["primed"]:
+            for ev in in_free + out_free:
+                ev.record(main)
+            upload(slot)
+            state["primed"] = True
+        upload(slot ^ 1)                   # next step's inputs travel while this step computes
+        main.wait_event(in_ready[slot])
+        xb, ib, sb = stage_in[slot]
+        x_static.copy_(xb, non_blocking=True)
+        ids_static.copy_(ib, non_blocking=True)
+        scores_static.copy_(sb, non_blocking=True)
+        in_free[slot].record(main)
+        out = run_step()
+        main.wait_event(out_free[slot])    # the device->host copy that last read this output buffer is done
+        stage_out[slot].copy_(out.detach(), non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(down_stream):
+            down_stream.wait_event(done)
+            out_host.copy_(stage_out[slot], non_blocking=True)
+            out_free[slot].record(down_stream)
+        state["k"] = k + 1
+
+    def drain():
+        torch.cuda.current_stream(dev).wait_stream(copy_stream)
+        torch.cuda.current_stream(dev).wait_stream(down_stream)
+
+    return step, drain
+
+
+
 def reference_gpu_step_times(args):
     """Time the unmodified reference (installed under baseline/_ref) on GPU 0 through its own public API:
     ``dist_moe.routed_experts`` forward + backward on this benchmark's inputs with all 64 experts on one rank.
@@ -298,20 +358,21 @@ def reference_gpu_step_times(args):
                 return out_static
             return step()
 
-        def run_e2e():
-            x.copy_(x_pin, non_blocking=True)
-            ids.copy_(ids_pin, non_blocking=True)
-            scores.copy_(scores_pin, non_blocking=True)
-            out_host.copy_(run_step().detach(), non_blocking=True)
+        # the same pipelined harness as this repository's arm: copies on a second stream, two staging buffers
+        run_e2e, drain_e2e = pipelined_e2e(dev, (x_pin, ids_pin, scores_pin), (x, ids, scores), run_step, out_host)
 
-        def timed(fn):
+        def timed(fn, drain=None):
             for _ in range(2):
                 fn()
+            if drain is not None:
+                drain()
             torch.cuda.synchronize()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             for _ in range(args.steps):
                 fn()
+            if drain is not None:
+                drain()
             e.record()
             torch.cuda.synchronize()
             return s.elapsed_time(e) / args.steps
@@ -321,7 +382,7 @@ def reference_gpu_step_times(args):
         time.sleep(0.3)
         sampler.mark()
         ms = timed(run_step)
-        e2e_ms = timed(run_e2e)
+        e2e_ms = timed(run_e2e, drain_e2e)
         sampler.mark()
         clocks = sampler.stop()
         ctx.close()
@@ -688,54 +749,9 @@ def run_ours(args):
     ctx.check_status()
 
     # ---- end to end: every step copies its inputs from pinned host memory and its output back, all inside
-    # the timed region.  Copies run on a second stream with two staging buffers, so the host->device copy of
-    # step i+1 and the device->host copy of step i-1 overlap the kernels of step i.
-    copy_stream = torch.cuda.Stream(device=dev)
-    stage_in = [(torch.empty_like(x), torch.empty_like(ids), torch.empty_like(scores)) for _ in range(2)]
-    stage_out = [torch.empty(T, D, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    in_ready = [torch.cuda.Event() for _ in range(2)]
-    in_free = [torch.cuda.Event() for _ in range(2)]
-    out_free = [torch.cuda.Event() for _ in range(2)]
-    e2e_state = {"k": 0, "primed": False}
-
-    def upload(slot):
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(in_free[slot])  # the step that last read this staging buffer has finished
-            xb, ib, sb = stage_in[slot]
-            xb.copy_(x_pin, non_blocking=True)
-            ib.copy_(ids_pin, non_blocking=True)
-            sb.copy_(scores_pin, non_blocking=True)
-            in_ready[slot].record(copy_stream)
-
-    def step_e2e():
-        main = torch.cuda.current_stream(dev)
-        k = e2e_state["k"]
-        slot = k & 1
-        if not e2e_state["primed"]:
-            for ev in in_free + out_free:
-                ev.record(main)
-            upload(slot)
-            e2e_state["primed"] = True
-        upload(slot ^ 1)                   # next step's inputs travel while this step computes
-        main.wait_event(in_ready[slot])
-        xb, ib, sb = stage_in[slot]
-        x_static.copy_(xb, non_blocking=True)
-        ids_static.copy_(ib, non_blocking=True)
-        scores_static.copy_(sb, non_blocking=True)
-        in_free[slot].record(main)
-        out = run_step()
-        main.wait_event(out_free[slot])    # the device->host copy that last read this output buffer is done
-        stage_out[slot].copy_(out.detach(), non_blocking=True)
-        done = torch.cuda.Event()
-        done.record(main)
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(done)
-            out_host.copy_(stage_out[slot], non_blocking=True)
-            out_free[slot].record(copy_stream)
-        e2e_state["k"] = k + 1
-
-    def drain_e2e():
-        torch.cuda.current_stream(dev).wait_stream(copy_stream)
+    # the timed region (copies pipelined on a second stream; the reference arm uses the same harness)
+    step_e2e, drain_e2e = pipelined_e2e(dev, (x_pin, ids_pin, scores_pin), (x_static, ids_static, scores_static),
+                                        run_step, out_host)
 
     for _ in range(2):
         step_e2e()

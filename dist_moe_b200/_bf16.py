@@ -54,6 +54,9 @@ _gemm_wgrad = _profiled(nat.lib.dm_gemm_wgrad)
 # Fused dispatch pulls the routed rows inside the W13 / W2-dgrad GEMM launches (gather warps overlap the peer
 # transfer with the tensor cores).  With False the rows are gathered by a separate kernel first.
 FUSED_DISPATCH = True
+# The plain backward reads saved expert outputs where they were saved (chosen on the device) instead of copying
+# them back into the communication buffer first.  False restores the copy.
+READ_SAVED_H3_IN_PLACE = True
 
 
 def _dispatch_fprop(state, ptrs, a_op_off, w, c_op, h2_op, c, N, Kd, fuse, act, condp, what):
@@ -262,8 +265,11 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
         _gemm_fprop(_op(state, bo[2:3]), w2.data_ptr(), _none(), _none(), c.sct.data_ptr(),
                                         c.offsets.data_ptr(), el, c.max_rows, D, F, 0, 0, 1.0, 0.0, cond.data_ptr(),
                                         state.num_sms, status, st, what="gemm_fprop(w2 recompute)")
-        nat.check(nat.lib.dm_cond_copy(arena, fs[4:5].data_ptr(), state.combine.local().data_ptr(), None,
-                                       T * K * D * 2, cond.data_ptr(), 0, st), "dm_cond_copy(load h3)")
+        # Saved path: the fused RMSNorm backward works on the expert outputs in place in the communication buffer,
+        # so they are copied back there; the plain backward reads them where they were saved (selected on the device).
+        if is_norm or not READ_SAVED_H3_IN_PLACE:
+            nat.check(nat.lib.dm_cond_copy(arena, fs[4:5].data_ptr(), state.combine.local().data_ptr(), None,
+                                           T * K * D * 2, cond.data_ptr(), 0, st), "dm_cond_copy(load h3)")
         state.barrier(state.combine, cond)
     span.__exit__(None, None, None)
     span = record_function("dist_moe_backward")
@@ -278,11 +284,18 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     elif is_callback:
         hooks.postprocess_backward(state, c, grad_out, scores, ids, grad_scores)
     else:
-        nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(),
-                                                 int(scores.dtype == torch.bfloat16), ids.data_ptr(),
-                                                 int(ids.dtype == torch.int64), combine if need_scores else None,
-                                                 None, combine, nat.ptr(grad_scores), T, K, D, st),
-                  "dm_broadcast_and_scale")
+        if need_scores and READ_SAVED_H3_IN_PLACE:
+            nat.check(nat.lib.dm_broadcast_and_scale_select(grad_out.data_ptr(), scores.data_ptr(),
+                                                            int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                                            int(ids.dtype == torch.int64), arena, fs[4:5].data_ptr(),
+                                                            combine, cond.data_ptr(), combine, nat.ptr(grad_scores), T,
+                                                            K, D, st), "dm_broadcast_and_scale")
+        else:
+            nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(),
+                                                     int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                                     int(ids.dtype == torch.int64), combine if need_scores else None,
+                                                     None, combine, nat.ptr(grad_scores), T, K, D, st),
+                      "dm_broadcast_and_scale")
     state.barrier(state.combine)
     # ---- W2: input gradient and weight gradient ----------------------------------
     if FUSED_DISPATCH:

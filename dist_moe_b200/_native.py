@@ -92,6 +92,7 @@ _SIGNATURES = {
     "dm_swiglu_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_float, c_float, _P]),
     "dm_scale_and_sum": (c_int, [_P, _P, c_int, _P, c_int, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int, _P]),
     "dm_broadcast_and_scale": (c_int, [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, c_int64, c_int, c_int64, _P]),
+    "dm_broadcast_and_scale_select": (c_int, [_P, _P, c_int, _P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P]),
     "dm_zero_padded_rows": (c_int, [_P, _P, c_int, c_int64, c_int, c_int64, _P]),
     "dm_gemm_blockscaled": (
         c_int,

@@ -170,10 +170,12 @@ template <typename IdT>
 __global__ void __launch_bounds__(256) broadcast_and_scale_kernel(const uint4* __restrict__ grad_out,
                                                                   const void* scores, int scores_are_bf16,
                                                                   const IdT* __restrict__ ids, const uint8_t* h3_base,
-                                                                  const int64_t* h3_offset, uint4* grad_h3,
+                                                                  const int64_t* h3_offset, const uint8_t* h3_alt,
+                                                                  const int* use_alt, uint4* grad_h3,
                                                                   float* grad_scores, int64_t T, int K,
                                                                   int vec_per_row) {
   const uint4* h3 = h3_base ? reinterpret_cast<const uint4*>(h3_base + (h3_offset ? *h3_offset : 0)) : nullptr;
+  if (h3_alt != nullptr && use_alt != nullptr && *use_alt != 0) h3 = reinterpret_cast<const uint4*>(h3_alt);
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int64_t routes = T * K;
@@ -303,9 +305,10 @@ extern "C" int dm_scale_and_sum(const void* h3, const void* scores, int scores_a
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int dm_broadcast_and_scale(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
-                                      int ids_are_int64, const void* h3_base, const int64_t* h3_offset, void* grad_h3,
-                                      float* grad_scores, int64_t T, int K, int64_t D, void* stream) {
+static int broadcast_and_scale_launch(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
+                                      int ids_are_int64, const void* h3_base, const int64_t* h3_offset,
+                                      const void* h3_alt, const int* use_alt, void* grad_h3, float* grad_scores,
+                                      int64_t T, int K, int64_t D, void* stream) {
   if (!grad_out || !scores || !ids || !grad_h3 || T <= 0 || K <= 0 || D <= 0 || (D % 8) != 0) return kRcBadArg;
   const int vec = static_cast<int>(D / 8);
   const int blocks = grid_for(T * K * 32, 256, grid_cap(16));
@@ -313,10 +316,32 @@ extern "C" int dm_broadcast_and_scale(const void* grad_out, const void* scores, 
   if (ids_are_int64)
     broadcast_and_scale_kernel<int64_t><<<blocks, 256, 0, st>>>(
         static_cast<const uint4*>(grad_out), scores, scores_are_bf16, static_cast<const int64_t*>(ids),
-        static_cast<const uint8_t*>(h3_base), h3_offset, static_cast<uint4*>(grad_h3), grad_scores, T, K, vec);
+        static_cast<const uint8_t*>(h3_base), h3_offset, static_cast<const uint8_t*>(h3_alt), use_alt,
+        static_cast<uint4*>(grad_h3), grad_scores, T, K, vec);
   else
     broadcast_and_scale_kernel<int32_t><<<blocks, 256, 0, st>>>(
         static_cast<const uint4*>(grad_out), scores, scores_are_bf16, static_cast<const int32_t*>(ids),
-        static_cast<const uint8_t*>(h3_base), h3_offset, static_cast<uint4*>(grad_h3), grad_scores, T, K, vec);
+        static_cast<const uint8_t*>(h3_base), h3_offset, static_cast<const uint8_t*>(h3_alt), use_alt,
+        static_cast<uint4*>(grad_h3), grad_scores, T, K, vec);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_broadcast_and_scale(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
+                                      int ids_are_int64, const void* h3_base, const int64_t* h3_offset, void* grad_h3,
+                                      float* grad_scores, int64_t T, int K, int64_t D, void* stream) {
+  return broadcast_and_scale_launch(grad_out, scores, scores_are_bf16, ids, ids_are_int64, h3_base, h3_offset, nullptr,
+                                    nullptr, grad_h3, grad_scores, T, K, D, stream);
+}
+
+// The same with the expert outputs read from one of two places chosen on the device: `h3_alt` when *use_alt != 0
+// (they were recomputed into the communication buffer), else h3_base + *h3_offset (they were saved in the slot).
+// Saves the copy of the saved outputs back into the communication buffer.
+extern "C" int dm_broadcast_and_scale_select(const void* grad_out, const void* scores, int scores_are_bf16,
+                                             const void* ids, int ids_are_int64, const void* h3_base,
+                                             const int64_t* h3_offset, const void* h3_alt, const int* use_alt,
+                                             void* grad_h3, float* grad_scores, int64_t T, int K, int64_t D,
+                                             void* stream) {
+  if (!h3_base || !h3_alt || !use_alt) return kRcBadArg;
+  return broadcast_and_scale_launch(grad_out, scores, scores_are_bf16, ids, ids_are_int64, h3_base, h3_offset, h3_alt,
+                                    use_alt, grad_h3, grad_scores, T, K, D, stream);
 }

@@ -207,6 +207,13 @@ int dm_scale_and_sum(const void* h3, const void* scores, int scores_are_bf16, co
 int dm_broadcast_and_scale(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
                            int ids_are_int64, const void* h3_base, const int64_t* h3_offset, void* grad_h3,
                            float* grad_scores, int64_t T, int K, int64_t D, void* stream);
+/* dm_broadcast_and_scale with the expert outputs read from `h3_alt` when *use_alt != 0 (recomputed into the
+ * communication buffer), else from h3_base + *h3_offset (saved in the activation slot): the choice the planner
+ * made on the device, without copying the saved outputs back first. */
+int dm_broadcast_and_scale_select(const void* grad_out, const void* scores, int scores_are_bf16, const void* ids,
+                                  int ids_are_int64, const void* h3_base, const int64_t* h3_offset, const void* h3_alt,
+                                  const int* use_alt, void* grad_h3, float* grad_scores, int64_t T, int K, int64_t D,
+                                  void* stream);
 /* Zero the rows of a bf16 [T, K, D] route tensor whose expert id is negative, before a Python callback reads it
  * (dist_moe/kernels/triton/conditional_copy.py:215-235 `zero_out_padded_rows_`, 364-380 its kernel). */
 int dm_zero_padded_rows(void* routes_TKD, const void* ids, int ids_are_int64, int64_t T, int K, int64_t D, void* stream);

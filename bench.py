@@ -761,6 +761,11 @@ def run_ours(args):
     sampler.mark()
     clocks = sampler.stop() if rank == 0 else None  # samples of the two timed regions
     ctx.check_status()
+    # the same copies with no layer step between them: what the host side alone sustains with all ranks copying
+    idle_out = out_static if out_static is not None else torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+    copy_step, copy_drain = pipelined_e2e(dev, (x_pin, ids_pin, scores_pin), (x_static, ids_static, scores_static),
+                                          lambda: idle_out, out_host)
+    copies_ms = timed(copy_step, args.steps, copy_drain)
 
     # ---- GEMM timing pass: the same K steps once more, eager, every grouped-GEMM launch bracketed by CUDA events
     _bf16.PROFILE = []
@@ -824,6 +829,9 @@ def run_ours(args):
             "e2e": {"value": world * T / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": x_pin.numel() * 2 + ids_pin.numel() * 8 + scores_pin.numel() * 4,
                     "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / args.steps,
+                    "copies_only_ms_per_step": copies_ms / args.steps,
+                    "copies_only_GBps_per_rank_each_way": (x_pin.numel() * 2 + ids_pin.numel() * 8
+                                                           + scores_pin.numel() * 4) / (copies_ms / args.steps) / 1e6,
                     "host_numa_node_rank0": numa_node},
             "gpu_launches": launches,
             "step_mode": "cuda-graph replay" if graph is not None else "eager",

@@ -40,7 +40,7 @@ from torch.profiler import record_function
 
 from . import _native as nat
 from ._execution import ExecutionOptions, PreparedWeight, RMSNormPostprocess
-from .formats import BlockScaledFormat
+from .formats import BlockScaledFormat, format_constants
 
 
 def _fmt_id(fmt: BlockScaledFormat) -> int:
@@ -52,6 +52,14 @@ def _geometry(fmt: BlockScaledFormat, dim: int) -> tuple[int, int]:
     if fmt is BlockScaledFormat.NVFP4:
         return dim // 2, dim // 16
     return dim, dim // 32
+
+
+def planner_storage(fmt: BlockScaledFormat) -> list[int]:
+    """Storage geometry the arena planner sizes bundles with (dist_moe/_activation_buffer.py:958-1075
+    ``BlockscaledStorageConfig``): [operand element bytes, values per element, scale bytes, row-scale storage
+    multiple, per-row global-scale bytes, scale vector]."""
+    ob, vpe, sb, vec, gs = format_constants(fmt)
+    return [ob, vpe, sb, 4, gs, vec]
 
 
 def packed_row_stride(fmt: BlockScaledFormat, dim: int) -> int:

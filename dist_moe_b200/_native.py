@@ -86,6 +86,15 @@ _SIGNATURES = {
         [_P] * 10 + [c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, _P, _P],
     ),
     "dm_plan_bwd_bf16": (c_int, [_P] * 9 + [c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "dm_plan_fwd_blockscaled": (
+        c_int,
+        [_P] * 12 + [c_int, c_int64, c_int, c_int64, c_int64, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_int, _P, _P],
+    ),
+    "dm_plan_bwd_blockscaled": (
+        c_int,
+        [_P] * 10 + [c_int, c_int64, c_int, c_int64, c_int64, _P, c_int64, c_int64, c_int, c_int, c_int, _P, _P],
+    ),
     "dm_gather_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int64, _P, _P]),
     "dm_cond_copy": (c_int, [_P, _P, _P, _P, c_int64, _P, c_int, _P]),
     "dm_swiglu_fwd": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_float, c_float, _P, c_float, _P, _P]),

@@ -160,6 +160,42 @@ int dm_plan_bwd_bf16(const int32_t* recv_rows, const int32_t* per_rank, int64_t*
                      int* status, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Activation-arena planner, block-scaled paths
+ * (dist_moe/_activation_buffer.py:2108-2315 `_get_blockscaled_forward_plan` / `_get_blockscaled_backward_plan`;
+ * kernels dist_moe/_activation_buffer_planner_kernel.py:293-647 and 651-1065).
+ * Same state tensors as the BF16 planner.  What is placed are bundles: quantised data immediately followed by its
+ * scale factors; row bundles feed the forward / input-gradient GEMMs, column bundles the weight-gradient GEMMs.
+ * `storage` (host int[6]) = {operand element bytes, values per storage element, scale element bytes,
+ * row-scale storage multiple, per-row global-scale bytes, scale vector length} (the reference's
+ * BlockscaledStorageConfig, dist_moe/_activation_buffer.py:958-1075): MXFP8 {1,1,1,4,0,32}, NVFP4 {1,2,1,4,4,16}.
+ *   fwd_offsets[10] = {x, 0, h1, 0, h3, x_row, x_col, h2_row, h2_col, slot selector} (entry 9 is recorded so that
+ *                      the backward rewinds the slot the forward used);
+ *   fwd_activation_offsets[2*9]: groups {W13 dispatch, W2 combine} of
+ *                      {a_q, b_q, c, a_scale, b_scale, source_x, source_y, col_q, col_scale}; -1 = not present;
+ *   bwd_offsets[16] = {0|x_gathered, h1, 0|h2, grad_h2, 0|grad_h3_gathered, 0|grad_h1, x_row, x_col, h2_row, h2_col,
+ *                      grad_h3_row, grad_h3_col, dxy_row, dxy_col, x_row global scales, h2_row global scales};
+ *   bwd_activation_offsets[6*9]: groups {recompute dispatch, recompute combine, W2 dgrad, W2 wgrad, W13 dgrad,
+ *                      W13 wgrad}.
+ * per_rank_snapshot (optional) receives a copy of per_rank.  Rows above capacity_rows set
+ * DM_STATUS_CAPACITY_EXCEEDED, an overflowing slot or scratch region DM_STATUS_ARENA_OVERFLOW (the reference
+ * asserts on the device).
+ * ------------------------------------------------------------------------- */
+int dm_plan_fwd_blockscaled(const int32_t* recv_rows, const int32_t* per_rank, int32_t* per_rank_snapshot,
+                            int64_t* saved_bytes_per_rank, int64_t* buffer_offsets, int64_t* peak_min_free,
+                            uint8_t* need_recompute, int32_t* recompute_cond, int64_t* fwd_offsets,
+                            int64_t* fwd_activation_offsets, const int64_t* slot_selector, int64_t* moe_layer_id,
+                            int ep, int64_t num_tokens, int K, int64_t D, int64_t F, const int* storage,
+                            int64_t capacity_rows, int64_t slot_bytes, int num_slots, int num_moe_layers, int mega,
+                            int inference_mode, int scratch_only, int native_backward, int interleaved_fc13,
+                            int* status, void* stream);
+int dm_plan_bwd_blockscaled(const int32_t* recv_rows, const int32_t* per_rank, int64_t* saved_bytes_per_rank,
+                            int64_t* buffer_offsets, int64_t* peak_min_free, const uint8_t* need_recompute,
+                            const int64_t* fwd_offsets, int64_t* bwd_offsets, int64_t* bwd_activation_offsets,
+                            int64_t* moe_layer_id, int ep, int64_t num_tokens, int K, int64_t D, int64_t F,
+                            const int* storage, int64_t capacity_rows, int64_t slot_bytes, int num_slots, int mega,
+                            int native_backward, int* status, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Row gather (the gather half of dist_moe/kernels/dist_grouped_gemm.py:1148-1237
  * `dist_grouped_gemm_fprop_dispatch` and 1441-1489 `..._dgrad_dispatch`):
  *   dst[r, :] = *(ptrs[r])   for r < *num_rows, a zero row where ptrs[r] == 0.

@@ -7,9 +7,10 @@ Run where a checkout of the reference is available and pass its location:
 What runs, unmodified, from the reference:
 * ``dist_moe.plan_memory`` (pure Python) -> ``plan_memory.json``;
 * the Triton routing kernels (gather / split / prefix / combine,
-  ``dist_moe/kernels/triton/dist_dispatch_routing_kernel.py``) and the BF16 planner
-  kernels (``dist_moe/_activation_buffer_planner_kernel.py``) under Triton's CPU
-  interpreter (``TRITON_INTERPRET=1``) -> ``routing_*.npz``, ``planner_bf16.json``.
+  ``dist_moe/kernels/triton/dist_dispatch_routing_kernel.py``) and the BF16 and block-scaled
+  planner kernels (``dist_moe/_activation_buffer_planner_kernel.py``) under Triton's CPU
+  interpreter (``TRITON_INTERPRET=1``) -> ``routing_*.npz``, ``planner_bf16.json``,
+  ``planner_blockscaled.json``.
 
 Quantised bytes and floating-point outputs come from the reference's GPU kernels run on a B200 instead:
 see ``gen_golden_gpu.py`` in this directory.
@@ -303,13 +304,125 @@ def gen_planner(ref):
     print("planner_bf16.json:", len(out), "scenarios")
 
 
+# name: (format, EP, T, K, D, F, slots, layers, slot factor, flags, ops); ops as in PLANNER_SCENARIOS.  The slot
+# factor decides which scenarios save (1.0) and which recompute (small); flags are the kernel's constexpr switches.
+BLOCKSCALED_PLANNER_SCENARIOS = {
+    "mxfp8_saved": ("MXFP8_E4M3", 2, 64, 2, 256, 128, 1, 1, 1.0, {},
+                    [("f", 0, 256, [128, 128], False), ("b", 0)]),
+    "mxfp8_recompute": ("MXFP8_E4M3", 2, 64, 2, 256, 128, 1, 1, 0.25, {},
+                        [("f", 0, 256, [150, 106], False), ("b", 0)]),
+    "mxfp8_mixed_stack": ("MXFP8_E4M3", 4, 32, 4, 512, 256, 1, 3, 0.3, {},
+                          [("f", 0, 512, [100, 140, 160, 112], False), ("f", 0, 384, [33, 120, 150, 81], False),
+                           ("f", 0, 640, [160, 160, 160, 160], False), ("b", 2), ("b", 1), ("b", 0)]),
+    "mxfp8_two_slots_scratch_only": ("MXFP8_E4M3", 2, 48, 2, 384, 256, 2, 2, 1.0, {},
+                                     [("f", 0, 256, [96, 96], False), ("f", 1, 128, [70, 26], False),
+                                      ("f", 1, 256, [128, 100], True), ("f", 1, 256, [60, 130], False), ("b", 3),
+                                      ("b", 1), ("b", 0)]),
+    "mxfp8_mega": ("MXFP8_E4M3", 2, 64, 2, 256, 384, 1, 2, 0.22, {"mega": True},
+                   [("f", 0, 256, [128, 100], False), ("f", 0, 384, [200, 150], False), ("b", 1), ("b", 0)]),
+    "mxfp8_native_backward": ("MXFP8_E4M3", 2, 64, 2, 256, 128, 1, 2, 0.3, {"native_backward": True},
+                              [("f", 0, 256, [128, 128], False), ("f", 0, 256, [90, 140], False), ("b", 1), ("b", 0)]),
+    "nvfp4_saved_and_recompute": ("NVFP4", 2, 64, 4, 512, 256, 1, 2, 0.35, {},
+                                  [("f", 0, 384, [180, 190], False), ("f", 0, 512, [256, 250], False), ("b", 1),
+                                   ("b", 0)]),
+    "nvfp4_inference": ("NVFP4", 2, 64, 4, 512, 256, 0, 1, None, {"inference_mode": True},
+                        [("f", 0, 384, [180, 190], True)]),
+    "nvfp4_inference_interleaved_mega": ("NVFP4", 2, 64, 4, 512, 256, 0, 1, None,
+                                         {"inference_mode": True, "interleaved_fc13": True, "mega": True},
+                                         [("f", 0, 256, [128, 120], True)]),
+    "mxfp8_inference_interleaved_mega": ("MXFP8_E4M3", 2, 64, 4, 512, 256, 0, 1, None,
+                                         {"inference_mode": True, "interleaved_fc13": True, "mega": True},
+                                         [("f", 0, 256, [128, 120], True)]),
+}
+
+
+def gen_planner_blockscaled(ref):
+    import numpy as np
+    import torch
+    import triton.language as tl
+    from triton.runtime.interpreter import TensorHandle
+
+    import dist_moe
+    from dist_moe import _activation_buffer_planner_kernel as P
+
+    _shim(P, np, tl, TensorHandle)
+    storages = {"MXFP8_E4M3": [1, 1, 1, 4, 0, 32], "NVFP4": [1, 2, 1, 4, 4, 16]}
+    out = {}
+    for name, (fmt, EP, T, K, D, F, slots, layers, factor, flags, ops) in BLOCKSCALED_PLANNER_SCENARIOS.items():
+        inference = bool(flags.get("inference_mode"))
+        kw = dict(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=4 * EP,
+                  max_moe_layers_per_activation_slot=layers, num_activation_slots=slots,
+                  device_scratch_capacity_factor=float(EP), inference=inference,
+                  # the reference's Config admits NVFP4 for inference only: a training scenario takes its slot and
+                  # arena sizes from the MXFP8 plan and still runs the kernels with the NVFP4 storage geometry
+                  block_scaled=dist_moe.BlockScaledConfig(format=getattr(dist_moe.BlockScaledFormat,
+                                                                         fmt if inference else "MXFP8_E4M3"),
+                                                          pipeline="mega" if flags.get("mega") else "staged"))
+        if factor is not None:
+            kw["activation_slot_capacity_factor"] = factor
+        plan = dist_moe.plan_memory(dist_moe.Config(**kw), EP)
+        slot_bytes, arena, capacity = plan.activation_slot_bytes, plan.total_device_buffer_bytes, \
+            plan.total_scratch_capacity_rows
+        st = storages[fmt]
+        geometry = dict(element_size=2, operand_element_size=st[0], operand_values_per_storage_element=st[1],
+                        scale_element_size=st[2], row_scale_storage_multiple=st[3],
+                        row_global_scale_element_size=st[4], sf_vec_size=st[5])
+        i64 = lambda v: torch.tensor(v, dtype=torch.int64)  # noqa: E731
+        buffer_offsets = i64([i * slot_bytes for i in range(slots)] + [arena])
+        saved = torch.zeros(max(1, slots * EP), dtype=torch.int64)
+        peak = i64([slot_bytes] * slots + [arena - slots * slot_bytes])
+        layer = torch.zeros(max(1, slots), dtype=torch.int64)
+        mega, native = bool(flags.get("mega")), bool(flags.get("native_backward"))
+        steps, fwd_records = [], []
+        for op in ops:
+            if op[0] == "f":
+                _, slot, R, per_rank, scratch_only = op
+                need = torch.zeros(1, dtype=torch.bool)
+                cond = torch.zeros(1, dtype=torch.int32)
+                offsets = torch.zeros(9, dtype=torch.int64)
+                table = torch.zeros(18, dtype=torch.int64)
+                sel = i64([slot])
+                P._triton_get_blockscaled_forward_plan[(1,)](
+                    torch.tensor([R], dtype=torch.int32), torch.tensor(per_rank, dtype=torch.int32), None, saved,
+                    buffer_offsets, peak, need, cond, offsets, table, EP=EP, num_tokens=T, topk=K, **geometry,
+                    hidden_dim=D, intermediate_dim=F, capacity_rows=capacity, microbatch_id_ptr=sel,
+                    activation_slot_bytes=slot_bytes, num_activation_slots=slots, moe_layer_id_ptr=layer,
+                    num_moe_layers=layers, mega=mega, inference_mode=inference,
+                    scratch_only=bool(scratch_only) and not inference, native_backward=native,
+                    interleaved_fc13=bool(flags.get("interleaved_fc13")))
+                rec = dict(op="f", slot=slot, R=R, per_rank=per_rank, scratch_only=bool(scratch_only),
+                           need=bool(need[0]), cond=int(cond[0]), offsets=offsets.tolist(), table=table.tolist())
+                fwd_records.append(rec)
+            else:
+                f = fwd_records[op[1]]
+                fo = i64(f["offsets"])
+                offsets = torch.zeros(16, dtype=torch.int64)
+                table = torch.zeros(54, dtype=torch.int64)
+                P._triton_get_blockscaled_backward_plan[(1,)](
+                    torch.tensor([f["R"]], dtype=torch.int32), torch.tensor(f["per_rank"], dtype=torch.int32),
+                    buffer_offsets, peak, torch.tensor([f["need"]]), fo[0:1], fo[2:3], fo[6:7], fo[8:9], fo[5:6],
+                    fo[7:8], saved, offsets, table, EP=EP, num_tokens=T, topk=K, **geometry, hidden_dim=D,
+                    intermediate_dim=F, capacity_rows=capacity, microbatch_id_ptr=i64([f["slot"]]),
+                    activation_slot_bytes=slot_bytes, num_activation_slots=slots, moe_layer_id_ptr=layer, mega=mega,
+                    native_backward=native)
+                rec = dict(op="b", of=op[1], offsets=offsets.tolist(), table=table.tolist())
+            rec["state"] = dict(buffer_offsets=buffer_offsets.tolist(), saved=saved.tolist(), peak=peak.tolist(),
+                                layer=layer.tolist())
+            steps.append(rec)
+        out[name] = dict(format=fmt, storage=st, EP=EP, T=T, K=K, D=D, F=F, slots=slots, layers=layers,
+                         slot_bytes=slot_bytes, arena_bytes=arena, capacity_rows=capacity, flags=flags, steps=steps)
+    (HERE / "planner_blockscaled.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+    print("planner_blockscaled.json:", len(out), "scenarios")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("DIST_MOE_REFERENCE", "reference"))
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
-    steps = {"plan": gen_plan_memory, "routing": gen_routing, "planner": gen_planner}
+    steps = {"plan": gen_plan_memory, "routing": gen_routing, "planner": gen_planner,
+             "planner_blockscaled": gen_planner_blockscaled}
     for name, fn in steps.items():
         if not args.only or name in args.only.split(","):
             fn(args.reference)

@@ -987,6 +987,7 @@ def run_mxfp8_train(args, emit=True):
     w13.grad, w2.grad = torch.zeros_like(w13), torch.zeros_like(w2)
     cfg = dm.Config(max_num_local_input_tokens=Tn, hidden_dim=Dn, intermediate_dim=Fn, top_k=Kn, num_experts=En,
                     max_moe_layers_per_activation_slot=1, block_scaled=dm.BlockScaledConfig(),
+                    activation_slot_capacity_factor=1.0 if world == 1 else min(float(world), 1.25),
                     device_scratch_capacity_factor=factor)
     ctx = dm.create_context(group=group, config=cfg, device=dev)
     opts = dm.ExecutionOptions(inplace_wgrad_accum=True)
@@ -1055,6 +1056,8 @@ def run_mxfp8_train(args, emit=True):
         setattr(_native.lib, n, saved[n])
     breakdown = [[n[3:], round(a0.elapsed_time(a1) * 1e3, 1)] for n, a0, a1 in events]
     rows = int(padded) if world == 1 else None
+    last = getattr(ctx._state, "last_train_call", None)  # what the device planner decided for the layer
+    decision = None if last is None else ("recompute" if bool(last.need.item()) else "saved")
     line = None
     if rank == 0:
         line = ({
@@ -1065,7 +1068,8 @@ def run_mxfp8_train(args, emit=True):
             "config": {"workload": f"mxfp8-train: T={Tn} tokens/rank, D={Dn}, F={Fn}, E={En} (E_local={e_local}), K={Kn}, "
                                    f"plain SwiGLU, fwd+bwd, prepared weights, in-place wgrad accumulation",
                        "l2": "no flush: weights and routed activations exceed the 126 MB L2",
-                       "capacity_factor": factor},
+                       "capacity_factor": factor, "activation_slot_capacity_factor": cfg.activation_slot_capacity_factor,
+                       "planner_decision": decision},
             "gpu_launches": launches, "step_mode": "cuda-graph replay" if graph is not None else "eager", "clocks": clocks,
             "padded_rows_busiest_rank": rows,
             "flops_per_step_rank0_balanced": 18.0 * Tn * Kn * Dn * Fn,

@@ -482,7 +482,242 @@ def _training_weights(w13_param, w2_param, p13, p2, cfg):
 
 class _TrainCall:
     __slots__ = ("T", "R", "offsets", "recv", "fwd", "bwd", "sct", "h1", "x_col", "x_col_sf", "h2_col", "h2_col_sf",
-                 "h3", "p13", "p2", "rstd")
+                 "h3", "p13", "p2", "rstd", "planned", "per_rank", "need", "cond", "fwd_state", "fwd_table")
+
+
+# MXFP8 training keeps its activations in the context's arena, placed by the device planner (saved bundles in the
+# selected activation slot, transient ones in the shared scratch, save-or-recompute decided on the device from every
+# rank's row counts: dist_moe/_blockscaled.py:1150-1420, 2284-2512).  Contexts without activation slots and calls that
+# ask for the SwiGLU clip counters (which need a dense h2 the plan has no room for) use per-call tensors instead.
+PLANNED_ARENA = True
+
+# groups of the planner's offset tables, nine entries each
+_A_Q, _B_Q, _C, _A_SF, _B_SF, _SRC_X, _SRC_Y, _COL_Q, _COL_SF = range(9)
+
+
+def _route_training(state, x, ids, options, c: "_TrainCall"):
+    """publish -> barrier -> routing tables (rows of every expert padded to 128)."""
+    cfg = state.config
+    D, K, E = cfg.hidden_dim, cfg.top_k, cfg.num_experts
+    T, dev, el, ep = x.shape[0], x.device, state.e_local, state.ep
+    st, status = nat.stream_ptr(), state.status.data_ptr()
+    nat.check(nat.lib.dm_publish(x.data_ptr(), ids.data_ptr(), int(ids.dtype == torch.int64),
+                                 state.dispatch.local().data_ptr(), state.routing.local().data_ptr(), T, D, K, E,
+                                 int(options.validate_expert_ids), status, st), "dm_publish")
+    state.barrier(state.dispatch)
+    size = max((ep * T * min(K, el) + el * 127 + 127) // 128 * 128, 128)
+    c.T = T
+    c.R = min(size, state.capacity_rows // 128 * 128)
+    counts = torch.empty(el, dtype=torch.int32, device=dev)
+    c.per_rank = torch.empty(ep, dtype=torch.int32, device=dev)
+    c.offsets = torch.empty(el + 1, dtype=torch.int32, device=dev)
+    c.fwd = torch.empty(size, dtype=torch.int64, device=dev)
+    c.bwd = torch.empty(size, dtype=torch.int64, device=dev)
+    c.sct = torch.empty(size, dtype=torch.int64, device=dev)
+    stride = D * 2
+    nat.check(nat.lib.dm_route(state.routing.peer_ptrs.data_ptr(), state.dispatch.peer_ptrs.data_ptr(),
+                               state.combine.peer_ptrs.data_ptr(), state.rank, ep, T, K, E, stride, stride, stride, 128,
+                               state.capacity_rows, size, counts.data_ptr(), c.per_rank.data_ptr(),
+                               c.offsets.data_ptr(), c.fwd.data_ptr(), c.bwd.data_ptr(), c.sct.data_ptr(),
+                               state.route_workspace.data_ptr(), state.route_workspace_words, status, st),
+              nat.route_call_name(ep, T, el))
+    c.recv = c.offsets[el:]
+
+
+def _storage_array(state):
+    import ctypes
+
+    arr = getattr(state, "_planner_storage", None)
+    if arr is None:
+        arr = (ctypes.c_int * 6)(*planner_storage(state.config.block_scaled.format))
+        state._planner_storage = arr
+    return arr
+
+
+def _mxfp8_forward_planned(state, x, ids, scores, p13, p2, options, need_h3: bool):
+    cfg = state.config
+    D, F, K = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k
+    T, dev, el, ep = x.shape[0], x.device, state.e_local, state.ep
+    st, status = nat.stream_ptr(), state.status.data_ptr()
+    clamped = 1 if cfg.activation == "swiglu_clamped" else 0
+    alpha, limit = float(cfg.swiglu_alpha), float(cfg.swiglu_limit)
+    c = _TrainCall()
+    c.planned, c.p13, c.p2 = True, p13, p2
+    c.h1 = c.x_col = c.x_col_sf = c.h2_col = c.h2_col_sf = c.h3 = None
+    _route_training(state, x, ids, options, c)
+    R, recv = c.R, c.recv.data_ptr()
+    c.need = torch.empty(1, dtype=torch.uint8, device=dev)
+    c.cond = torch.empty(1, dtype=torch.int32, device=dev)
+    c.fwd_state = torch.empty(10, dtype=torch.int64, device=dev)  # [x, -, h1, -, h3, x_row, x_col, h2_row, h2_col, slot]
+    c.fwd_table = torch.empty(18, dtype=torch.int64, device=dev)
+    nat.check(nat.lib.dm_plan_fwd_blockscaled(
+        recv, c.per_rank.data_ptr(), None, state.saved_bytes.data_ptr(), state.buffer_offsets.data_ptr(),
+        state.peak_min_free.data_ptr(), c.need.data_ptr(), c.cond.data_ptr(), c.fwd_state.data_ptr(),
+        c.fwd_table.data_ptr(), state.slot_selector.data_ptr(), state.moe_layer_id.data_ptr(), ep,
+        cfg.max_num_local_input_tokens, K, D, F, _storage_array(state), state.capacity_rows, state.slot_bytes,
+        state.num_slots, state.num_layers_in_slot, 0, 0, 0, 0, 0, status, st), "dm_plan_fwd_blockscaled")
+    fs, ft = c.fwd_state, c.fwd_table
+    A = lambda table, group, entry: state.arena_operand(table[group * 9 + entry:group * 9 + entry + 1])  # noqa: E731
+    none = nat.Operand(None, 0, None)
+    arena = state.arena.data_ptr()
+    # a layer that will be recomputed keeps only its dense input
+    nat.check(nat.lib.dm_cond_copy(x.data_ptr(), None, arena, fs[0:1].data_ptr(), T * D * 2, c.cond.data_ptr(), 1, st),
+              "dm_cond_copy(save x)")
+    # dispatch: the routed rows are pulled through the pointer table by the quantiser itself
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol_gather_at(c.fwd.data_ptr(), recv, R, D, A(ft, 0, _A_Q), A(ft, 0, _A_SF),
+                                                      A(ft, 0, _COL_Q), A(ft, 0, _COL_SF), None, st),
+              "dm_quant_mxfp8_rowcol_gather_at(x)")
+    nat.check(nat.lib.dm_gemm_blockscaled(0, A(ft, 0, _A_Q), A(ft, 0, _A_SF), p13.fprop_data.data_ptr(),
+                                          p13.fprop_scale.data_ptr(), A(ft, 0, _C), none, None, none, None,
+                                          c.offsets.data_ptr(), el, R, 2 * F, D, 0, 0, 1.0, 0.0, None, state.num_sms,
+                                          status, st), "dm_gemm_blockscaled(w13)")
+    nat.check(nat.lib.dm_swiglu_fwd_quant_mxfp8_rowcol_at(A(ft, 1, _SRC_X), recv, R, F, clamped, alpha, limit,
+                                                          A(ft, 1, _A_Q), A(ft, 1, _A_SF), A(ft, 1, _COL_Q),
+                                                          A(ft, 1, _COL_SF), None, st),
+              "dm_swiglu_fwd_quant_mxfp8_rowcol_at")
+    nat.check(nat.lib.dm_gemm_blockscaled(0, A(ft, 1, _A_Q), A(ft, 1, _A_SF), p2.fprop_data.data_ptr(),
+                                          p2.fprop_scale.data_ptr(), none, none, c.sct.data_ptr(), none, None,
+                                          c.offsets.data_ptr(), el, R, D, F, 0, 0, 1.0, 0.0, None, state.num_sms, status,
+                                          st), "dm_gemm_blockscaled(w2)")
+    state.barrier(state.combine)
+    out = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+    post = options.experts_output_postprocess
+    is_norm = isinstance(post, RMSNormPostprocess)
+    c.rstd = None
+    if is_norm:
+        from ._postprocess import rmsnorm_combine_forward
+
+        c.rstd = rmsnorm_combine_forward(state, c, post, scores, ids, out, save=True)
+    elif post is not None:
+        raise NotImplementedError("callable expert-output post-processing runs on the BF16 eager path only")
+    else:
+        # the expert outputs go to the slot (when the layer is saved) only if the score gradient will read them
+        nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
+                                           int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                           int(ids.dtype == torch.int64), out.data_ptr(), T, K, D,
+                                           arena if need_h3 else None, fs[4:5].data_ptr() if need_h3 else None,
+                                           c.cond.data_ptr() if need_h3 else None, 0, st), "dm_scale_and_sum")
+    state.last_recv = c.recv
+    state.last_train_call = c
+    return out, c
+
+
+def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_param, grad_out, options, needs,
+                            wgrad_explicit=(None, None)):
+    from ._bf16 import _wgrad_destination
+
+    cfg = state.config
+    D, F, K = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k
+    T, R, el, ep, dev = c.T, c.R, state.e_local, state.ep, grad_out.device
+    st, status = nat.stream_ptr(), state.status.data_ptr()
+    clamped = 1 if cfg.activation == "swiglu_clamped" else 0
+    alpha, limit = float(cfg.swiglu_alpha), float(cfg.swiglu_limit)
+    need_x, need_scores, need_w13, need_w2 = needs
+    recv, offs = c.recv.data_ptr(), c.offsets.data_ptr()
+    none = nat.Operand(None, 0, None)
+    arena, combine = state.arena.data_ptr(), state.combine.local().data_ptr()
+    bo = torch.empty(16, dtype=torch.int64, device=dev)
+    bt = torch.empty(54, dtype=torch.int64, device=dev)
+    nat.check(nat.lib.dm_plan_bwd_blockscaled(
+        recv, c.per_rank.data_ptr(), state.saved_bytes.data_ptr(), state.buffer_offsets.data_ptr(),
+        state.peak_min_free.data_ptr(), c.need.data_ptr(), c.fwd_state.data_ptr(), bo.data_ptr(), bt.data_ptr(),
+        state.moe_layer_id.data_ptr(), ep, cfg.max_num_local_input_tokens, K, D, F, _storage_array(state),
+        state.capacity_rows, state.slot_bytes, state.num_slots, 0, 0, status, st), "dm_plan_bwd_blockscaled")
+    A = lambda group, entry: state.arena_operand(bt[group * 9 + entry:group * 9 + entry + 1])  # noqa: E731
+    fs, cond = c.fwd_state, c.cond
+    post = options.experts_output_postprocess
+    is_norm = isinstance(post, RMSNormPostprocess)
+    # ---- recompute block: every launch is a no-op unless the forward chose to recompute this layer ------------
+    with record_function("dist_moe_recompute"):
+        nat.check(nat.lib.dm_cond_copy(arena, fs[0:1].data_ptr(), state.dispatch.local().data_ptr(), None, T * D * 2,
+                                       cond.data_ptr(), 1, st), "dm_cond_copy(republish x)")
+        state.barrier(state.dispatch, cond)
+        nat.check(nat.lib.dm_quant_mxfp8_rowcol_gather_at(c.fwd.data_ptr(), recv, R, D, A(0, _A_Q), A(0, _A_SF),
+                                                          A(0, _COL_Q), A(0, _COL_SF), cond.data_ptr(), st),
+                  "dm_quant_mxfp8_rowcol_gather_at(x recompute)")
+        nat.check(nat.lib.dm_gemm_blockscaled(0, A(0, _A_Q), A(0, _A_SF), c.p13.fprop_data.data_ptr(),
+                                              c.p13.fprop_scale.data_ptr(), A(0, _C), none, None, none, None, offs, el,
+                                              R, 2 * F, D, 0, 0, 1.0, 0.0, cond.data_ptr(), state.num_sms, status, st),
+                  "dm_gemm_blockscaled(w13 recompute)")
+        nat.check(nat.lib.dm_swiglu_fwd_quant_mxfp8_rowcol_at(A(1, _SRC_X), recv, R, F, clamped, alpha, limit,
+                                                              A(1, _A_Q), A(1, _A_SF), A(1, _COL_Q), A(1, _COL_SF),
+                                                              cond.data_ptr(), st),
+                  "dm_swiglu_fwd_quant_mxfp8_rowcol_at(recompute)")
+        if need_scores or is_norm:
+            # the expert outputs again, scattered to their owners' combine buffers
+            nat.check(nat.lib.dm_gemm_blockscaled(0, A(1, _A_Q), A(1, _A_SF), c.p2.fprop_data.data_ptr(),
+                                                  c.p2.fprop_scale.data_ptr(), none, none, c.sct.data_ptr(), none, None,
+                                                  offs, el, R, D, F, 0, 0, 1.0, 0.0, cond.data_ptr(), state.num_sms,
+                                                  status, st), "dm_gemm_blockscaled(w2 recompute)")
+            if is_norm:  # the fused RMSNorm backward works on the expert outputs in place in the combine buffer
+                nat.check(nat.lib.dm_cond_copy(arena, fs[4:5].data_ptr(), combine, None, T * K * D * 2,
+                                               cond.data_ptr(), 0, st), "dm_cond_copy(load h3)")
+            state.barrier(state.combine, cond)
+    # ---- gradient with respect to the expert outputs and the scores ------------------------------------------
+    grad_scores = torch.empty(T, K, dtype=torch.float32, device=dev) if need_scores else None
+    if is_norm:
+        from ._postprocess import rmsnorm_combine_backward
+
+        rmsnorm_combine_backward(state, c, post, grad_out, scores, ids, grad_scores)
+    elif need_scores:
+        nat.check(nat.lib.dm_broadcast_and_scale_select(grad_out.data_ptr(), scores.data_ptr(),
+                                                        int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                                        int(ids.dtype == torch.int64), arena, fs[4:5].data_ptr(),
+                                                        combine, cond.data_ptr(), combine, nat.ptr(grad_scores), T, K,
+                                                        D, st), "dm_broadcast_and_scale")
+    else:
+        nat.check(nat.lib.dm_broadcast_and_scale(grad_out.data_ptr(), scores.data_ptr(),
+                                                 int(scores.dtype == torch.bfloat16), ids.data_ptr(),
+                                                 int(ids.dtype == torch.int64), None, None, combine, None, T, K, D, st),
+                  "dm_broadcast_and_scale")
+    state.barrier(state.combine)
+    # ---- W2 ----------------------------------------------------------------------------------------------------
+    nat.check(nat.lib.dm_quant_mxfp8_rowcol_gather_at(c.sct.data_ptr(), recv, R, D, A(2, _A_Q), A(2, _A_SF),
+                                                      A(2, _COL_Q) if need_w2 else none,
+                                                      A(2, _COL_SF) if need_w2 else none, None, st),
+              "dm_quant_mxfp8_rowcol_gather_at(grad_h3)")
+    nat.check(nat.lib.dm_gemm_blockscaled_dgrad(A(2, _A_Q), A(2, _A_SF), c.p2.fprop_data.data_ptr(),
+                                                c.p2.dgrad_scale.data_ptr(), A(2, _C), None, offs, el, R, F, D, None,
+                                                state.num_sms, status, st), "dm_gemm_blockscaled_dgrad(w2)")
+    grad_w13 = grad_w2 = None
+    owners = options.wgrad_parameter_owners or (None, None)
+    if need_w2:
+        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1])
+        nat.check(nat.lib.dm_gemm_blockscaled_wgrad_compact(A(3, _A_Q), A(3, _A_SF), A(3, _B_Q), A(3, _B_SF),
+                                                            dst.data_ptr(), int(dst.dtype == torch.float32), acc, offs,
+                                                            el, R, D, F, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled_wgrad(w2)")
+        grad_w2 = dst.view(w2_param.shape) if ret else None
+    # ---- SwiGLU backward, W13 ---------------------------------------------------------------------------------
+    if need_x or need_w13:
+        nat.check(nat.lib.dm_swiglu_bwd_quant_mxfp8_at(A(4, _SRC_Y), A(4, _SRC_X), recv, R, F, clamped, alpha, limit,
+                                                       A(4, _A_Q) if need_x else none, A(4, _A_SF) if need_x else none,
+                                                       A(4, _COL_Q) if need_w13 else none,
+                                                       A(4, _COL_SF) if need_w13 else none, st),
+                  "dm_swiglu_bwd_quant_mxfp8_at")
+    if need_x:
+        nat.check(nat.lib.dm_gemm_blockscaled_dgrad(A(4, _A_Q), A(4, _A_SF), c.p13.fprop_data.data_ptr(),
+                                                    c.p13.dgrad_scale.data_ptr(), none, c.bwd.data_ptr(), offs, el, R, D,
+                                                    2 * F, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled_dgrad(w13)")
+    if need_w13:
+        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0])
+        nat.check(nat.lib.dm_gemm_blockscaled_wgrad_compact(A(5, _A_Q), A(5, _A_SF), A(5, _B_Q), A(5, _B_SF),
+                                                            dst.data_ptr(), int(dst.dtype == torch.float32), acc, offs,
+                                                            el, R, 2 * F, D, None, state.num_sms, status, st),
+                  "dm_gemm_blockscaled_wgrad(w13)")
+        grad_w13 = dst.view(w13_param.shape) if ret else None
+    grad_x = None
+    # unconditional, as in the reference (dist_moe/api.py:2580): peers may still be reading this rank's combine buffer
+    state.barrier(state.dispatch)
+    if need_x:
+        grad_x = torch.empty(x_shape, dtype=torch.bfloat16, device=dev)
+        nat.check(nat.lib.dm_scale_and_sum(state.dispatch.local().data_ptr(), None, 0, ids.data_ptr(),
+                                           int(ids.dtype == torch.int64), grad_x.data_ptr(), T, K, D, None, None, None,
+                                           0, st), "dm_scale_and_sum(reduce_from_topk)")
+    if grad_scores is not None and scores.dtype != torch.float32:
+        grad_scores = grad_scores.to(scores.dtype)
+    return grad_x, grad_scores, grad_w13, grad_w2
 
 
 def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
@@ -498,7 +733,7 @@ def _mxfp8_forward(state, x, ids, scores, p13, p2, options, need_h3: bool):
     state.barrier(state.dispatch)
     size = max((ep * T * min(K, el) + el * 127 + 127) // 128 * 128, 128)
     c = _TrainCall()
-    c.T, c.p13, c.p2 = T, p13, p2
+    c.T, c.p13, c.p2, c.planned = T, p13, p2, False
     R = c.R = min(size, state.capacity_rows // 128 * 128)
     counts = torch.empty(el, dtype=torch.int32, device=dev)
     per_rank = torch.empty(ep, dtype=torch.int32, device=dev)
@@ -661,9 +896,11 @@ class _Mxfp8Function(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, ids, scores, w13_param, w2_param, state, options, p13, p2):
         p13, p2 = _training_weights(w13_param, w2_param, p13, p2, state.config)
+        planned = PLANNED_ARENA and state.num_slots > 0 and options.swiglu_clip_stats_out_3 is None
         with record_function("dist_moe_forward"):
-            out, call = _mxfp8_forward(state, x.detach().contiguous(), ids, scores.detach(), p13, p2, options,
-                                       need_h3=scores.requires_grad)
+            forward = _mxfp8_forward_planned if planned else _mxfp8_forward
+            out, call = forward(state, x.detach().contiguous(), ids, scores.detach(), p13, p2, options,
+                                need_h3=scores.requires_grad)
         ctx.state, ctx.call, ctx.options, ctx.x_shape = state, call, options, x.shape
         ctx.save_for_backward(ids, scores, w13_param, w2_param)
         return out
@@ -673,6 +910,7 @@ class _Mxfp8Function(torch.autograd.Function):
         ids, scores, w13_param, w2_param = ctx.saved_tensors
         needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
         with torch.cuda.device(ctx.state.device), record_function("dist_moe_backward"):
-            gx, gs, gw13, gw2 = _mxfp8_backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param,
-                                                w2_param, grad_out.contiguous(), ctx.options, needs)
+            backward = _mxfp8_backward_planned if ctx.call.planned else _mxfp8_backward
+            gx, gs, gw13, gw2 = backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param, w2_param,
+                                         grad_out.contiguous(), ctx.options, needs)
         return gx, None, gs, gw13, gw2, None, None, None, None

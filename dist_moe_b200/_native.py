@@ -131,6 +131,15 @@ _SIGNATURES = {
         c_int,
         [Operand, Operand, Operand, Operand, _P, c_int, c_int, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P],
     ),
+    "dm_gemm_blockscaled_wgrad_compact": (
+        c_int,
+        [Operand, Operand, Operand, Operand, _P, c_int, c_int, _P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, _P],
+    ),
+    "dm_quant_mxfp8_rowcol_gather_at": (c_int, [_P, _P, c_int64, c_int64, Operand, Operand, Operand, Operand, _P, _P]),
+    "dm_swiglu_fwd_quant_mxfp8_rowcol_at": (
+        c_int, [Operand, _P, c_int64, c_int64, c_int, c_float, c_float, Operand, Operand, Operand, Operand, _P, _P]),
+    "dm_swiglu_bwd_quant_mxfp8_at": (
+        c_int, [Operand, Operand, _P, c_int64, c_int64, c_int, c_float, c_float, Operand, Operand, Operand, Operand, _P]),
     "dm_rmsnorm_combine_fwd": (
         c_int,
         [_P, _P, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int,

@@ -47,7 +47,7 @@ struct BsParams {
   const int* cond;
   int* status;
   int64_t sfb_group_bytes;
-  int e_local, max_rows, N, k_iters, fp4, swiglu, a_col_atoms, b_col_atoms;
+  int e_local, max_rows, N, k_iters, fp4, swiglu, a_col_atoms, b_col_atoms, compact_cols;
   int mode;       // 0 fprop (A, W K-major), 1 dgrad (W N-major), 2 wgrad (both operands MN-major, K = expert rows)
   int Kw;         // dgrad: rows of one expert's W (the contraction extent); wgrad: dW columns
   int out_fp32, accumulate;
@@ -192,6 +192,9 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
       const uint8_t* sfb_dyn = p.sfb + (p.sfb_off ? *p.sfb_off : 0);
       const uint32_t sf_bytes = atoms * 512;
       const int row_blocks = ((p.mode == 2 ? p.Kw : p.N) + 127) >> 7;  // 128-wide blocks of the B side
+      int a_col_atoms = p.a_col_atoms, b_col_atoms = p.b_col_atoms;
+      // column bundles sized by the device row count: their scale layout has rows/128 column atoms
+      if (p.mode == 2 && p.compact_cols) a_col_atoms = b_col_atoms = ((s_off[p.e_local] + 31) / 32 + 3) / 4;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const BsTile t = bs_decode(tile, e, s_tile_start, s_off, p.mode, n_tiles, p.k_iters);
@@ -199,13 +202,13 @@ __global__ void __launch_bounds__(kWdThreads, 1) blockscaled_wide_kernel(const _
         const uint8_t* sfb_row0;
         if (p.mode == 2) {
           // scales of the column-quantised operands: rows = features, columns = 32-row blocks of the packed rows
-          sfa_row = sfa + (static_cast<int64_t>(t.m_blk) * p.a_col_atoms + (t.row0 >> 7)) * 512;
-          sfb_row0 = sfb_dyn + (static_cast<int64_t>(t.n_blk * 2) * p.b_col_atoms + (t.row0 >> 7)) * 512;
+          sfa_row = sfa + (static_cast<int64_t>(t.m_blk) * a_col_atoms + (t.row0 >> 7)) * 512;
+          sfb_row0 = sfb_dyn + (static_cast<int64_t>(t.n_blk * 2) * b_col_atoms + (t.row0 >> 7)) * 512;
         } else {
-          sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * p.a_col_atoms * 512;
-          sfb_row0 = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk * 2) * p.b_col_atoms * 512;
+          sfa_row = sfa + static_cast<int64_t>(t.row0 >> 7) * a_col_atoms * 512;
+          sfb_row0 = p.sfb + t.e * p.sfb_group_bytes + static_cast<int64_t>(t.n_blk * 2) * b_col_atoms * 512;
         }
-        const uint8_t* sfb_row1 = sfb_row0 + static_cast<int64_t>(p.b_col_atoms) * 512;
+        const uint8_t* sfb_row1 = sfb_row0 + static_cast<int64_t>(b_col_atoms) * 512;
         const bool second = t.n_blk * 2 + 1 < row_blocks;  // the tile's upper 128 columns exist
         for (int kb = 0; kb < t.k_iters && ok; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag);
@@ -752,10 +755,10 @@ extern "C" int dm_gemm_blockscaled_dgrad(dm_operand dy, dm_operand sf_dy, const 
 // Weight gradient: dW[e][m, n] (+)= sum_{r in expert e} dY[r, m] * X[r, n].  Both operands are quantised
 // along the row dimension (32 rows share a scale, per column); their scales are blocked with the
 // feature as the row index and the 32-row block as the column index.
-extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col, dm_operand sf_x_col,
-                                         void* dw, int dw_is_fp32, int accumulate, const int32_t* expert_offsets,
-                                         int e_local, int64_t max_rows, int64_t M, int64_t N, const int* cond,
-                                         int num_sms, int* status, void* stream) {
+static int blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col, dm_operand sf_x_col, void* dw,
+                             int dw_is_fp32, int accumulate, const int32_t* expert_offsets, int e_local,
+                             int64_t max_rows, int64_t M, int64_t N, const int* cond, int num_sms, int* status,
+                             void* stream, int compact_cols) {
   if (!dy_col.base || !sf_dy_col.base || !x_col.base || !sf_x_col.base || !dw || !expert_offsets || e_local <= 0 ||
       max_rows < 0 || M <= 0 || N <= 0)
     return kRcBadArg;
@@ -788,8 +791,28 @@ extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col
   p.N = static_cast<int>(M);
   p.Kw = static_cast<int>(N);
   p.mode = 2;
+  p.compact_cols = compact_cols;
   p.out_fp32 = dw_is_fp32 ? 1 : 0;
   p.accumulate = accumulate ? 1 : 0;
   p.act = ActParams{0, 1.0f, 0.0f};
   return bs_launch(p, num_sms, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col, dm_operand sf_x_col,
+                                         void* dw, int dw_is_fp32, int accumulate, const int32_t* expert_offsets,
+                                         int e_local, int64_t max_rows, int64_t M, int64_t N, const int* cond,
+                                         int num_sms, int* status, void* stream) {
+  return blockscaled_wgrad(dy_col, sf_dy_col, x_col, sf_x_col, dw, dw_is_fp32, accumulate, expert_offsets, e_local,
+                           max_rows, M, N, cond, num_sms, status, stream, 0);
+}
+
+// The same product for column bundles whose scale layout was sized by the device row count
+// (expert_offsets[e_local] rows, as the *_at quantisers write them) instead of by max_rows.
+extern "C" int dm_gemm_blockscaled_wgrad_compact(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col,
+                                                 dm_operand sf_x_col, void* dw, int dw_is_fp32, int accumulate,
+                                                 const int32_t* expert_offsets, int e_local, int64_t max_rows,
+                                                 int64_t M, int64_t N, const int* cond, int num_sms, int* status,
+                                                 void* stream) {
+  return blockscaled_wgrad(dy_col, sf_dy_col, x_col, sf_x_col, dw, dw_is_fp32, accumulate, expert_offsets, e_local,
+                           max_rows, M, N, cond, num_sms, status, stream, 1);
 }

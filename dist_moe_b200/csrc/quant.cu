@@ -275,16 +275,44 @@ __device__ __forceinline__ void slab_quantise(uint8_t* slab, int64_t rows, int64
   }
 }
 
+// Placement chosen on the device: each pointer is an allocation base and the byte offset is read from device memory
+// when the kernel starts (all null = the pointers are final).  `compact_cols` sizes the column-scale layout from the
+// device row count instead of max_rows, so that a column bundle occupies exactly dim * rows / 32 bytes; `cond`
+// (optional) turns the whole launch into a no-op when it reads 0.
+struct PlacedOffsets {
+  const int64_t* x;
+  const int64_t* x2;
+  const int64_t* q_col;
+  const int64_t* s_col;
+  const int64_t* q_row;
+  const int64_t* s_row;
+  const int* cond;
+  int compact_cols;
+};
+
+template <class T>
+__device__ __forceinline__ T* placed(T* base, const int64_t* off) {
+  if (base == nullptr || off == nullptr) return base;
+  return reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(base) + static_cast<uintptr_t>(*off));
+}
+
 template <int kSource>
 __global__ void __launch_bounds__(256) mxfp8_colrow_kernel(const uint4* __restrict__ x, const int64_t* __restrict__ row_ptrs,
                                                            ActParams act, const int32_t* num_rows,
                                                            int64_t max_rows, int C, uint8_t* __restrict__ q_col,
                                                            uint8_t* __restrict__ s_col, int blocked, int col_atoms,
                                                            uint8_t* __restrict__ q_row, uint8_t* __restrict__ s_row,
-                                                           int row_atoms) {
+                                                           int row_atoms, PlacedOffsets at) {
   __shared__ __align__(16) uint8_t slab[32 * kSlabRawStride];
+  if (at.cond != nullptr && *at.cond == 0) return;
   int64_t rows = num_rows ? *num_rows : max_rows;
   if (rows > max_rows) rows = max_rows;
+  x = placed(x, at.x);
+  q_col = placed(q_col, at.q_col);
+  s_col = placed(s_col, at.s_col);
+  q_row = placed(q_row, at.q_row);
+  s_row = placed(s_row, at.s_row);
+  if (at.compact_cols) col_atoms = static_cast<int>(((rows + 31) / 32 + 3) / 4);
   const int64_t row0 = static_cast<int64_t>(blockIdx.y) * 32;
   const int col0 = blockIdx.x * kSlabCols;
   if (row0 >= rows) return;
@@ -329,12 +357,20 @@ __global__ void __launch_bounds__(256) mxfp8_swiglu_bwd_colrow_kernel(const uint
                                                                       uint8_t* __restrict__ q_col,
                                                                       uint8_t* __restrict__ s_col, int col_atoms,
                                                                       uint8_t* __restrict__ q_row,
-                                                                      uint8_t* __restrict__ s_row, int row_atoms) {
+                                                                      uint8_t* __restrict__ s_row, int row_atoms,
+                                                                      PlacedOffsets at) {
   extern __shared__ __align__(16) uint8_t slabs[];  // two slabs
   uint8_t* slab_g = slabs;
   uint8_t* slab_u = slabs + 32 * kSlabRawStride;
   int64_t rows = num_rows ? *num_rows : max_rows;
   if (rows > max_rows) rows = max_rows;
+  h1 = placed(h1, at.x);
+  dz = placed(dz, at.x2);
+  q_col = placed(q_col, at.q_col);
+  s_col = placed(s_col, at.s_col);
+  q_row = placed(q_row, at.q_row);
+  s_row = placed(s_row, at.s_row);
+  if (at.compact_cols) col_atoms = static_cast<int>(((rows + 31) / 32 + 3) / 4);
   const int64_t row0 = static_cast<int64_t>(blockIdx.y) * 32;
   const int col0 = blockIdx.x * kSlabCols;
   if (row0 >= rows) return;
@@ -633,7 +669,7 @@ extern "C" int dm_quant_mxfp8_col(const void* x, const int32_t* num_rows, int64_
     const dim3 fast(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
     mxfp8_colrow_kernel<kSlabDense><<<fast, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(x), nullptr, ActParams{0, 1.0f, 0.0f}, num_rows, max_rows, static_cast<int>(C),
-        static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales), blocked, atoms, nullptr, nullptr, 0);
+        static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales), blocked, atoms, nullptr, nullptr, 0, PlacedOffsets{});
     return static_cast<int>(cudaGetLastError());
   }
   const dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>((max_rows + 31) / 32));
@@ -654,32 +690,45 @@ extern "C" int dm_quant_mxfp8_rowcol(const void* x, const int32_t* num_rows, int
   mxfp8_colrow_kernel<kSlabDense><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), nullptr, ActParams{0, 1.0f, 0.0f}, num_rows, max_rows, static_cast<int>(C),
       static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms,
-      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms, PlacedOffsets{});
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int dm_quant_mxfp8_rowcol_gather(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows, int64_t C,
-                                            void* q_row, void* scales_row_blocked, void* q_col,
-                                            void* scales_col_blocked, void* stream) {
-  if (!row_ptrs || !q_row || !scales_row_blocked || !q_col || !scales_col_blocked || max_rows < 0 || C <= 0 ||
+static int launch_rowcol_gather(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows, int64_t C,
+                                void* q_row, void* sf_row, void* q_col, void* sf_col, PlacedOffsets at, void* stream) {
+  if (!row_ptrs || !q_row || !sf_row || (q_col == nullptr) != (sf_col == nullptr) || max_rows < 0 || C <= 0 ||
       (C % 32) != 0)
-    return kRcBadArg;
+    return kRcBadArg;  // the column copy may be left out (a forward nothing will differentiate)
   if (max_rows == 0) return kRcOk;
   const dim3 grid(static_cast<unsigned>((C + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
   const int col_atoms = static_cast<int>(((max_rows + 31) / 32 + 3) / 4);
   const int row_atoms = static_cast<int>((C / 32 + 3) / 4);
   mxfp8_colrow_kernel<kSlabGather><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       nullptr, row_ptrs, ActParams{0, 1.0f, 0.0f}, num_rows, max_rows, static_cast<int>(C), static_cast<uint8_t*>(q_col),
-      static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms, static_cast<uint8_t*>(q_row),
-      static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+      static_cast<uint8_t*>(sf_col), 1, col_atoms, static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(sf_row),
+      row_atoms, at);
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* num_rows, int64_t max_rows, int64_t F,
-                                                int clamped, float alpha, float limit, void* q_row,
-                                                void* scales_row_blocked, void* q_col, void* scales_col_blocked,
-                                                void* stream) {
-  if (!h1 || !q_row || !scales_row_blocked || !q_col || !scales_col_blocked || max_rows < 0 || F <= 0 || (F % 32) != 0)
+extern "C" int dm_quant_mxfp8_rowcol_gather(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows, int64_t C,
+                                            void* q_row, void* scales_row_blocked, void* q_col,
+                                            void* scales_col_blocked, void* stream) {
+  return launch_rowcol_gather(row_ptrs, num_rows, max_rows, C, q_row, scales_row_blocked, q_col, scales_col_blocked,
+                              PlacedOffsets{}, stream);
+}
+
+extern "C" int dm_quant_mxfp8_rowcol_gather_at(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows,
+                                               int64_t C, dm_operand q_row, dm_operand sf_row, dm_operand q_col,
+                                               dm_operand sf_col, const int* cond, void* stream) {
+  PlacedOffsets at{nullptr, nullptr, q_col.offset, sf_col.offset, q_row.offset, sf_row.offset, cond, 1};
+  return launch_rowcol_gather(row_ptrs, num_rows, max_rows, C, q_row.base, sf_row.base, q_col.base, sf_col.base, at,
+                              stream);
+}
+
+static int launch_swiglu_fwd_quant(const void* h1, const int32_t* num_rows, int64_t max_rows, int64_t F, int clamped,
+                                   float alpha, float limit, void* q_row, void* sf_row, void* q_col, void* sf_col,
+                                   PlacedOffsets at, void* stream) {
+  if (!h1 || !q_row || !sf_row || (q_col == nullptr) != (sf_col == nullptr) || max_rows < 0 || F <= 0 || (F % 32) != 0)
     return kRcBadArg;
   if (max_rows == 0) return kRcOk;
   const dim3 grid(static_cast<unsigned>((F + kSlabCols - 1) / kSlabCols), static_cast<unsigned>((max_rows + 31) / 32));
@@ -687,16 +736,33 @@ extern "C" int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* n
   const int row_atoms = static_cast<int>((F / 32 + 3) / 4);
   mxfp8_colrow_kernel<kSlabSwiglu><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(h1), nullptr, ActParams{clamped, alpha, limit}, num_rows, max_rows, static_cast<int>(F),
-      static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), 1, col_atoms,
-      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+      static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(sf_col), 1, col_atoms, static_cast<uint8_t*>(q_row),
+      static_cast<uint8_t*>(sf_row), row_atoms, at);
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, const int32_t* num_rows, int64_t max_rows,
-                                        int64_t F, int clamped, float alpha, float limit, void* q_row,
-                                        void* scales_row_blocked, void* q_col, void* scales_col_blocked, void* stream) {
+extern "C" int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* num_rows, int64_t max_rows, int64_t F,
+                                                int clamped, float alpha, float limit, void* q_row,
+                                                void* scales_row_blocked, void* q_col, void* scales_col_blocked,
+                                                void* stream) {
+  return launch_swiglu_fwd_quant(h1, num_rows, max_rows, F, clamped, alpha, limit, q_row, scales_row_blocked, q_col,
+                                 scales_col_blocked, PlacedOffsets{}, stream);
+}
+
+extern "C" int dm_swiglu_fwd_quant_mxfp8_rowcol_at(dm_operand h1, const int32_t* num_rows, int64_t max_rows, int64_t F,
+                                                   int clamped, float alpha, float limit, dm_operand q_row,
+                                                   dm_operand sf_row, dm_operand q_col, dm_operand sf_col,
+                                                   const int* cond, void* stream) {
+  PlacedOffsets at{h1.offset, nullptr, q_col.offset, sf_col.offset, q_row.offset, sf_row.offset, cond, 1};
+  return launch_swiglu_fwd_quant(h1.base, num_rows, max_rows, F, clamped, alpha, limit, q_row.base, sf_row.base,
+                                 q_col.base, sf_col.base, at, stream);
+}
+
+static int launch_swiglu_bwd_quant(const void* h1, const void* grad_h2, const int32_t* num_rows, int64_t max_rows,
+                                   int64_t F, int clamped, float alpha, float limit, void* q_row, void* sf_row,
+                                   void* q_col, void* sf_col, PlacedOffsets at, void* stream) {
   if (!h1 || !grad_h2 || max_rows < 0 || F <= 0 || (F % 32) != 0) return kRcBadArg;
-  if ((q_row == nullptr) != (scales_row_blocked == nullptr) || (q_col == nullptr) != (scales_col_blocked == nullptr) ||
+  if ((q_row == nullptr) != (sf_row == nullptr) || (q_col == nullptr) != (sf_col == nullptr) ||
       (q_row == nullptr && q_col == nullptr))
     return kRcBadArg;
   if (max_rows == 0) return kRcOk;
@@ -712,9 +778,25 @@ extern "C" int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, co
   const int row_atoms = static_cast<int>((2 * F / 32 + 3) / 4);
   mxfp8_swiglu_bwd_colrow_kernel<<<grid, 256, kSmem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(h1), static_cast<const uint4*>(grad_h2), ActParams{clamped, alpha, limit}, num_rows,
-      max_rows, static_cast<int>(F), static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(scales_col_blocked), col_atoms,
-      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(scales_row_blocked), row_atoms);
+      max_rows, static_cast<int>(F), static_cast<uint8_t*>(q_col), static_cast<uint8_t*>(sf_col), col_atoms,
+      static_cast<uint8_t*>(q_row), static_cast<uint8_t*>(sf_row), row_atoms, at);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, const int32_t* num_rows, int64_t max_rows,
+                                        int64_t F, int clamped, float alpha, float limit, void* q_row,
+                                        void* scales_row_blocked, void* q_col, void* scales_col_blocked, void* stream) {
+  return launch_swiglu_bwd_quant(h1, grad_h2, num_rows, max_rows, F, clamped, alpha, limit, q_row, scales_row_blocked,
+                                 q_col, scales_col_blocked, PlacedOffsets{}, stream);
+}
+
+extern "C" int dm_swiglu_bwd_quant_mxfp8_at(dm_operand h1, dm_operand grad_h2, const int32_t* num_rows,
+                                           int64_t max_rows, int64_t F, int clamped, float alpha, float limit,
+                                           dm_operand q_row, dm_operand sf_row, dm_operand q_col, dm_operand sf_col,
+                                           void* stream) {
+  PlacedOffsets at{h1.offset, grad_h2.offset, q_col.offset, sf_col.offset, q_row.offset, sf_row.offset, nullptr, 1};
+  return launch_swiglu_bwd_quant(h1.base, grad_h2.base, num_rows, max_rows, F, clamped, alpha, limit, q_row.base,
+                                 sf_row.base, q_col.base, sf_col.base, at, stream);
 }
 
 extern "C" int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,

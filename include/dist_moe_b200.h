@@ -375,6 +375,14 @@ int dm_gemm_blockscaled_wgrad(dm_operand dy_col, dm_operand sf_dy_col, dm_operan
                               int dw_is_fp32, int accumulate, const int32_t* expert_offsets, int e_local,
                               int64_t max_rows, int64_t M, int64_t N, const int* cond, int num_sms, int* status,
                               void* stream);
+/* dm_gemm_blockscaled_wgrad for column bundles that the arena planner sized from the device row count: the scale
+ * layout of dY_col / X_col then has expert_offsets[e_local] / 128 column atoms instead of max_rows / 128, so that a
+ * bundle takes exactly dim * rows / 32 scale bytes (dist_moe/_activation_buffer_planner_kernel.py:146-161).  The
+ * *_at quantisers below write that layout. */
+int dm_gemm_blockscaled_wgrad_compact(dm_operand dy_col, dm_operand sf_dy_col, dm_operand x_col, dm_operand sf_x_col,
+                                      void* dw, int dw_is_fp32, int accumulate, const int32_t* expert_offsets,
+                                      int e_local, int64_t max_rows, int64_t M, int64_t N, const int* cond,
+                                      int num_sms, int* status, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Fused post-expert RMSNorm + weighted top-k reduction
@@ -446,6 +454,20 @@ int dm_swiglu_fwd_quant_mxfp8_rowcol(const void* h1, const int32_t* num_rows, in
 int dm_swiglu_bwd_quant_mxfp8(const void* h1, const void* grad_h2, const int32_t* num_rows, int64_t max_rows, int64_t F,
                               int clamped, float alpha, float limit, void* q_row, void* scales_row_blocked, void* q_col,
                               void* scales_col_blocked, void* stream);
+/* The three fused quantisers above with every activation pointer given as (allocation, device byte offset*), for
+ * bundles whose place the arena planner chose on the device (dist_moe/_blockscaled.py:461-507, 1260-1420 pass the
+ * planner's offset tables to the reference's quantisers in the same way).  Column scales use the compact layout
+ * (see dm_gemm_blockscaled_wgrad_compact); `num_rows` must be the padded row total the planner saw.  `cond`
+ * (optional) turns the launch into a no-op when it reads 0 (recompute launches in the backward). */
+int dm_quant_mxfp8_rowcol_gather_at(const int64_t* row_ptrs, const int32_t* num_rows, int64_t max_rows, int64_t C,
+                                    dm_operand q_row, dm_operand sf_row, dm_operand q_col, dm_operand sf_col,
+                                    const int* cond, void* stream);
+int dm_swiglu_fwd_quant_mxfp8_rowcol_at(dm_operand h1, const int32_t* num_rows, int64_t max_rows, int64_t F,
+                                        int clamped, float alpha, float limit, dm_operand q_row, dm_operand sf_row,
+                                        dm_operand q_col, dm_operand sf_col, const int* cond, void* stream);
+int dm_swiglu_bwd_quant_mxfp8_at(dm_operand h1, dm_operand grad_h2, const int32_t* num_rows, int64_t max_rows,
+                                 int64_t F, int clamped, float alpha, float limit, dm_operand q_row, dm_operand sf_row,
+                                 dm_operand q_col, dm_operand sf_col, void* stream);
 int dm_quant_mxfp8_tile32(const void* w, int64_t experts, int64_t N, int64_t K, void* q, void* row_scales,
                           void* col_scales, int blocked, void* stream);
 int dm_quant_nvfp4_token(const void* x, const int32_t* num_rows, int64_t max_rows, int64_t C, void* q,

@@ -139,9 +139,11 @@ def run_block_scaled_case(dm, group, rank, world, dev, fmt, T, D, F, K, E):
         ctx.close()
 
 
-def run_mxfp8_training_case(dm, group, rank, world, dev, T, D, F, K, E):
+def run_mxfp8_training_case(dm, group, rank, world, dev, T, D, F, K, E, recompute=False):
     """MXFP8 forward + backward across ranks (bf16 rows dispatched, quantised by the expert rank); the reference's
     two-rank block-scaled widths and bounds (tests/test_dist_moe.py:317-322: relative L2 < 0.075, cosine > 0.9975).
+    ``recompute`` sizes the activation slot for the dense input only, so that every rank's planner decides to rebuild
+    the layer in the backward (input republished, conditional barriers taken by all ranks).
     The algorithm's own error at these widths is about 0.065 (two E4M3 GEMMs in sequence), so the cosine floor
     (equivalent to a relative L2 of 0.0707) leaves little room; 512 tokens per rank instead of the reference's 128
     keep the sampling noise of the aggregate (about 0.065 / sqrt(2 * samples)) well inside that room."""
@@ -152,7 +154,9 @@ def run_mxfp8_training_case(dm, group, rank, world, dev, T, D, F, K, E):
     gos = [torch.randn(T, D, generator=gen).bfloat16() for _ in range(world)]
     cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
                     max_moe_layers_per_activation_slot=1, device_scratch_capacity_factor=float(world),
-                    block_scaled=dm.BlockScaledConfig())
+                    block_scaled=dm.BlockScaledConfig(),
+                    **(dict(activation_slot_bytes=(T * D * 2 + 127) // 128 * 128) if recompute else
+                       dict(activation_slot_capacity_factor=float(world))))
     ctx = dm.create_context(group=group, config=cfg, device=dev)
     try:
         xr = [x.clone().requires_grad_(True) for x in xs]
@@ -167,6 +171,8 @@ def run_mxfp8_training_case(dm, group, rank, world, dev, T, D, F, K, E):
             wa = w13[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
             wb = w2[rank * el:(rank + 1) * el].to(dev).requires_grad_(True)
             out = dm.routed_experts(x, ids[rank].to(dev), s, wa, wb, ctx)
+            decision = bool(ctx._state.last_train_call.need.item())
+            assert decision == recompute, ("MXFP8 training planner decision", rank, decision)
             out.backward(gos[rank].to(dev))
             ctx.check_status()
             pairs = ((out, refs[rank]), (x.grad, xr[rank].grad), (s.grad, sr[rank].grad),
@@ -195,6 +201,7 @@ def main():
     run_block_scaled_case(dm, group, rank, world, dev, "MXFP8_E4M3", 200, 512, 256, 4, 4 * world)
     run_block_scaled_case(dm, group, rank, world, dev, "NVFP4", 130, 512, 256, 2, 4 * world)
     run_mxfp8_training_case(dm, group, rank, world, dev, 512, 1024, 1024, 2, 2 * world)
+    run_mxfp8_training_case(dm, group, rank, world, dev, 512, 1024, 1024, 2, 2 * world, recompute=True)
     dist.barrier()
     if rank == 0:
         print("MULTI_RANK_OK", world, flush=True)

@@ -1,0 +1,167 @@
+"""MXFP8 training with activations placed by the device planner (bundles in the context's arena) against the same
+kernels run on per-call tensors: placement must not change a single bit of the output or of any gradient, whether the
+planner saves the layer, recomputes it, or stacks two layers in one slot; afterwards the planner state is rewound and
+the peak counters show the slot and the scratch region in use.  The column bundles use the compact scale layout
+(sized by the device row count), which the weight-gradient GEMM must read back identically."""
+
+import pytest
+import torch
+
+from tests.test_bf16_layer_gpu import make_case
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+def _align(v):
+    return (v + 127) // 128 * 128
+
+
+def _context(dm, T, D, F, K, E, layers=1, slot_bytes=None, **kw):
+    sizing = dict(activation_slot_capacity_factor=1.0) if slot_bytes is None else dict(activation_slot_bytes=slot_bytes)
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=layers, block_scaled=dm.BlockScaledConfig(), **sizing, **kw)
+    return dm.create_context(group=None, config=cfg, device=0)
+
+
+def _leaves(*tensors):
+    return tuple(t.detach().clone().to(DEV).requires_grad_() for t in tensors)
+
+
+def _rewound(ctx):
+    st = ctx._state
+    n = st.num_slots
+    assert st.buffer_offsets.tolist()[:n] == [i * st.slot_bytes for i in range(n)]
+    assert not st.saved_bytes.any().item() and not st.moe_layer_id.any().item()
+
+
+def _run(dm, ctx, case, planned, *, options=None, grads=(True, True, True, True), layers=1):
+    """forward (+ second stacked layer) and backward; returns (outputs and grads, recompute decisions)."""
+    import dist_moe_b200._blockscaled as bs
+
+    x, ids, scores, w13, w2 = case
+    bs.PLANNED_ARENA = planned
+    try:
+        leaves = _leaves(x, scores, w13, w2)
+        for leaf, wanted in zip(leaves, grads):
+            leaf.requires_grad_(wanted)
+        ids_d = ids.to(DEV)
+        kw = {} if options is None else dict(options=options)
+        if layers > 1:
+            ctx.select_activation_slot(0, layers)
+        h, decisions = leaves[0], []
+        for _ in range(layers):
+            h = dm.routed_experts(h, ids_d, leaves[1], leaves[2], leaves[3], ctx, **kw)
+            if planned:
+                decisions.append(ctx._state.last_train_call.need)
+        g = torch.randn(h.shape, generator=torch.Generator().manual_seed(5)).bfloat16().to(DEV)
+        h.backward(g)
+        ctx.check_status()
+        got = [h.detach()] + [leaf.grad for leaf in leaves]
+        return got, [bool(d.item()) for d in decisions]
+    finally:
+        bs.PLANNED_ARENA = True
+
+
+def _same(a, b):
+    for i, (p, q) in enumerate(zip(a, b)):
+        assert (p is None) == (q is None), i
+        if p is not None:
+            assert torch.equal(p, q), f"tensor {i} differs between arena placement and per-call tensors"
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+@pytest.mark.parametrize("T,D,F,K,E", [(200, 512, 384, 4, 8), (64, 256, 256, 2, 4), (16, 256, 128, 2, 8)])
+def test_planned_placement_is_bit_identical(T, D, F, K, E, recompute):
+    import dist_moe_b200 as dm
+
+    case = make_case(T, D, F, K, E, seed=T + K, w_scale=D**-0.5)
+    slot = _align(T * D * 2) + 256 if recompute else None  # room for the dense input only
+    ctx = _context(dm, T, D, F, K, E, slot_bytes=slot)
+    try:
+        planned, decisions = _run(dm, ctx, case, True)
+        assert decisions == [recompute]
+        _rewound(ctx)
+        info = ctx.check_overflow()
+        assert info.scratch_max_used > 0 and info.slot_max_used[0] > 0
+        again, _ = _run(dm, ctx, case, True)
+        _same(planned, again)
+        plain, _ = _run(dm, ctx, case, False)
+        _same(planned, plain)
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("grads", [(True, False, True, True), (False, True, False, True), (True, True, True, False),
+                                   (False, False, True, False)])
+@pytest.mark.parametrize("recompute", [False, True])
+def test_partial_gradients(grads, recompute):
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 96, 256, 384, 2, 4
+    case = make_case(T, D, F, K, E, seed=9, w_scale=D**-0.5)
+    ctx = _context(dm, T, D, F, K, E, slot_bytes=_align(T * D * 2) if recompute else None)
+    try:
+        planned, decisions = _run(dm, ctx, case, True, grads=grads)
+        assert decisions == [recompute]
+        _rewound(ctx)
+        plain, _ = _run(dm, ctx, case, False, grads=grads)
+        _same(planned, plain)
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("slot_kind", ["both_saved", "second_recomputed", "both_recomputed"])
+def test_two_layers_stacked_in_one_slot(slot_kind):
+    import dist_moe_b200 as dm
+    from oracle import planner_blockscaled as ob
+
+    T, D, F, K, E = 512, 256, 256, 2, 4
+    case = make_case(T, D, F, K, E, seed=3, w_scale=D**-0.5)
+    ids = case[1]
+    x_mem, h3_mem = _align(T * D * 2), _align(T * K * D * 2)
+    # what the planner charges for a saved layer (unpadded rows) and what its bundles occupy (rows padded per expert)
+    charged = ob._saved_cost(T * K, h3_mem, D, F, ob.MXFP8, False)
+    padded = sum((int((ids == e).sum()) + 127) // 128 * 128 for e in range(E))
+    placed = sum(ob.col_sizes(padded, D, ob.MXFP8)) + _align(padded * 2 * F * 2) + sum(ob.col_sizes(padded, F, ob.MXFP8)) \
+        + h3_mem
+    middle = max(charged, placed) + x_mem + 1024  # layer 1 fits with room for layer 2's input, layer 2 does not
+    assert middle < 2 * charged
+    slot = {"both_saved": 2 * placed + 4096, "second_recomputed": middle, "both_recomputed": 2 * x_mem}[slot_kind]
+    ctx = _context(dm, T, D, F, K, E, layers=2, slot_bytes=slot)
+    try:
+        planned, decisions = _run(dm, ctx, case, True, layers=2)
+        expect = {"both_saved": [False, False], "second_recomputed": [False, True], "both_recomputed": [True, True]}
+        assert decisions == expect[slot_kind], (decisions, slot, charged, placed)
+        _rewound(ctx)
+        plain, _ = _run(dm, ctx, case, False, layers=2)
+        _same(planned, plain)
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_fused_rmsnorm_on_the_planned_path(recompute):
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 64, 256, 256, 2, 4
+    case = make_case(T, D, F, K, E, seed=17, w_scale=D**-0.5)
+    ctx = _context(dm, T, D, F, K, E, slot_bytes=_align(T * D * 2) if recompute else None)
+    try:
+        post = dm.RMSNormPostprocess(eps=1e-5, norm_output_dtype=torch.float32, output_dtype=torch.bfloat16)
+        opts = dm.ExecutionOptions(experts_output_postprocess=post)
+        planned, decisions = _run(dm, ctx, case, True, options=opts)
+        assert decisions == [recompute]
+        _rewound(ctx)
+        plain, _ = _run(dm, ctx, case, False, options=opts)
+        _same(planned, plain)
+    finally:
+        ctx.close()
+
+
+def test_slot_below_the_mandatory_inputs_is_refused_at_planning_time():
+    import dist_moe_b200 as dm
+
+    T, D = 64, 256
+    with pytest.raises(ValueError, match="below the minimum"):
+        _context(dm, T, D, 256, 2, 4, slot_bytes=_align(T * D * 2) - 128)

@@ -117,7 +117,10 @@ def test_kernels_match_reference_kernels(name):
             assert table.tolist() == step["table"]
         got = dict(buffer_offsets=offs.tolist(), saved=saved.tolist(), peak=peak.tolist(), layer=layer.tolist())
         assert got == step["state"], (step["op"], got, step["state"])
-    assert status[0].item() == 0
+    # two recorded scenarios run out of room (the reference's device assertion is inert under the interpreter): the
+    # numbers still match, and the status word says so
+    overflowed = min(min(step["state"]["peak"]) for step in c["steps"]) < 0
+    assert nat.STATUS_NAMES[status[0].item()] == ("activation arena overflow" if overflowed else "ok")
 
 
 @pytest.mark.gpu

@@ -235,8 +235,12 @@ def _workspace(state):
     ws = getattr(state, "_bs_workspace", None)
     if ws is None:
         lay = _Layout(state)
-        if lay.total <= state.arena.numel():
-            buf = state.arena
+        # only the shared scratch region may be used: on a training context the activation slots in front of it hold
+        # what earlier forwards saved for their backward, and a no-grad call (an evaluation step, the first pass of a
+        # checkpointed region) must leave them alone
+        scratch = state.arena[state.num_slots * state.slot_bytes:]
+        if lay.total <= scratch.numel():
+            buf = scratch
         else:  # the reference aliases x and h2 row slots; this layout keeps them apart and may need more room
             buf = torch.zeros(lay.total, dtype=torch.uint8, device=state.device)
         ws = (lay, buf)

@@ -225,6 +225,7 @@ class ContextState:
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
+        self._bs_workspace = None  # a view of the arena's scratch region (block-scaled forward-only calls)
         if getattr(self, "vmm_arena", None) is not None:
             self.arena = None
             self.vmm_arena.close()

@@ -165,3 +165,60 @@ def test_slot_below_the_mandatory_inputs_is_refused_at_planning_time():
     T, D = 64, 256
     with pytest.raises(ValueError, match="below the minimum"):
         _context(dm, T, D, 256, 2, 4, slot_bytes=_align(T * D * 2) - 128)
+
+
+def test_no_grad_call_between_forward_and_backward_leaves_the_slot_alone():
+    """An evaluation step (or the first pass of a checkpointed region) on the same context runs on the scratch region
+    only; the activations an earlier forward saved in its slot survive it."""
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 96, 256, 256, 2, 4
+    x, ids, scores, w13, w2 = make_case(T, D, F, K, E, seed=41, w_scale=D**-0.5)
+    ctx = _context(dm, T, D, F, K, E)
+    try:
+        ids_d = ids.to(DEV)
+        g = torch.randn(T, D, generator=torch.Generator().manual_seed(6)).bfloat16().to(DEV)
+        results = []
+        for interleave in (False, True):
+            leaves = _leaves(x, scores, w13, w2)
+            out = dm.routed_experts(leaves[0], ids_d, leaves[1], leaves[2], leaves[3], ctx)
+            assert not bool(ctx._state.last_train_call.need.item())  # saved in the slot
+            if interleave:
+                with torch.no_grad():
+                    other = dm.routed_experts(torch.randn_like(leaves[0]), ids_d.flip(0), leaves[1], leaves[2],
+                                              leaves[3], ctx)
+                assert torch.isfinite(other.float()).all()
+            out.backward(g)
+            ctx.check_status()
+            results.append([out.detach()] + [leaf.grad for leaf in leaves])
+        _same(results[0], results[1])
+        _rewound(ctx)
+    finally:
+        ctx.close()
+
+
+def test_backward_rewinds_the_slot_its_forward_used():
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 64, 256, 256, 2, 4
+    case = make_case(T, D, F, K, E, seed=43, w_scale=D**-0.5)
+    x, ids, scores, w13, w2 = case
+    ctx = _context(dm, T, D, F, K, E, num_activation_slots=2)
+    try:
+        ids_d = ids.to(DEV)
+        ctx.select_activation_slot(0, 1)
+        ref_leaves = _leaves(x, scores, w13, w2)
+        ref = dm.routed_experts(ref_leaves[0], ids_d, ref_leaves[1], ref_leaves[2], ref_leaves[3], ctx)
+        g = torch.randn_like(ref)
+        ref.backward(g)
+        ctx.select_activation_slot(1, 1)
+        leaves = _leaves(x, scores, w13, w2)
+        out = dm.routed_experts(leaves[0], ids_d, leaves[1], leaves[2], leaves[3], ctx)
+        assert ctx._state.buffer_offsets[1].item() > ctx._state.slot_bytes  # slot 1 holds this call's bundles
+        ctx.select_activation_slot(0, 1)  # another microbatch selects slot 0 before this backward runs
+        out.backward(g)
+        ctx.check_status()
+        _same([ref.detach()] + [leaf.grad for leaf in ref_leaves], [out.detach()] + [leaf.grad for leaf in leaves])
+        _rewound(ctx)
+    finally:
+        ctx.close()

@@ -179,7 +179,10 @@ def forward_impl(state, x, ids, scores, w13, w2, options: ExecutionOptions, save
     if isinstance(post, RMSNormPostprocess):
         from ._postprocess import rmsnorm_combine_forward
 
-        c.rstd = rmsnorm_combine_forward(state, c, post, scores, ids, out, save=not scratch_only)
+        if hooks is not None:
+            hooks.observe_expert_output(state, post, ids, T)
+        c.rstd = rmsnorm_combine_forward(state, c, post, scores, ids, out, save=not scratch_only,
+                                         observers_allowed=hooks is not None)
     elif post is not None:
         if hooks is None:
             raise RuntimeError("a callable expert-output post-process runs on the eager path only")
@@ -280,7 +283,16 @@ def backward_impl(state, c: _Call, x_shape, ids, scores, w13, w2, w13_param, w2_
     if is_norm:
         from ._postprocess import rmsnorm_combine_backward
 
-        rmsnorm_combine_backward(state, c, post, grad_out, scores, ids, grad_scores)
+        kept = None
+        if hooks is not None:
+            # the replay of a recomputed layer shows its expert outputs to the forward observer again; whether the
+            # layer was recomputed is a device-side decision, read here because observers run on the host anyway
+            if post.observe_expert_output_fn is not None and bool(c.need.item()):
+                hooks.observe_expert_output(state, post, ids, T)
+            kept = hooks.preserved_expert_output(state, post, ids, T)
+        rmsnorm_combine_backward(state, c, post, grad_out, scores, ids, grad_scores, h3=kept)
+        if kept is not None:
+            hooks.observe_expert_output_grad(state, post, kept, T)
     elif is_callback:
         hooks.postprocess_backward(state, c, grad_out, scores, ids, grad_scores)
     else:

@@ -12,6 +12,9 @@ supplies the callback hooks and the autograd function that re-materialises the c
   score-weighted top-k sum; its backward runs through PyTorch autograd on the saved graph, so parameters the callable
   closes over accumulate their own gradients.  With ``zero_out_padded_callback_inputs`` the rows of dropped routes are
   zeroed first (``dm_zero_padded_rows``).
+* ``RMSNormPostprocess.observe_expert_output_fn(h3[T*K, D])`` sees the pre-norm expert outputs in every forward and in
+  the backward's replay of a recomputed layer; ``observe_expert_output_grad_fn(h3, grad_h3)`` sees the saved or
+  recomputed expert outputs together with their gradient.  Both are read-only taps for statistics.
 * ``wgrad_postprocess_fn(name, grad) -> grad | None``: called as soon as each weight gradient exists; ``None`` means the
   callback took ownership.
 * ``wgrad_destination_fn(name, shape, dtype, device) -> (tensor, accumulate)``: names the tensor a weight gradient is
@@ -68,6 +71,39 @@ class CallbackHooks:
         grad_routes = source.grad if source.grad is not None else torch.zeros_like(source)
         state.combine.local()[: T * K * D * 2].view(torch.bfloat16).view(T, K, D).copy_(grad_routes)
         call.callback_state = None
+
+    # ---- observers of the fused RMSNorm post-process (dist_moe/_postprocess.py:1245-1256, 1385-1412) --------
+    def _routes(self, state, T):
+        cfg = state.config
+        K, D = cfg.top_k, cfg.hidden_dim
+        return state.combine.local()[: T * K * D * 2].view(torch.bfloat16).view(T * K, D)
+
+    def observe_expert_output(self, state, post, ids, T) -> None:
+        """The pre-norm expert outputs [T*K, D], as they sit in the combine buffer (read-only for the observer)."""
+        fn = post.observe_expert_output_fn
+        if fn is None:
+            return
+        routes = self._routes(state, T)
+        if self.options.zero_out_padded_callback_inputs:
+            cfg = state.config
+            nat.check(nat.lib.dm_zero_padded_rows(routes.data_ptr(), ids.data_ptr(), int(ids.dtype == torch.int64), T,
+                                                  cfg.top_k, cfg.hidden_dim, nat.stream_ptr()), "dm_zero_padded_rows")
+        fn(routes)
+
+    def preserved_expert_output(self, state, post, ids, T):
+        """A copy of the expert outputs for the gradient observer: the fused backward then reads it and writes the
+        gradient to the combine buffer instead of working in place.  None when there is no such observer."""
+        if post.observe_expert_output_grad_fn is None:
+            return None
+        kept = self._routes(state, T).clone()
+        if self.options.zero_out_padded_callback_inputs:
+            cfg = state.config
+            nat.check(nat.lib.dm_zero_padded_rows(kept.data_ptr(), ids.data_ptr(), int(ids.dtype == torch.int64), T,
+                                                  cfg.top_k, cfg.hidden_dim, nat.stream_ptr()), "dm_zero_padded_rows")
+        return kept
+
+    def observe_expert_output_grad(self, state, post, kept, T) -> None:
+        post.observe_expert_output_grad_fn(kept, self._routes(state, T))
 
     # ---- weight gradients --------------------------------------------------------------------------------------
     def wgrad_destination(self, name: str, shape, dtype: torch.dtype, device):

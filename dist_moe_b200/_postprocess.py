@@ -15,7 +15,8 @@ from . import _native as nat
 from ._execution import RMSNormPostprocess
 
 
-def validate_rmsnorm(post: RMSNormPostprocess, *, config, training: bool, x_dtype: torch.dtype) -> None:
+def validate_rmsnorm(post: RMSNormPostprocess, *, config, training: bool, x_dtype: torch.dtype,
+                     observers_allowed: bool = False) -> None:
     if not isinstance(post.eps, (int, float)) or not math.isfinite(post.eps) or post.eps <= 0:
         raise ValueError("RMSNormPostprocess.eps must be finite and positive")
     if post.output_dtype != x_dtype:
@@ -24,8 +25,9 @@ def validate_rmsnorm(post: RMSNormPostprocess, *, config, training: bool, x_dtyp
         raise ValueError("RMSNormPostprocess.norm_output_dtype must be float32 or bfloat16")
     if post.use_kahan and post.weight is not None:
         raise ValueError("input-scale weight is not supported with Kahan summation")
-    if post.observe_expert_output_fn is not None or post.observe_expert_output_grad_fn is not None:
-        raise NotImplementedError("expert-output observers need eager callbacks, which dist_moe_b200 does not run")
+    if (post.observe_expert_output_fn is not None or post.observe_expert_output_grad_fn is not None) \
+            and not observers_allowed:
+        raise NotImplementedError("expert-output observers run on BF16 contexts only (the eager callback path)")
     if post.weight is not None:
         if training:
             raise ValueError("RMSNormPostprocess.weight is supported for inference only")
@@ -36,13 +38,13 @@ def validate_rmsnorm(post: RMSNormPostprocess, *, config, training: bool, x_dtyp
 
 
 def rmsnorm_combine_forward(state, call, post: RMSNormPostprocess, scores, ids, out, *, save: bool,
-                            save_to: torch.Tensor | None = None):
+                            save_to: torch.Tensor | None = None, observers_allowed: bool = False):
     """Normalise and reduce the expert outputs in the local combine buffer.  ``save`` keeps a copy of them for the
     backward: in the planner's slot (device-predicated on the call's save/recompute decision) or, when ``save_to``
     is given, unconditionally in that tensor."""
     cfg = state.config
     T, K, D = out.shape[0], cfg.top_k, cfg.hidden_dim
-    validate_rmsnorm(post, config=cfg, training=save, x_dtype=out.dtype)
+    validate_rmsnorm(post, config=cfg, training=save, x_dtype=out.dtype, observers_allowed=observers_allowed)
     rstd = None
     if save and not post.recompute_rstd:
         rstd = torch.empty(T, K, dtype=torch.float32, device=out.device)

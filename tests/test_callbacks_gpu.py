@@ -178,3 +178,68 @@ def test_training_call_dispatches_through_the_registered_operators():
         assert_close(eager[3], ref[3].grad, what="grad w13", **BF16_WGRAD)
     finally:
         ctx.close()
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_rmsnorm_observers_see_expert_outputs_and_their_gradient(recompute):
+    """``observe_expert_output_fn`` sees the pre-norm expert outputs in the forward (and again in the replay of a
+    recomputed layer), ``observe_expert_output_grad_fn`` the same outputs with their gradient; both are read-only
+    taps, so results are bit-identical to the run without them (dist_moe/_postprocess.py:1245-1256, 1385-1412)."""
+    import dist_moe_b200 as dm
+
+    x, ids, scores, w13, w2 = make_case(T, D, F, K, E, seed=12, drop=0.15, w_scale=D**-0.5)
+    sizing = dict(activation_slot_bytes=(T * D * 2 + 127) // 128 * 128) if recompute else \
+        dict(activation_slot_capacity_factor=1.0)
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, **sizing)
+    ctx = dm.create_context(group=None, config=cfg, device=DEV)
+    try:
+        seen_fwd, seen_bwd = [], []
+        plain = dm.RMSNormPostprocess(eps=1e-5, norm_output_dtype=torch.float32, output_dtype=torch.bfloat16)
+        tapped = dm.RMSNormPostprocess(eps=1e-5, norm_output_dtype=torch.float32, output_dtype=torch.bfloat16,
+                                       observe_expert_output_fn=lambda h3: seen_fwd.append(h3.clone()),
+                                       observe_expert_output_grad_fn=lambda h3, g: seen_bwd.append((h3.clone(), g.clone())))
+        g = torch.randn(T, D, generator=torch.Generator().manual_seed(8)).bfloat16().to(DEV)
+        results = []
+        for post in (plain, tapped):
+            leaves = [t.detach().clone().to(DEV).requires_grad_() for t in (x, scores, w13, w2)]
+            out = dm.routed_experts(leaves[0], ids.to(DEV), leaves[1], leaves[2], leaves[3], ctx,
+                                    options=dm.ExecutionOptions(experts_output_postprocess=post,
+                                                                zero_out_padded_callback_inputs=True))
+            out.backward(g)
+            ctx.check_status()
+            results.append([out.detach()] + [leaf.grad for leaf in leaves])
+        for a, b in zip(*results):
+            assert torch.equal(a, b)
+        assert len(seen_fwd) == (2 if recompute else 1) and len(seen_bwd) == 1
+        h3 = seen_fwd[0]
+        assert h3.shape == (T * K, D) and h3.dtype == torch.bfloat16
+        assert torch.equal(seen_fwd[-1], h3)                     # the replay rebuilt the same expert outputs
+        dropped = (ids.reshape(-1) < 0).to(DEV)
+        assert dropped.any() and not h3[dropped].any()            # rows of dropped routes were zeroed first
+        kept, grad = seen_bwd[0]
+        assert torch.equal(kept, h3) and grad.shape == h3.shape and torch.isfinite(grad.float()).all()
+        # the observed outputs reproduce the layer's result through the same normalise-and-reduce arithmetic
+        h = h3.float().view(T, K, D)
+        y = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)
+        ref = (y * scores.to(DEV).float().masked_fill(ids.to(DEV) < 0, 0.0).unsqueeze(-1)).sum(1)
+        assert_close(results[1][0], ref.cpu(), what="output from the observed expert outputs", **BF16_FWD)
+    finally:
+        ctx.close()
+
+
+def test_observers_are_refused_on_block_scaled_contexts():
+    import dist_moe_b200 as dm
+
+    cfg = dm.Config(max_num_local_input_tokens=T, hidden_dim=D, intermediate_dim=F, top_k=K, num_experts=E,
+                    max_moe_layers_per_activation_slot=1, block_scaled=dm.BlockScaledConfig())
+    ctx = dm.create_context(group=None, config=cfg, device=DEV)
+    try:
+        x, ids, scores, w13, w2 = make_case(T, D, F, K, E, seed=13, w_scale=D**-0.5)
+        post = dm.RMSNormPostprocess(eps=1e-5, norm_output_dtype=torch.float32, output_dtype=torch.bfloat16,
+                                     observe_expert_output_fn=lambda h3: None)
+        with pytest.raises(NotImplementedError):
+            dm.routed_experts(x.to(DEV).requires_grad_(True), ids.to(DEV), scores.to(DEV), w13.to(DEV), w2.to(DEV), ctx,
+                              options=dm.ExecutionOptions(experts_output_postprocess=post))
+    finally:
+        ctx.close()

@@ -278,11 +278,20 @@ def run_block_scaled(x, ids, scores, w13_weight, w2_weight, context: Any, option
     state = context._state
     cfg = state.config
     fmt = cfg.block_scaled.format
-    if options.requires_eager:
-        raise NotImplementedError("Python callbacks are not supported by dist_moe_b200")
     D, F, K, E = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k, cfg.num_experts
     if D % 128 or F % 128:
         raise ValueError("block-scaled execution needs hidden_dim and intermediate_dim to be multiples of 128")
+    if options.requires_eager:
+        # Python callbacks between launches (dist_moe/_blockscaled.py:2596-2700 `_run_blockscaled_eager`): MXFP8
+        # training calls on contexts with activation slots
+        post = options.experts_output_postprocess
+        if isinstance(post, RMSNormPostprocess):
+            raise NotImplementedError("expert-output observers run on BF16 contexts only")
+        if not save_for_backward or fmt is BlockScaledFormat.NVFP4 or state.num_slots == 0 \
+                or options.swiglu_clip_stats_out_3 is not None or isinstance(w13_weight, PreparedWeight):
+            raise NotImplementedError("Python callbacks on block-scaled contexts are supported for MXFP8 training calls "
+                                      "with tensor weights only")
+        return _EagerMxfp8Function.apply(x, ids, scores, w13_weight, w2_weight, state, options)
     if save_for_backward:
         if fmt is BlockScaledFormat.NVFP4:
             raise RuntimeError("NVFP4 is inference-only: it has no backward")
@@ -486,7 +495,8 @@ def _training_weights(w13_param, w2_param, p13, p2, cfg):
 
 class _TrainCall:
     __slots__ = ("T", "R", "offsets", "recv", "fwd", "bwd", "sct", "h1", "x_col", "x_col_sf", "h2_col", "h2_col_sf",
-                 "h3", "p13", "p2", "rstd", "planned", "per_rank", "need", "cond", "fwd_state", "fwd_table")
+                 "h3", "p13", "p2", "rstd", "planned", "per_rank", "need", "cond", "fwd_state", "fwd_table",
+                 "callback_state")
 
 
 # MXFP8 training keeps its activations in the context's arena, placed by the device planner (saved bundles in the
@@ -538,7 +548,7 @@ def _storage_array(state):
     return arr
 
 
-def _mxfp8_forward_planned(state, x, ids, scores, p13, p2, options, need_h3: bool):
+def _mxfp8_forward_planned(state, x, ids, scores, p13, p2, options, need_h3: bool, hooks=None):
     cfg = state.config
     D, F, K = cfg.hidden_dim, cfg.intermediate_dim, cfg.top_k
     T, dev, el, ep = x.shape[0], x.device, state.e_local, state.ep
@@ -547,7 +557,7 @@ def _mxfp8_forward_planned(state, x, ids, scores, p13, p2, options, need_h3: boo
     alpha, limit = float(cfg.swiglu_alpha), float(cfg.swiglu_limit)
     c = _TrainCall()
     c.planned, c.p13, c.p2 = True, p13, p2
-    c.h1 = c.x_col = c.x_col_sf = c.h2_col = c.h2_col_sf = c.h3 = None
+    c.h1 = c.x_col = c.x_col_sf = c.h2_col = c.h2_col_sf = c.h3 = c.callback_state = None
     _route_training(state, x, ids, options, c)
     R, recv = c.R, c.recv.data_ptr()
     c.need = torch.empty(1, dtype=torch.uint8, device=dev)
@@ -593,7 +603,9 @@ def _mxfp8_forward_planned(state, x, ids, scores, p13, p2, options, need_h3: boo
 
         c.rstd = rmsnorm_combine_forward(state, c, post, scores, ids, out, save=True)
     elif post is not None:
-        raise NotImplementedError("callable expert-output post-processing runs on the BF16 eager path only")
+        if hooks is None:
+            raise RuntimeError("a callable expert-output post-process runs on the eager path only")
+        hooks.postprocess_forward(state, c, post, scores, ids, out, save=True)  # keeps its own input and output
     else:
         # the expert outputs go to the slot (when the layer is saved) only if the score gradient will read them
         nat.check(nat.lib.dm_scale_and_sum(state.combine.local().data_ptr(), scores.data_ptr(),
@@ -607,7 +619,7 @@ def _mxfp8_forward_planned(state, x, ids, scores, p13, p2, options, need_h3: boo
 
 
 def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_param, w2_param, grad_out, options, needs,
-                            wgrad_explicit=(None, None)):
+                            wgrad_explicit=(None, None), hooks=None):
     from ._bf16 import _wgrad_destination
 
     cfg = state.config
@@ -631,6 +643,7 @@ def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_para
     fs, cond = c.fwd_state, c.cond
     post = options.experts_output_postprocess
     is_norm = isinstance(post, RMSNormPostprocess)
+    is_callback = post is not None and not is_norm  # the callable kept its own input and output (eager path)
     # ---- recompute block: every launch is a no-op unless the forward chose to recompute this layer ------------
     with record_function("dist_moe_recompute"):
         nat.check(nat.lib.dm_cond_copy(arena, fs[0:1].data_ptr(), state.dispatch.local().data_ptr(), None, T * D * 2,
@@ -647,7 +660,7 @@ def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_para
                                                               A(1, _A_Q), A(1, _A_SF), A(1, _COL_Q), A(1, _COL_SF),
                                                               cond.data_ptr(), st),
                   "dm_swiglu_fwd_quant_mxfp8_rowcol_at(recompute)")
-        if need_scores or is_norm:
+        if (need_scores or is_norm) and not is_callback:
             # the expert outputs again, scattered to their owners' combine buffers
             nat.check(nat.lib.dm_gemm_blockscaled(0, A(1, _A_Q), A(1, _A_SF), c.p2.fprop_data.data_ptr(),
                                                   c.p2.fprop_scale.data_ptr(), none, none, c.sct.data_ptr(), none, None,
@@ -663,6 +676,8 @@ def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_para
         from ._postprocess import rmsnorm_combine_backward
 
         rmsnorm_combine_backward(state, c, post, grad_out, scores, ids, grad_scores)
+    elif is_callback:
+        hooks.postprocess_backward(state, c, grad_out, scores, ids, grad_scores)
     elif need_scores:
         nat.check(nat.lib.dm_broadcast_and_scale_select(grad_out.data_ptr(), scores.data_ptr(),
                                                         int(scores.dtype == torch.bfloat16), ids.data_ptr(),
@@ -686,12 +701,14 @@ def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_para
     grad_w13 = grad_w2 = None
     owners = options.wgrad_parameter_owners or (None, None)
     if need_w2:
-        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1])
+        dst, acc, ret = _wgrad_destination(w2_param, (el, D, F), options, cfg, owners[1], wgrad_explicit[1], hooks, "w2")
         nat.check(nat.lib.dm_gemm_blockscaled_wgrad_compact(A(3, _A_Q), A(3, _A_SF), A(3, _B_Q), A(3, _B_SF),
                                                             dst.data_ptr(), int(dst.dtype == torch.float32), acc, offs,
                                                             el, R, D, F, None, state.num_sms, status, st),
                   "dm_gemm_blockscaled_wgrad(w2)")
         grad_w2 = dst.view(w2_param.shape) if ret else None
+        if hooks is not None:
+            grad_w2 = hooks.wgrad_postprocess("w2", grad_w2)
     # ---- SwiGLU backward, W13 ---------------------------------------------------------------------------------
     if need_x or need_w13:
         nat.check(nat.lib.dm_swiglu_bwd_quant_mxfp8_at(A(4, _SRC_Y), A(4, _SRC_X), recv, R, F, clamped, alpha, limit,
@@ -705,12 +722,15 @@ def _mxfp8_backward_planned(state, c: _TrainCall, x_shape, ids, scores, w13_para
                                                     2 * F, None, state.num_sms, status, st),
                   "dm_gemm_blockscaled_dgrad(w13)")
     if need_w13:
-        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0])
+        dst, acc, ret = _wgrad_destination(w13_param, (el, 2 * F, D), options, cfg, owners[0], wgrad_explicit[0], hooks,
+                                           "w13")
         nat.check(nat.lib.dm_gemm_blockscaled_wgrad_compact(A(5, _A_Q), A(5, _A_SF), A(5, _B_Q), A(5, _B_SF),
                                                             dst.data_ptr(), int(dst.dtype == torch.float32), acc, offs,
                                                             el, R, 2 * F, D, None, state.num_sms, status, st),
                   "dm_gemm_blockscaled_wgrad(w13)")
         grad_w13 = dst.view(w13_param.shape) if ret else None
+        if hooks is not None:
+            grad_w13 = hooks.wgrad_postprocess("w13", grad_w13)
     grad_x = None
     # unconditional, as in the reference (dist_moe/api.py:2580): peers may still be reading this rank's combine buffer
     state.barrier(state.dispatch)
@@ -918,3 +938,50 @@ class _Mxfp8Function(torch.autograd.Function):
             gx, gs, gw13, gw2 = backward(ctx.state, ctx.call, ctx.x_shape, ids, scores.detach(), w13_param, w2_param,
                                          grad_out.contiguous(), ctx.options, needs)
         return gx, None, gs, gw13, gw2, None, None, None, None
+
+
+class _EagerMxfp8Function(torch.autograd.Function):
+    """MXFP8 training with Python callbacks inside the launch sequence: compute weights materialised from their
+    sources (and quantised) in the forward and again before the backward, a callable post-process on the expert
+    outputs, named destinations and post-processing of the weight gradients."""
+
+    @staticmethod
+    def _weights(options, w13_source, w2_source, state):
+        from ._eager import _compute_weights
+
+        w13, w2 = _compute_weights(options, w13_source, w2_source, state)
+        return w13, w2, prepare_weight(w13, state.config), prepare_weight(w2, state.config)
+
+    @staticmethod
+    def forward(ctx, x, ids, scores, w13_source, w2_source, state, options):
+        from ._eager import CallbackHooks
+
+        if options.inplace_wgrad_accum and options.weights_preprocess_fn is not None:
+            raise ValueError("inplace_wgrad_accum needs compute weights that own their gradient; it cannot be combined "
+                             "with weights_preprocess_fn")
+        hooks = CallbackHooks(options)
+        _, _, p13, p2 = _EagerMxfp8Function._weights(options, w13_source, w2_source, state)
+        with record_function("dist_moe_forward"):
+            out, call = _mxfp8_forward_planned(state, x.detach().contiguous(), ids, scores.detach(), p13, p2, options,
+                                               need_h3=scores.requires_grad, hooks=hooks)
+        call.p13 = call.p2 = None  # re-materialised before the backward, as the reference does
+        ctx.state, ctx.call, ctx.options, ctx.hooks, ctx.x_shape = state, call, options, hooks, x.shape
+        ctx.save_for_backward(ids, scores, w13_source, w2_source)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ids, scores, w13_source, w2_source = ctx.saved_tensors
+        state, options, call = ctx.state, ctx.options, ctx.call
+        # compute weights are materialised again, as in the forward; the weight gradients take their shapes and are
+        # handed back in the sources' shapes
+        w13, w2, call.p13, call.p2 = _EagerMxfp8Function._weights(options, w13_source, w2_source, state)
+        needs = (ctx.needs_input_grad[0], ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4])
+        with torch.cuda.device(state.device), record_function("dist_moe_backward"):
+            gx, gs, g13, g2 = _mxfp8_backward_planned(state, call, ctx.x_shape, ids, scores.detach(), w13, w2,
+                                                      grad_out.contiguous(), options, needs, hooks=ctx.hooks)
+        if g13 is not None:
+            g13 = g13.reshape(w13_source.shape)
+        if g2 is not None:
+            g2 = g2.reshape(w2_source.shape)
+        return gx, None, gs, g13, g2, None, None

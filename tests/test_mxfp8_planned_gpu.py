@@ -222,3 +222,125 @@ def test_backward_rewinds_the_slot_its_forward_used():
         _rewound(ctx)
     finally:
         ctx.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Python callbacks on MXFP8 training calls (dist_moe/_blockscaled.py:2596-2700 `_run_blockscaled_eager`)
+# ---------------------------------------------------------------------------------------------------------------
+def _plain_run(dm, ctx, case, g):
+    x, ids, scores, w13, w2 = case
+    leaves = _leaves(x, scores, w13, w2)
+    out = dm.routed_experts(leaves[0], ids.to(DEV), leaves[1], leaves[2], leaves[3], ctx)
+    out.backward(g)
+    ctx.check_status()
+    return [out.detach()] + [leaf.grad for leaf in leaves]
+
+
+def test_weights_preprocess_fn_on_an_mxfp8_context():
+    """fp32 master weights of another shape are turned into bf16 compute weights (and quantised) in the forward and
+    again before the backward; the weight gradients come back in the sources' shapes, bit-identical to a plain call."""
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 96, 256, 256, 2, 4
+    case = make_case(T, D, F, K, E, seed=51, w_scale=D**-0.5)
+    x, ids, scores, w13, w2 = case
+    ctx = _context(dm, T, D, F, K, E)
+    try:
+        g = torch.randn(T, D, generator=torch.Generator().manual_seed(7)).bfloat16().to(DEV)
+        ref = _plain_run(dm, ctx, case, g)
+        calls = []
+
+        def preprocess(w):
+            calls.append(tuple(w.shape))
+            return w.to(torch.bfloat16).contiguous()
+
+        src13 = w13.float().reshape(E * 2 * F, D).to(DEV).requires_grad_(True)
+        src2 = w2.float().to(DEV).requires_grad_(True)
+        xs, ss = x.to(DEV).requires_grad_(True), scores.to(DEV).requires_grad_(True)
+        out = dm.routed_experts(xs, ids.to(DEV), ss, src13, src2, ctx,
+                                options=dm.ExecutionOptions(weights_preprocess_fn=preprocess))
+        out.backward(g)
+        ctx.check_status()
+        assert len(calls) == 4 and calls[0] == (E * 2 * F, D)
+        assert src13.grad.shape == src13.shape and src2.grad.shape == src2.shape
+        _same(ref, [out.detach(), xs.grad, ss.grad, src13.grad.reshape(ref[3].shape).to(ref[3].dtype),
+                    src2.grad.reshape(ref[4].shape).to(ref[4].dtype)])
+        _rewound(ctx)
+    finally:
+        ctx.close()
+
+
+def test_wgrad_callbacks_on_an_mxfp8_context():
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 96, 256, 256, 2, 4
+    case = make_case(T, D, F, K, E, seed=52, w_scale=D**-0.5)
+    x, ids, scores, w13, w2 = case
+    ctx = _context(dm, T, D, F, K, E)
+    try:
+        g = torch.randn(T, D, generator=torch.Generator().manual_seed(7)).bfloat16().to(DEV)
+        ref = _plain_run(dm, ctx, case, g)
+        taken = {}
+
+        def postprocess(name, grad):
+            if name == "w13":
+                taken[name] = grad.clone()
+                return None
+            return (grad.float() * 2).to(grad.dtype)
+
+        leaves = _leaves(x, scores, w13, w2)
+        out = dm.routed_experts(leaves[0], ids.to(DEV), leaves[1], leaves[2], leaves[3], ctx,
+                                options=dm.ExecutionOptions(wgrad_postprocess_fn=postprocess))
+        out.backward(g)
+        ctx.check_status()
+        assert leaves[2].grad is None and torch.equal(taken["w13"].reshape(ref[3].shape), ref[3])
+        assert torch.equal(leaves[3].grad, (ref[4].float() * 2).to(ref[4].dtype))
+        assert torch.equal(leaves[0].grad, ref[1])
+
+        dst = {"w13": torch.zeros(E, 2 * F, D, dtype=torch.bfloat16, device=DEV),
+               "w2": torch.full((E, D, F), 3.0, dtype=torch.bfloat16, device=DEV)}
+        leaves = _leaves(x, scores, w13, w2)
+        out = dm.routed_experts(leaves[0], ids.to(DEV), leaves[1], leaves[2], leaves[3], ctx,
+                                options=dm.ExecutionOptions(wgrad_destination_fn=lambda n, s, dt, dev: (dst[n], n == "w13")))
+        out.backward(g)
+        ctx.check_status()
+        assert leaves[2].grad is None and leaves[3].grad is None
+        assert torch.equal(dst["w13"].reshape(ref[3].shape), ref[3])     # added to zeros
+        assert torch.equal(dst["w2"].reshape(ref[4].shape), ref[4])      # overwritten
+        _rewound(ctx)
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_callable_postprocess_on_an_mxfp8_context(recompute):
+    """``y = post(h3)`` before the weighted top-k sum; identity gives the plain call bit for bit, a scaling callable
+    with a parameter of its own gets that parameter's gradient through the nested backward."""
+    import dist_moe_b200 as dm
+
+    T, D, F, K, E = 96, 256, 256, 2, 4
+    case = make_case(T, D, F, K, E, seed=53, w_scale=D**-0.5)
+    x, ids, scores, w13, w2 = case
+    ctx = _context(dm, T, D, F, K, E, slot_bytes=_align(T * D * 2) if recompute else None)
+    try:
+        g = torch.randn(T, D, generator=torch.Generator().manual_seed(7)).bfloat16().to(DEV)
+        ref = _plain_run(dm, ctx, case, g)
+        leaves = _leaves(x, scores, w13, w2)
+        out = dm.routed_experts(leaves[0], ids.to(DEV), leaves[1], leaves[2], leaves[3], ctx,
+                                options=dm.ExecutionOptions(experts_output_postprocess=lambda h3: h3 * 1.0))
+        assert bool(ctx._state.last_train_call.need.item()) == recompute
+        out.backward(g)
+        ctx.check_status()
+        _same(ref, [out.detach()] + [leaf.grad for leaf in leaves])
+        gain = torch.full((D,), 2.0, dtype=torch.bfloat16, device=DEV, requires_grad=True)
+        leaves = _leaves(x, scores, w13, w2)
+        out = dm.routed_experts(leaves[0], ids.to(DEV), leaves[1], leaves[2], leaves[3], ctx,
+                                options=dm.ExecutionOptions(experts_output_postprocess=lambda h3: h3 * gain))
+        out.backward(g)
+        ctx.check_status()
+        assert torch.allclose(out.float(), 2 * ref[0].float(), rtol=2e-2, atol=2e-2)
+        assert gain.grad is not None and torch.isfinite(gain.grad.float()).all() and gain.grad.abs().sum() > 0
+        assert torch.allclose(leaves[0].grad.float(), 2 * ref[1].float(), rtol=5e-2, atol=5e-2)
+        _rewound(ctx)
+    finally:
+        ctx.close()

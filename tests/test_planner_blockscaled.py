@@ -145,3 +145,125 @@ def test_overflow_sets_the_status_word_instead_of_asserting():
     torch.cuda.synchronize()
     assert nat.STATUS_NAMES[status[0].item()] == "activation arena overflow"
     assert peak[1].item() < 0  # the overflow is also visible in the peak counters
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Size-independent properties on seeded random scenarios (sizes up to the MXFP8 training configuration and beyond
+# 2**31 bytes), and the CUDA kernels against the oracle on the same scenarios.
+# ---------------------------------------------------------------------------------------------------------------
+def _random_scenarios(count=24, seed=1234):
+    import random
+
+    rng = random.Random(seed)
+    out = []
+    for i in range(count):
+        big = i % 6 == 0
+        ep = rng.choice([1, 2, 4, 8])
+        T = rng.choice([8192, 4096]) if big else rng.choice([16, 64, 200, 512])
+        K = rng.choice([2, 4, 8])
+        D = rng.choice([4096, 7168]) if big else rng.choice([128, 256, 512, 1024])
+        F = rng.choice([1536, 2048]) if big else rng.choice([128, 384, 512])
+        layers = rng.choice([1, 2, 3])
+        native, mega = rng.random() < 0.3, rng.random() < 0.3
+        storage = oracle_bs.NVFP4 if rng.random() < 0.3 else oracle_bs.MXFP8
+        calls = []
+        for _ in range(layers):
+            per_rank = [max(0, int(T * K * rng.uniform(0.2, 1.8))) for _ in range(ep)]
+            rows = (per_rank[0] + rng.randrange(0, 16) * 128 + 127) // 128 * 128
+            calls.append((rows, per_rank))
+        worst_rows = max(r for r, _ in calls)
+        x_mem = oracle_bs.packed_dispatch_size(T, D, storage) if native else oracle_planner.align(T * D * 2)
+        full = max(oracle_bs._saved_cost(max(p), oracle_planner.align(T * K * D * 2), D, F, storage, native)
+                   for _, p in calls)
+        # slot between "inputs only" and "everything saved", so that both decisions occur across scenarios
+        slot = oracle_planner.align(int(layers * x_mem + rng.uniform(0.0, 1.2) * layers * full) + 128 * 1024)
+        scratch = 8 * worst_rows * (D + 6 * F + 64) + (1 << 20)
+        out.append(dict(ep=ep, T=T, K=K, D=D, F=F, layers=layers, native=native, mega=mega, storage=storage,
+                        calls=calls, slot=slot, arena=slot + oracle_planner.align(scratch)))
+    return out
+
+
+def _live_ranges(fwd, bwd, sc, rows):
+    """(name, start, size) of what the backward reads or writes at the same time, from the two plans."""
+    s, D, F = sc["storage"], sc["D"], sc["F"]
+    xc = sum(oracle_bs.col_sizes(rows, D, s))
+    hc = sum(oracle_bs.col_sizes(rows, F, s))
+    dc = sum(oracle_bs.col_sizes(rows, 2 * F, s))
+    h1, g2 = oracle_planner.align(rows * 2 * F * 2), oracle_planner.align(rows * F * 2)
+    o = bwd["offsets"]
+    return [("x_col", o[7], xc), ("h1", o[1], h1), ("h2_col", o[9], hc), ("grad_h3_col", o[11], xc), ("grad_h2", o[3], g2),
+            ("dxy_col", o[13], dc)]
+
+
+def test_oracle_properties_on_random_scenarios():
+    decisions = set()
+    for sc in _random_scenarios():
+        st = oracle_planner.PlannerState(1, sc["ep"], sc["slot"], sc["arena"])
+        initial = st.snapshot()
+        kw = dict(T=sc["T"], K=sc["K"], D=sc["D"], F=sc["F"], storage=sc["storage"])
+        plans = []
+        for rows, per_rank in sc["calls"]:
+            f = oracle_bs.plan_forward(st, rows, per_rank, 0, num_layers=sc["layers"], mega=sc["mega"],
+                                       native=sc["native"], **kw)
+            decisions.add(f["need"])
+            assert all(v % 128 == 0 for v in f["offsets"][:9]), f
+            assert all(v == oracle_bs.MISSING or v % 128 == 0 for v in f["table"] if v != f["table"][15]), f
+            plans.append((rows, per_rank, f))
+        fits = min(st.peak) >= 0
+        for rows, per_rank, f in reversed(plans):
+            b = oracle_bs.plan_backward(st, rows, per_rank, f["need"], f["offsets"], mega=sc["mega"],
+                                        native=sc["native"], **kw)
+            assert all(v % 128 == 0 for v in b["offsets"][:14]), b
+            if not sc["native"] and fits and min(st.peak) >= 0:
+                live = sorted(_live_ranges(f, b, sc, rows), key=lambda r: r[1])
+                for (na, a0, an), (nb, b0, _) in zip(live, live[1:]):
+                    assert a0 + an <= b0, (na, nb, a0, an, b0)          # no two live tensors share a byte
+                assert live[-1][1] + live[-1][2] <= sc["arena"]
+        after = st.snapshot()
+        assert after["buffer_offsets"] == initial["buffer_offsets"] and after["saved"] == initial["saved"] \
+            and after["layer"] == initial["layer"]                       # LIFO: the slot is exactly rewound
+    assert decisions == {True, False}
+
+
+@pytest.mark.gpu
+def test_kernels_match_the_oracle_on_random_scenarios():
+    import ctypes
+
+    from dist_moe_b200 import _native as nat
+
+    dev = torch.device("cuda", 0)
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)  # noqa: E731
+    for sc in _random_scenarios():
+        ep = sc["ep"]
+        st = oracle_planner.PlannerState(1, ep, sc["slot"], sc["arena"])
+        storage = (ctypes.c_int * 6)(*sc["storage"].as_list())
+        offs, saved = i64(st.buffer_offsets), torch.zeros(ep, dtype=torch.int64, device=dev)
+        peak, layer, sel = i64(st.peak), torch.zeros(1, dtype=torch.int64, device=dev), i64([0])
+        status = torch.zeros(8, dtype=torch.int32, device=dev)
+        kw = dict(T=sc["T"], K=sc["K"], D=sc["D"], F=sc["F"], storage=sc["storage"])
+        dims = (ep, sc["T"], sc["K"], sc["D"], sc["F"], storage, 1 << 40, sc["slot"], 1)
+        held = []
+        for rows, per_rank in sc["calls"]:
+            want = oracle_bs.plan_forward(st, rows, per_rank, 0, num_layers=sc["layers"], mega=sc["mega"],
+                                          native=sc["native"], **kw)
+            r = torch.tensor([rows], dtype=torch.int32, device=dev)
+            pr = torch.tensor(per_rank, dtype=torch.int32, device=dev)
+            need = torch.zeros(1, dtype=torch.uint8, device=dev)
+            fo, ft = torch.zeros(10, dtype=torch.int64, device=dev), torch.zeros(18, dtype=torch.int64, device=dev)
+            nat.check(nat.lib.dm_plan_fwd_blockscaled(
+                r.data_ptr(), pr.data_ptr(), None, saved.data_ptr(), offs.data_ptr(), peak.data_ptr(), need.data_ptr(),
+                None, fo.data_ptr(), ft.data_ptr(), sel.data_ptr(), layer.data_ptr(), *dims, sc["layers"],
+                int(sc["mega"]), 0, 0, int(sc["native"]), 0, status.data_ptr(), nat.stream_ptr()), "plan_fwd_blockscaled")
+            assert bool(need.item()) == want["need"] and fo.tolist() == want["offsets"] and ft.tolist() == want["table"]
+            held.append((r, pr, need, fo, rows, per_rank, want))
+        for r, pr, need, fo, rows, per_rank, f in reversed(held):
+            want = oracle_bs.plan_backward(st, rows, per_rank, f["need"], f["offsets"], mega=sc["mega"],
+                                           native=sc["native"], **kw)
+            bo, bt = torch.zeros(16, dtype=torch.int64, device=dev), torch.zeros(54, dtype=torch.int64, device=dev)
+            nat.check(nat.lib.dm_plan_bwd_blockscaled(
+                r.data_ptr(), pr.data_ptr(), saved.data_ptr(), offs.data_ptr(), peak.data_ptr(), need.data_ptr(),
+                fo.data_ptr(), bo.data_ptr(), bt.data_ptr(), layer.data_ptr(), *dims, int(sc["mega"]), int(sc["native"]),
+                status.data_ptr(), nat.stream_ptr()), "plan_bwd_blockscaled")
+            assert bo.tolist() == want["offsets"] and bt.tolist() == want["table"]
+        assert dict(buffer_offsets=offs.tolist(), saved=saved.tolist(), peak=peak.tolist(), layer=layer.tolist()) \
+            == st.snapshot()
